@@ -1,0 +1,323 @@
+#!/usr/bin/env python
+"""Headline benchmark: aspin LM prefill tok/s (configuration 1) with decode ms/token and per-kernel roofline beside it.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Product arm (default). One step = LM.forward_carried over B=16 sequences of 2048 synthetic token ids per GPU, as four
+carried 512-token windows, on the random-init d768 / 12-layer / 12x64-head aspin LM with bf16 weights and fp32 state.
+Sequences are independent, so N GPUs run N such batches (weak scaling, no collective on the data path). Prints ONE JSON
+line on rank 0: `value` = tokens/s over all GPUs with inputs resident in HBM, timed per step with CUDA events on the
+launching stream (L2 flushed between steps), max over ranks; `e2e` = the same call with token ids coming from pinned
+host memory and the returned logits copied back, both copies inside the timed region; `roofline` = the chunked-prefill
+kernel alone at the workload's shape; `cpu_baseline` = the CPU oracle's forward_carried on a bounded sample of the same
+workload, timed on this host; `decode` = configuration 2 (ms/token at batch 1 and 64 and the state kernel's HBM GB/s).
+
+Reference arm (--impl reference). The reference's CPU implementation of the path, restated in oracle/ (the reference
+checkout is not on the GPU box), with all host threads; each step is the bounded sample named in `cpu_baseline.sample`.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CFG = dict(vocab=8192, d=768, layers=12, mlp_mult=4, ctx=512, mixer="aspin", norm="rms")
+B_PER_GPU, T_TOTAL, WINDOW = 16, 2048, 512
+CPU_SAMPLE_B, CPU_SAMPLE_T = 2, 2048
+WORKLOAD = "cfg1: aspin LM prefill d768 L12 H12x64 V8192, B=16 x T=2048 per GPU as four carried 512-token windows"
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the prefill kernel at the bench shape (B16 H12 T512 D64),
+# from the ncu capture summarised under profiles/; None until captured.
+NCU_TRAFFIC_BYTES = {"aspin_prefill": None}
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm_gbs=float(d["hbm_gbs"]), tflops=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), src="measured")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, src="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows = []; self.proc = None; self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) >= 9:
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+# ------------------------------------------------------------------------------------------------------------------
+def cpu_reference_time(steps: int, warmup: int):
+    """The CPU oracle's forward_carried on the bounded sample; returns (tok/s, seconds per step, threads)."""
+    import oracle
+    from pragnosia_b200 import synth
+    torch.set_num_threads(os.cpu_count() or 1)
+    cfg = oracle.lm_config(**CFG)
+    P = oracle.init_lm_params(cfg, seed=0)
+    ids = synth.token_ids(CPU_SAMPLE_B, CPU_SAMPLE_T, CFG["vocab"], seed=1)
+    times = []
+    with torch.no_grad():
+        for i in range(warmup + steps):
+            t0 = time.perf_counter()
+            oracle.lm_forward_carried(P, cfg, ids, WINDOW)
+            if i >= warmup:
+                times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    return CPU_SAMPLE_B * CPU_SAMPLE_T / sec, sec, torch.get_num_threads()
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    toks, sec, threads = cpu_reference_time(args.steps, args.warmup)
+    sample = (f"B={CPU_SAMPLE_B} x T={CPU_SAMPLE_T} of the same LM and window (the path is linear in B*T), fp32, "
+              f"torch CPU with {threads} threads")
+    print(json.dumps({
+        "impl": "reference", "metric": "aspin_lm_prefill_tokens_per_s", "value": toks, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": toks, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": toks, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ------------------------------------------------------------------------------------------------------------------
+def event_time_ms(fn, iters: int, flush=None):
+    """Average CUDA-event time of fn() over iters calls on the current stream, L2 flushed before each."""
+    tot = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fn(); b.record(); b.synchronize()
+        tot += a.elapsed_time(b)
+    return tot / iters
+
+
+def product_arm(args):
+    import torch.distributed as dist
+    from pragnosia_b200 import ops, synth
+    from pragnosia_b200.model import LM
+    from pragnosia_b200.generate import Decoder
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product arm has no CPU path (use --impl reference for the CPU timing)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    torch.manual_seed(0)
+    model = LM(**CFG).to(dev).to(torch.bfloat16).eval()
+    ids_host = synth.token_ids(B_PER_GPU, T_TOTAL, CFG["vocab"], seed=1 + rank).pin_memory()
+    ids = ids_host.to(dev)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flush = lambda: flush_buf.zero_()
+
+    def step():
+        return model.forward_carried(ids, WINDOW)
+
+    def step_e2e(out_host):
+        x = ids_host.to(dev, non_blocking=True)
+        lg = model.forward_carried(x, WINDOW)
+        out_host.copy_(lg, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 3)):
+            step()
+        sampler = ClockSampler(local); sampler.start()
+        barrier()
+        ms = []
+        for _ in range(args.steps):
+            flush()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); step(); b.record(); b.synchronize()
+            ms.append(a.elapsed_time(b))
+        barrier()
+        clocks = sampler.stop()
+        ms_step = sum(ms) / len(ms)
+        # end to end: host ids in, logits out, wall clock around the whole call (copies included)
+        out_host = torch.empty(B_PER_GPU, WINDOW, CFG["vocab"], dtype=torch.bfloat16).pin_memory()
+        for _ in range(2):
+            step_e2e(out_host)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step_e2e(out_host)
+        barrier()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    t = torch.tensor([ms_step, e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step, e2e_ms = t.tolist()
+    tokens = world * B_PER_GPU * T_TOTAL
+    result = {
+        "metric": "aspin_lm_prefill_tokens_per_s", "value": tokens / (ms_step * 1e-3), "unit": "tok/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "params_m": round(sum(p.numel() for p in model.parameters()) / 1e6, 2),
+                   "state": "fp32", "l2": "flushed between timed steps (256 MiB write); weights 184 MB > L2",
+                   "parallelism": f"batch-sharded x{world}, no data-path collective"},
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": ids_host.numel() * 8,
+                "d2h_bytes_per_step": out_host.numel() * 2},
+        "gpu_launches": args.steps * CFG["layers"] * (T_TOTAL // WINDOW) * 2,     # prep + prefill per layer-window
+        "clocks": clocks,
+    }
+    if rank == 0:
+        pk = peaks()
+        with torch.no_grad():
+            result["roofline"], result["kernels"] = kernel_rooflines(dev, pk, flush)
+            result["decode"] = decode_numbers(model, dev, pk, args)
+        if world == 1:
+            toks, sec, threads = cpu_reference_time(3, 1)
+            result["cpu_baseline"] = {"value": toks, "unit": "tok/s", "cores": threads, "kind": "port",
+                                      "sample": f"oracle forward_carried, B={CPU_SAMPLE_B} x T={CPU_SAMPLE_T}, fp32, "
+                                                f"{sec:.2f} s per pass, best-effort all {threads} threads"}
+        print(json.dumps(result))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def kernel_rooflines(dev, pk, flush):
+    """Each hand-written kernel alone at the workload's shape: algorithmic bytes / CUDA-event time against the measured
+    HBM copy bandwidth."""
+    from pragnosia_b200 import ops, synth
+    out = []
+    # chunked prefill at the configuration-1 window: B16 H12 T512 D64, bf16 I/O
+    B, H, T, D = B_PER_GPU, 12, WINDOW, 64
+    x = synth.assoc_op_inputs(B, H, T, D, seed=3, with_state=True)
+    q, k, v = (x[n].to(dev).to(torch.bfloat16) for n in "qkv")
+    la, S0 = x["la"].to(dev), x["S0"].to(dev)
+    fn = lambda: ops.prefill(q, k, v, la, None, S0)
+    for _ in range(3): fn()
+    ms = event_time_ms(fn, 20, flush)
+    alg = B * H * T * (4 * D * 2 + 4) + 2 * B * H * D * D * 4            # q,k,v,o bf16 + la, state in and out
+    roof = dict(bound="hbm", achieved=alg / ms / 1e6, peak=pk["hbm_gbs"], unit="GB/s", frac=alg / ms / 1e6 / pk["hbm_gbs"],
+                traffic=NCU_TRAFFIC_BYTES["aspin_prefill"], kernel="aspin_prefill (plain rule, B16 H12 T512 D64, bf16 I/O)",
+                us_per_launch=ms * 1e3, algorithmic_bytes=alg, peak_source=pk["src"])
+    out.append(dict(roof))
+    # fused prep at the same shape
+    proj = torch.randn(B, T, 3 * H * D + 2 * H, device=dev, dtype=torch.bfloat16)
+    d = H * D
+    views = [proj[..., i * d:(i + 1) * d].unflatten(-1, (H, D)) for i in range(3)]
+    th, pos = x["theta"].to(dev), x["pos"].to(dev)
+    fn = lambda: ops.prep(*views, proj[..., 3 * d + H:3 * d + 2 * H], th, pos)
+    for _ in range(3): fn()
+    ms = event_time_ms(fn, 20, flush)
+    alg = B * H * T * D * 2 * 6
+    out.append(dict(kernel="aspin_prep (B16 T512 H12 D64, bf16)", bound="hbm", achieved=alg / ms / 1e6, peak=pk["hbm_gbs"],
+                    unit="GB/s", frac=alg / ms / 1e6 / pk["hbm_gbs"], us_per_launch=ms * 1e3, algorithmic_bytes=alg))
+    # decode step at batch 64: state read + write
+    Bd = 64
+    S = torch.randn(Bd, H, D, D, device=dev) * 0.1
+    row = torch.randn(Bd, 3 * d + 2 * H, device=dev, dtype=torch.bfloat16)
+    vs = [row[:, i * d:(i + 1) * d].unflatten(1, (H, D)) for i in range(3)]
+    A = torch.zeros(H, device=dev) - 5
+    fn = lambda: ops.decode_step(*vs, row[:, 3 * d:3 * d + H], S, th, gate=row[:, 3 * d + H:], decay_A=A, shift=1.0, S_out=S)
+    for _ in range(3): fn()
+    ms = event_time_ms(fn, 50, flush)
+    alg = 2 * Bd * H * D * D * 4 + Bd * H * D * 2 * 4
+    out.append(dict(kernel="aspin_decode_step (B64 H12 D64, in place)", bound="hbm", achieved=alg / ms / 1e6, peak=pk["hbm_gbs"],
+                    unit="GB/s", frac=alg / ms / 1e6 / pk["hbm_gbs"], us_per_launch=ms * 1e3, algorithmic_bytes=alg))
+    # per-token lambda scan on a configuration-4 slice: B8 T4096 D768 fp32 (4 x 100 MB)
+    xs = synth.lambda_scan_inputs(8, 4096, 768, seed=4)
+    u, lm, an = (xs[n].to(dev) for n in ("u", "logmag", "ang"))
+    fn = lambda: ops.lambda_scan(u, lm, an)
+    for _ in range(3): fn()
+    ms = event_time_ms(fn, 10, flush)
+    alg = u.numel() * 16
+    out.append(dict(kernel="lambda_scan (B8 T4096 D768, per-token angle)", bound="hbm", achieved=alg / ms / 1e6,
+                    peak=pk["hbm_gbs"], unit="GB/s", frac=alg / ms / 1e6 / pk["hbm_gbs"], us_per_launch=ms * 1e3,
+                    algorithmic_bytes=alg))
+    return roof, out
+
+
+def decode_numbers(model, dev, pk, args):
+    """Configuration 2: 512-token prompt, then sampled steps (temperature 1, seeded) at batch 1 and 64."""
+    from pragnosia_b200 import synth
+    from pragnosia_b200.generate import Decoder
+    n = args.decode_steps
+    res = {"steps": n, "prompt": 512}
+    for B in (1, 64):
+        dec = Decoder(model, batch=B)
+        prompt = synth.token_ids(B, 512, CFG["vocab"], seed=7).to(dev)
+        dec.generate(prompt, 16, temp=1.0, seed=0)                      # captures the graph
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); dec.generate(prompt, n, temp=1.0, seed=0); b.record(); b.synchronize()
+        # the prompt pass is inside generate(); time it alone and subtract
+        c, d = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c.record(); dec.prefill(prompt); d.record(); d.synchronize()
+        ms_tok = (a.elapsed_time(b) - c.elapsed_time(d)) / n
+        state_bytes = 2 * B * CFG["layers"] * 12 * 64 * 64 * 4
+        res[f"b{B}_ms_per_token"] = ms_tok
+        res[f"b{B}_state_rw_gbs_over_whole_step"] = state_bytes / ms_tok / 1e6
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="product", choices=["product", "reference"])
+    ap.add_argument("--decode-steps", type=int, default=4096)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        product_arm(args)
+
+
+if __name__ == "__main__":
+    main()

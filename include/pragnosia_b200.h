@@ -1,0 +1,129 @@
+/*
+ * pragnosia_b200 -- C ABI of the B200 (sm_100a) carrier kernels.
+ *
+ * The reference (ladkabiharihai/pragnosia) has no C/FFI boundary of its own: its operator boundary is Python
+ * functions and torch custom ops that launch Triton kernels. Each entry point below is what a binding for one of
+ * those operators calls; the comment on each names the reference operator it stands in for (path:line inside the
+ * reference project).
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless its name ends in _host. The library never allocates, frees or
+ *     synchronises; outputs are caller-allocated; launches go to the given stream (a cudaStream_t passed as void*,
+ *     NULL = the legacy default stream), so every call can be captured in a CUDA graph.
+ *   - Every function returns a pgb_status (0 = OK). Argument checks happen on the host before anything is
+ *     launched, so a bad call never touches the GPU. pgb_status_string() names a code.
+ *   - Tensors are row-major and contiguous unless a stride argument says otherwise; strides are in ELEMENTS.
+ *   - dtype codes: PGB_F32 = 0, PGB_BF16 = 1. The recurrent state is always fp32, laid out [B][H][dk][dv]
+ *     (key axis first), bit-compatible with the reference's carried state (src/assoc.py:512).
+ */
+#ifndef PRAGNOSIA_B200_H
+#define PRAGNOSIA_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    PGB_OK = 0,
+    PGB_ERR_NULL_POINTER = 1,      /* a required pointer is NULL                                   */
+    PGB_ERR_BAD_SHAPE = 2,         /* a size is zero/negative or inconsistent                      */
+    PGB_ERR_UNSUPPORTED_DIM = 3,   /* head dimension / chunk the kernels are not built for         */
+    PGB_ERR_MISALIGNED = 4,        /* a pointer or stride breaks the kernel's alignment rule       */
+    PGB_ERR_BAD_DTYPE = 5,         /* unknown dtype code                                           */
+    PGB_ERR_CUDA = 6,              /* the launch itself failed; see pgb_last_cuda_error()          */
+    PGB_ERR_TOO_LARGE = 7          /* a size exceeds a documented maximum                          */
+} pgb_status;
+
+enum { PGB_F32 = 0, PGB_BF16 = 1 };
+
+/* precision of the chunked prefill: AUTO = tensor cores for bf16 I/O, fp32 FFMA for fp32 I/O */
+enum { PGB_PREFILL_AUTO = 0, PGB_PREFILL_FP32 = 1, PGB_PREFILL_TENSOR = 2 };
+
+const char *pgb_status_string(int status);
+const char *pgb_last_cuda_error(void);     /* text of the last CUDA error seen by this library (thread-local) */
+int pgb_abi_version(void);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Per-token complex recurrence  h_t = lambda_t h_{t-1} + u_t,  lambda_t = exp(logmag_t + i ang_t).
+ * Replaces src/scan_kernel.py:144-148 scan_triton (kernel _fwd :25-50); CPU definition src/spin.py:182-215.
+ *   u, logmag [B][T][D] fp32.  ang: fp32 with element strides (ang_stride_b, ang_stride_t) and unit stride
+ *   over D; strides (0,0) mean one angle per channel (the fspin layer's broadcast, src/spin.py:244).
+ *   h0r, h0i [B][D] fp32 or both NULL (zero state).
+ *   y [B][T][D] fp32 = Re h_t.  hr_out, hi_out [B][D] fp32 = final state.
+ * ------------------------------------------------------------------------------------------------------- */
+int pgb_lambda_scan_fwd(const float *u, const float *logmag, const float *ang, long long ang_stride_b,
+                        long long ang_stride_t, const float *h0r, const float *h0i, float *y, float *hr_out,
+                        float *hi_out, int B, int T, int D, void *stream);
+/* Same, with the number of time segments a warp scans in parallel fixed by the caller (a power of two in 1..32;
+ * 0 = choose from the shape). 1 is the literal sequential recurrence; used for tuning and by the parity tests. */
+int pgb_lambda_scan_fwd_ex(const float *u, const float *logmag, const float *ang, long long ang_stride_b,
+                           long long ang_stride_t, const float *h0r, const float *h0i, float *y, float *hr_out,
+                           float *hi_out, int B, int T, int D, int time_segments, void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Fused plumbing before the scan: L2-normalise q, k, v per head, scale k by sigmoid(gate), rotate q and k by
+ * pos[t] * theta[h][i] per channel pair, cast, and transpose (B,T,H,D) -> (B,H,T,D).
+ * Replaces src/assoc_kernel.py:888-891 prep_kernel (op membrae::assoc_prep :828, kernel _prep_fwd :742-769).
+ *   qp, kp, vp: in_dtype, logical shape (B,T,H,D), element strides (in_stride_b, in_stride_t, in_stride_h),
+ *   unit stride over D (views into one fused projection are fine).
+ *   gate: logits (B,T,H), same in_dtype, element strides (gate_stride_b, gate_stride_t), unit over H; NULL = none.
+ *   theta [H][D/2] fp32.  pos [T] int64.   q, k, v out: out_dtype, contiguous (B,H,T,D).   D in {64,128}.
+ * ------------------------------------------------------------------------------------------------------- */
+int pgb_aspin_prep_fwd(const void *qp, const void *kp, const void *vp, int in_dtype, long long in_stride_b,
+                       long long in_stride_t, long long in_stride_h, const void *gate, long long gate_stride_b,
+                       long long gate_stride_t, const float *theta, const long long *pos, void *q, void *k,
+                       void *v, int out_dtype, int B, int T, int H, int D, void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Chunked prefill of the associative carrier, plain rule (beta == NULL) or delta rule, one fused pass:
+ *   o_t = sum_{s<=t} exp(L_t-L_s) (q_t.k_s) w_s + exp(L_t) q_t S_entering ;  S carried chunk to chunk in fp32.
+ * Replaces src/assoc_kernel.py:302-323 assoc_scan_kernel (ops prefix_scan :231, assoc_out :128) and :512-546
+ * delta_scan_kernel (ops delta_inv :658, delta_loop_fwd :363, assoc_out); CPU definition src/assoc.py:254-269.
+ *   q, k, v [B][H][T][D] io_dtype (already normalised / gated / rotated).  la [B][H][T] fp32 log-decay <= 0.
+ *   beta [B][H][T] fp32 or NULL.  S0 [B][H][D][D] fp32 or NULL (zero).
+ *   theta [H][D/2] fp32 or NULL.  With theta given, S0's key axis is first rotated back by shift positions (the
+ *   rebase of src/assoc.py:399-402); shift = *shift_dev if shift_dev != NULL else shift_host.
+ *   o [B][H][T][D] o_dtype (fp32 output with bf16 inputs is allowed).  S_out [B][H][D][D] fp32.
+ *   sent: optional [B][H][ceil(T/64)][D][D] bf16, the state ENTERING every 64-token chunk (NULL = not wanted).
+ *   D in {64,128}.  precision: PGB_PREFILL_*.
+ * ------------------------------------------------------------------------------------------------------- */
+int pgb_aspin_prefill_fwd(const void *q, const void *k, const void *v, int io_dtype, const float *la,
+                          const float *beta, const float *S0, const float *theta, const float *shift_dev,
+                          float shift_host, void *o, int o_dtype, float *S_out, void *sent, int B, int H, int T,
+                          int D, int precision, void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Rotation of channel pairs (2i, 2i+1) of x (B,H,T,D) by pos[t] * theta[h][i]; any even D.
+ * Replaces src/assoc.py:34-39 rotate.   x, out: dtype, contiguous.  theta [H][D/2] fp32.  pos [T] fp32.
+ * ------------------------------------------------------------------------------------------------------- */
+int pgb_rotate_pairs(const void *x, int dtype, const float *theta, const float *pos, void *out, int B, int H, int T,
+                     int D, void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * One recurrent decode step per (sequence, head), fully fused: normalise q,k,v; write gate or beta; rebase
+ * rotation of the state's key axis by -shift*theta; decay; rank-1 write (plain or delta); read; optional per-head
+ * RMS norm of the read.  Replaces the T=1 PyTorch path of src/assoc.py:384-512 (about 80 launches per layer in
+ * the reference's graphed step, src/bench.py:281-288).
+ *   qp, kp, vp: in_dtype, (B,H,D) with batch stride in_stride_b (elements), unit stride over (H,D).
+ *   normalize != 0: L2-normalise q, k, v first (eps 1e-12 on the norm).
+ *   gate (B,H) in_dtype, batch stride gate_stride_b, or NULL.  Plain rule: k *= sigmoid(gate).  Delta rule
+ *   (delta != 0): beta = sigmoid(gate) if gate_is_logit else gate.
+ *   decay (B,H) in_dtype, batch stride decay_stride_b.  decay_A == NULL: decay holds log alpha.  Otherwise
+ *   log alpha = -softplus(decay) * exp(decay_A[h])  (src/assoc.py:355-356), decay_A [H] fp32.
+ *   theta [H][D/2] fp32.  shift_dev: device fp32 scalar (may be NULL: then shift_host is used) = number of
+ *   positions the carried state is rotated back by (the previous call's length).
+ *   S_in, S_out [B][H][D][D] fp32; may be the same buffer (in-place).
+ *   rms_weight [D] fp32 or NULL; rms_eps used only with rms_weight.
+ *   o: out_dtype, (B,H,D) with batch stride out_stride_b.
+ * ------------------------------------------------------------------------------------------------------- */
+int pgb_aspin_decode_step(const void *qp, const void *kp, const void *vp, int in_dtype, long long in_stride_b,
+                          int normalize, const void *gate, long long gate_stride_b, int gate_is_logit, int delta,
+                          const void *decay, long long decay_stride_b, const float *decay_A, const float *theta,
+                          const float *shift_dev, float shift_host, const float *S_in, float *S_out,
+                          const float *rms_weight, float rms_eps, void *o, int out_dtype, long long out_stride_b,
+                          int B, int H, int D, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PRAGNOSIA_B200_H */

@@ -1,0 +1,133 @@
+"""The associative carrier layer on the sm_100a kernels: same module API and parameter names as the reference's
+src/assoc.py (AssocCarrier :279-512, rotate :34, assoc_scan :254), so reference checkpoints load unchanged.
+
+In scope: the plain and delta rules, head dims 64 and 128, carried state across windows, the T=1 decode step.
+The reference's optional extras (short convolution, key_topk, hl_floor, write_all, pos_wrap, beta_scale) belong to its
+hybrid / experimental mixers and raise NotImplementedError here.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import ops
+
+
+def rotate(x, theta, pos):
+    """RoPE-style rotation of channel pairs by theta_i * pos. x (B,H,T,dk); theta (H,dk/2); pos (T,)."""
+    return ops.rotate(x, theta, pos)
+
+
+def assoc_scan(q, k, v, logalpha, S0=None, chunk: int = 64, recompute: bool = False, mm=None, beta=None, kernel=False):
+    """Chunked scan, (o, final state); plain rule or, with beta, the delta rule. The result does not depend on `chunk`;
+    recompute / mm / kernel are accepted for signature compatibility and ignored."""
+    o, S, _ = ops.prefill(q, k, v, logalpha, beta, S0)
+    return o, S
+
+
+class AssocCarrier(nn.Module):
+    def __init__(self, d: int, heads: int | None = None, chunk: int = 64, recompute: bool = False, delta: bool = False,
+                 head_dim: int | None = None, kernel: bool = True, key_topk: int = 0, hl_floor: bool = False,
+                 write_all: bool = False):
+        super().__init__()
+        if key_topk or hl_floor or write_all:
+            raise NotImplementedError("key_topk / hl_floor / write_all are outside the carrier hot path built here")
+        self.d, self.delta, self.chunk, self.kernel = d, delta, chunk, kernel
+        self.h = heads or max(1, d // (head_dim or 64))
+        assert d % self.h == 0 and (d // self.h) % 2 == 0
+        self.dk = d // self.h
+        if self.dk not in (64, 128):
+            raise NotImplementedError(f"head dim {self.dk}: the kernels are built for 64 and 128")
+        self.need_sent = False          # True: keep the state entering every 64-token chunk in self.sent (bf16)
+        self.inplace_state = False      # True: a T=1 step overwrites the state tensor it was given (graphed decode)
+        self.ln = nn.LayerNorm(d)
+        self.q = nn.Linear(d, d, bias=False); self.k = nn.Linear(d, d, bias=False)
+        self.v = nn.Linear(d, d, bias=False); self.o = nn.Linear(d, d, bias=False)
+        self.wa = nn.Linear(d, self.h)
+        self.wi = nn.Linear(d, self.h)
+        if delta:
+            self.wb = nn.Linear(d, self.h)
+        self.A = nn.Parameter(torch.linspace(math.log(0.1 / 0.69), math.log(1e-4 / 0.69), self.h))
+        base = 10000.0 ** (-torch.arange(0, self.dk, 2).float() / self.dk)
+        self.theta = nn.Parameter(base.unsqueeze(0).repeat(self.h, 1))
+        self.on = nn.RMSNorm(self.dk)
+        self.gate = nn.Parameter(torch.zeros(()))
+        self.sent = None
+        self._fused = None
+
+    def spectral_parameters(self):
+        return [self.A, self.theta, self.gate]
+
+    def logalpha(self, z):
+        return -F.softplus(self.wa(z)) * torch.exp(self.A)
+
+    # One GEMM for q, k, v, the decay gate and the write gate / write strength: z is read once. Rows: [q | k | v | wa | wg],
+    # padded to a multiple of 8 so every view into the product stays 16-byte aligned. Cached with the gated output
+    # weight and fp32 copies of the small per-head constants; rebuilt when a parameter changes.
+    def _consts(self):
+        gatew = self.wb if self.delta else self.wi
+        ps = (self.q.weight, self.k.weight, self.v.weight, self.wa.weight, self.wa.bias, gatew.weight, gatew.bias,
+              self.o.weight, self.gate, self.theta, self.A, self.on.weight)
+        key = tuple((p.data_ptr(), p._version, p.dtype) for p in ps)
+        if self._fused is None or self._fused[0] != key:
+            with torch.no_grad():
+                W = torch.cat([self.q.weight, self.k.weight, self.v.weight, self.wa.weight, gatew.weight])
+                b = torch.cat([torch.zeros(3 * self.d, device=W.device, dtype=W.dtype), self.wa.bias, gatew.bias])
+                pad = (-W.shape[0]) % 8
+                if pad:
+                    W = torch.cat([W, W.new_zeros(pad, W.shape[1])]); b = torch.cat([b, b.new_zeros(pad)])
+                c = dict(W=W.contiguous(), b=b.contiguous(), ow=(self.o.weight * torch.sigmoid(self.gate)).contiguous(),
+                         theta=self.theta.detach().float().contiguous(), A=self.A.detach().float().contiguous(),
+                         expA=torch.exp(self.A.detach().float()), onw=self.on.weight.detach().float().contiguous())
+            self._fused = (key, c)
+        return self._fused[1]
+
+    def forward(self, x, h0=None, pos0: int = 0):
+        """x (B,T,d) on CUDA; h0 = (S (B,H,dk,dk) fp32, p0) from the previous window or step, or None.
+        Returns (out (B,T,d), (S, T)): positions restart at every call and the carried state is rotated back by the
+        previous call's length instead (the reference's rebase, src/assoc.py:394-405)."""
+        B, T, D = x.shape
+        H, dk = self.h, self.dk
+        S0, p0 = (None, 0) if h0 is None else (h0[0], h0[1])
+        if h0 is not None and len(h0) == 3:
+            raise NotImplementedError("short-convolution state is outside the carrier hot path built here")
+        c = self._consts()
+        z = self.ln(x)
+        y = F.linear(z, c["W"], c["b"])                               # (B,T,3d+2h[+pad])
+        d = self.d
+        zero_shift = (not torch.is_tensor(p0)) and p0 == 0
+        if T == 1:
+            y2 = y.view(B, -1)
+            if S0 is None:
+                S0 = torch.zeros(B, H, dk, dk, device=x.device, dtype=torch.float32)
+            o = torch.empty(B, 1, d, device=x.device, dtype=x.dtype)
+            _, S = ops.decode_step(
+                y2[:, 0:d].unflatten(1, (H, dk)), y2[:, d:2 * d].unflatten(1, (H, dk)), y2[:, 2 * d:3 * d].unflatten(1, (H, dk)),
+                y2[:, 3 * d:3 * d + H], S0, c["theta"], gate=y2[:, 3 * d + H:3 * d + 2 * H], delta=self.delta,
+                gate_is_logit=True, decay_A=c["A"], normalize=True, shift=0.0 if zero_shift else p0,
+                rms_weight=c["onw"], rms_eps=self._rms_eps(x.dtype), out=o.view(B, H, dk),
+                S_out=S0 if self.inplace_state else None)
+            self.sent = None
+        else:
+            qp, kp, vp = (y[..., i * d:(i + 1) * d].unflatten(-1, (H, dk)) for i in range(3))
+            la = (-F.softplus(y[..., 3 * d:3 * d + H].float()) * c["expA"]).transpose(1, 2).contiguous()
+            g = y[..., 3 * d + H:3 * d + 2 * H]
+            beta = torch.sigmoid(g.float()).transpose(1, 2).contiguous() if self.delta else None
+            pos = torch.arange(T, device=x.device)
+            q, k, v = ops.prep(qp, kp, vp, None if self.delta else g, c["theta"], pos,
+                               out_dtype=torch.bfloat16 if x.dtype == torch.bfloat16 else torch.float32)
+            o, S, sent = ops.prefill(q, k, v, la, beta, S0, theta=c["theta"], shift=0.0 if zero_shift else p0,
+                                     want_sent=self.need_sent)
+            self.sent = sent
+            o = self.on(o.to(x.dtype)).transpose(1, 2).reshape(B, T, D)
+        out = x + F.linear(o, c["ow"])
+        if torch.is_tensor(p0):
+            # a device-side position (graphed decode): with inplace_state the caller owns and updates it
+            return out, (S, p0 if self.inplace_state else p0 * 0 + T)
+        return out, (S, T)
+
+    def _rms_eps(self, dtype):
+        return self.on.eps if self.on.eps is not None else torch.finfo(dtype).eps

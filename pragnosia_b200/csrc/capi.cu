@@ -1,0 +1,138 @@
+// The C ABI: argument checks on the host, then one launch. Declarations and contracts: include/pragnosia_b200.h.
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace pgb {
+
+static thread_local char g_err[256] = "";
+
+void set_cuda_error(cudaError_t e, const char *where) {
+    snprintf(g_err, sizeof(g_err), "%s: %s (%s)", where, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+
+int lambda_scan_launch(const float *, const float *, const float *, long long, long long, const float *, const float *,
+                       float *, float *, float *, int, int, int, int, cudaStream_t);
+int prep_launch(const void *, const void *, const void *, int, long long, long long, long long, const void *, long long,
+                long long, const float *, const long long *, void *, void *, void *, int, int, int, int, int, cudaStream_t);
+int prefill_fp32_launch(const PrefillArgs &, int, int, int, cudaStream_t);
+int prefill_tc_launch(const PrefillArgs &, int, int, cudaStream_t);
+bool prefill_tc_supported(int io_dtype, int D, bool delta);
+int decode_launch(const DecodeArgs &, int, int, int, int, cudaStream_t);
+int rotate_launch(const void *, int, const float *, const float *, void *, int, int, int, int, cudaStream_t);
+
+static inline size_t esize(int dt) { return dt == PGB_BF16 ? 2 : 4; }
+static inline bool dtype_ok(int dt) { return dt == PGB_F32 || dt == PGB_BF16; }
+
+}  // namespace pgb
+
+using namespace pgb;
+
+extern "C" {
+
+const char *pgb_status_string(int s) {
+    switch (s) {
+        case PGB_OK: return "ok";
+        case PGB_ERR_NULL_POINTER: return "a required pointer is NULL";
+        case PGB_ERR_BAD_SHAPE: return "bad or inconsistent shape";
+        case PGB_ERR_UNSUPPORTED_DIM: return "unsupported head dimension or chunk (D must be 64 or 128)";
+        case PGB_ERR_MISALIGNED: return "pointer or stride breaks the alignment rule";
+        case PGB_ERR_BAD_DTYPE: return "unknown dtype code";
+        case PGB_ERR_CUDA: return "CUDA launch failed";
+        case PGB_ERR_TOO_LARGE: return "size exceeds the documented maximum";
+        default: return "unknown status";
+    }
+}
+
+const char *pgb_last_cuda_error(void) { return g_err; }
+
+int pgb_abi_version(void) { return 1; }
+
+int pgb_lambda_scan_fwd_ex(const float *u, const float *logmag, const float *ang, long long ang_stride_b,
+                           long long ang_stride_t, const float *h0r, const float *h0i, float *y, float *hr_out,
+                           float *hi_out, int B, int T, int D, int time_segments, void *stream) {
+    if (!u || !logmag || !ang || !y || !hr_out || !hi_out) return PGB_ERR_NULL_POINTER;
+    if ((h0r == nullptr) != (h0i == nullptr)) return PGB_ERR_NULL_POINTER;
+    if (B <= 0 || T <= 0 || D <= 0 || ang_stride_b < 0 || ang_stride_t < 0) return PGB_ERR_BAD_SHAPE;
+    if (time_segments != 0 && (time_segments < 1 || time_segments > 32 || (time_segments & (time_segments - 1))))
+        return PGB_ERR_BAD_SHAPE;
+    if (!aligned(u, 4) || !aligned(logmag, 4) || !aligned(ang, 4) || !aligned(y, 4)) return PGB_ERR_MISALIGNED;
+    return lambda_scan_launch(u, logmag, ang, ang_stride_b, ang_stride_t, h0r, h0i, y, hr_out, hi_out, B, T, D,
+                              time_segments, (cudaStream_t)stream);
+}
+
+int pgb_lambda_scan_fwd(const float *u, const float *logmag, const float *ang, long long ang_stride_b,
+                        long long ang_stride_t, const float *h0r, const float *h0i, float *y, float *hr_out,
+                        float *hi_out, int B, int T, int D, void *stream) {
+    return pgb_lambda_scan_fwd_ex(u, logmag, ang, ang_stride_b, ang_stride_t, h0r, h0i, y, hr_out, hi_out, B, T, D, 0,
+                                  stream);
+}
+
+int pgb_aspin_prep_fwd(const void *qp, const void *kp, const void *vp, int in_dtype, long long in_stride_b,
+                       long long in_stride_t, long long in_stride_h, const void *gate, long long gate_stride_b,
+                       long long gate_stride_t, const float *theta, const long long *pos, void *q, void *k, void *v,
+                       int out_dtype, int B, int T, int H, int D, void *stream) {
+    if (!qp || !kp || !vp || !theta || !pos || !q || !k || !v) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(in_dtype) || !dtype_ok(out_dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || T <= 0 || H <= 0) return PGB_ERR_BAD_SHAPE;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    const int per = D / 32;                                           // channels a lane moves in one access
+    const size_t ia = per * esize(in_dtype), oa = per * esize(out_dtype);
+    if (!aligned(qp, ia) || !aligned(kp, ia) || !aligned(vp, ia) || !aligned(q, oa) || !aligned(k, oa) || !aligned(v, oa))
+        return PGB_ERR_MISALIGNED;
+    if (in_stride_b % per || in_stride_t % per || in_stride_h % per) return PGB_ERR_MISALIGNED;
+    return prep_launch(qp, kp, vp, in_dtype, in_stride_b, in_stride_t, in_stride_h, gate, gate_stride_b, gate_stride_t,
+                       theta, pos, q, k, v, out_dtype, B, T, H, D, (cudaStream_t)stream);
+}
+
+int pgb_aspin_prefill_fwd(const void *q, const void *k, const void *v, int io_dtype, const float *la, const float *beta,
+                          const float *S0, const float *theta, const float *shift_dev, float shift_host, void *o,
+                          int o_dtype, float *S_out, void *sent, int B, int H, int T, int D, int precision, void *stream) {
+    if (!q || !k || !v || !la || !o || !S_out) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(io_dtype) || !dtype_ok(o_dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || H <= 0 || T <= 0 || (long long)B * H > 0x7fffffffLL) return PGB_ERR_BAD_SHAPE;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    if (precision < PGB_PREFILL_AUTO || precision > PGB_PREFILL_TENSOR) return PGB_ERR_BAD_SHAPE;
+    if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(o, 16) || !aligned(S_out, 16) ||
+        (S0 && !aligned(S0, 16)) || (sent && !aligned(sent, 16)))
+        return PGB_ERR_MISALIGNED;
+    PrefillArgs a{q, k, v, la, beta, S0, o, S_out, (__nv_bfloat16 *)sent, theta, shift_dev, shift_host, B, H, T};
+    const bool tc_ok = prefill_tc_supported(io_dtype, D, beta != nullptr);
+    if (precision == PGB_PREFILL_TENSOR && !tc_ok) return PGB_ERR_UNSUPPORTED_DIM;
+    if (precision == PGB_PREFILL_TENSOR || (precision == PGB_PREFILL_AUTO && tc_ok))
+        return prefill_tc_launch(a, o_dtype, D, (cudaStream_t)stream);
+    return prefill_fp32_launch(a, io_dtype, o_dtype, D, (cudaStream_t)stream);
+}
+
+int pgb_rotate_pairs(const void *x, int dtype, const float *theta, const float *pos, void *out, int B, int H, int T, int D,
+                     void *stream) {
+    if (!x || !theta || !pos || !out) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || H <= 0 || T <= 0 || D <= 0 || (D & 1)) return PGB_ERR_BAD_SHAPE;
+    if (!aligned(x, 2 * esize(dtype)) || !aligned(out, 2 * esize(dtype))) return PGB_ERR_MISALIGNED;
+    return rotate_launch(x, dtype, theta, pos, out, B, H, T, D, (cudaStream_t)stream);
+}
+
+int pgb_aspin_decode_step(const void *qp, const void *kp, const void *vp, int in_dtype, long long in_stride_b,
+                          int normalize, const void *gate, long long gate_stride_b, int gate_is_logit, int delta,
+                          const void *decay, long long decay_stride_b, const float *decay_A, const float *theta,
+                          const float *shift_dev, float shift_host, const float *S_in, float *S_out,
+                          const float *rms_weight, float rms_eps, void *o, int out_dtype, long long out_stride_b, int B,
+                          int H, int D, void *stream) {
+    if (!qp || !kp || !vp || !decay || !theta || !S_in || !S_out || !o) return PGB_ERR_NULL_POINTER;
+    if (delta && !gate) return PGB_ERR_NULL_POINTER;                  // the delta rule needs its beta
+    if (!dtype_ok(in_dtype) || !dtype_ok(out_dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || H <= 0 || (long long)B * H > 0x7fffffffLL) return PGB_ERR_BAD_SHAPE;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    if (in_stride_b < (long long)H * D || out_stride_b < (long long)H * D || gate_stride_b < 0 || decay_stride_b < 0)
+        return PGB_ERR_BAD_SHAPE;
+    if (!aligned(S_in, 16) || !aligned(S_out, 16) || !aligned(qp, esize(in_dtype)) || !aligned(o, esize(out_dtype)))
+        return PGB_ERR_MISALIGNED;
+    DecodeArgs a{qp, kp, vp, in_stride_b, normalize, gate, gate_stride_b, gate_is_logit, decay, decay_stride_b, decay_A,
+                 theta, shift_dev, shift_host, S_in, S_out, rms_weight, rms_eps, o, out_stride_b, B, H};
+    return decode_launch(a, in_dtype, out_dtype, D, delta, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,56 @@
+// Shared helpers for the carrier kernels (sm_100a).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/pragnosia_b200.h"
+
+namespace pgb {
+
+// thread-local text of the last CUDA error this library saw
+void set_cuda_error(cudaError_t e, const char *where);
+
+inline int check_launch(const char *where) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_cuda_error(e, where);
+        return PGB_ERR_CUDA;
+    }
+    return PGB_OK;
+}
+
+inline bool aligned(const void *p, size_t n) { return (reinterpret_cast<uintptr_t>(p) % n) == 0; }
+
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ void from_f32(float &d, float x) { d = x; }
+__device__ __forceinline__ void from_f32(__nv_bfloat16 &d, float x) { d = __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// softplus with torch's threshold (x > 20 -> x)
+__device__ __forceinline__ float softplusf_(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+
+// launch arguments shared between the C ABI layer and the kernels' translation units
+struct PrefillArgs {
+    const void *q, *k, *v; const float *la, *beta, *S0; void *o; float *S_out; __nv_bfloat16 *sent;
+    const float *theta; const float *shift_dev; float shift_host;      // rebase of S0's key axis (theta NULL: none)
+    int B, H, T;
+};
+struct DecodeArgs {
+    const void *qp, *kp, *vp; long long in_sb; int normalize;
+    const void *gate; long long gate_sb; int gate_is_logit;
+    const void *decay; long long decay_sb; const float *decay_A;
+    const float *theta; const float *shift_dev; float shift_host;
+    const float *S_in; float *S_out; const float *rms_w; float rms_eps;
+    void *o; long long out_sb; int B, H;
+};
+
+}  // namespace pgb

@@ -1,0 +1,114 @@
+"""Windowed prefill and CUDA-graphed recurrent decode for a batch of sequences.
+
+The reference's driver (src/bench.py Ours.generate :193-239 and _generate_graphed :242-317) decodes one sequence and
+syncs with the host for every sampled token. Here the loop is batch-generic, each layer's T=1 step is one fused kernel
+that updates its state in place, the whole step is one CUDA graph, and sampling stays on the device (no per-token
+host round trip; tokens are read back once at the end).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from .assoc import AssocCarrier
+
+
+class Decoder:
+    def __init__(self, model, batch: int, use_graph: bool = True):
+        self.m = model.eval()
+        self.B = batch
+        self.use_graph = use_graph
+        self.dev = next(model.parameters()).device
+        self.w = model.ctx
+        self.states = None
+        self._graph = None
+        self.tok = torch.zeros(batch, 1, dtype=torch.long, device=self.dev)
+        self.pos = torch.zeros(1, dtype=torch.long, device=self.dev)
+        self.shift = torch.zeros((), dtype=torch.float32, device=self.dev)    # positions the states are rotated back by
+        self.logits = None
+
+    # ---- prompt
+    @torch.no_grad()
+    def prefill(self, ids: torch.Tensor):
+        """ids (B,Tp): consume the prompt window by window; returns the logits after its last token (B,V)."""
+        m, w = self.m, self.w
+        states = [None] * m.layers
+        h = None; n = 0
+        for s in range(0, ids.shape[1], w):
+            xw = ids[:, s:s + w]; n = xw.shape[1]
+            h = m._layers(m._embed(xw), states)
+        pw = n % w
+        new = []
+        for st in states:                                   # own, contiguous copies the graph can update in place
+            new.append(tuple(t.clone().contiguous() if torch.is_tensor(t) else t for t in st))
+        if self.states is None:
+            self.states = new
+        else:
+            for old, cur in zip(self.states, new):
+                for a, b in zip(old, cur):
+                    if torch.is_tensor(a): a.copy_(b)
+        self.pos.fill_(pw)
+        self.shift.fill_(float(n))                           # the last window's length (src/assoc.py:512 returns p0 + T)
+        return F.linear(m.n(h[:, -1:]), m.e.weight)[:, -1].float()
+
+    # ---- one token
+    def _step(self):
+        m = self.m
+        h = m.e(self.tok) + m.p(self.pos)
+        for i, (mx, mp) in enumerate(zip(m.mix, m.mlp)):
+            st = self.states[i]
+            if isinstance(mx, AssocCarrier):
+                mx.inplace_state = True
+                h, _ = mx(h, (st[0], self.shift))
+                mx.inplace_state = False
+            else:
+                h, new = mx(h, st)
+                for a, b in zip(st, new): a.copy_(b)
+            h = mp(h)
+        self.shift.fill_(1.0)
+        self.pos.copy_((self.pos + 1) % self.w)
+        return F.linear(m.n(h), m.e.weight)[:, -1].float()
+
+    @torch.no_grad()
+    def step(self, tok: torch.Tensor):
+        """tok (B,) ids -> logits (B,V). The first call captures the graph."""
+        self.tok.copy_(tok.reshape(self.B, 1))
+        if not self.use_graph:
+            return self._step()
+        if self._graph is None:
+            saved = [tuple(t.clone() if torch.is_tensor(t) else t for t in st) for st in self.states]
+            pos, shift = self.pos.clone(), self.shift.clone()
+            s = torch.cuda.Stream(); s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                for _ in range(2): self._step()
+            torch.cuda.current_stream().wait_stream(s)
+            self._graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self._graph):
+                self.logits = self._step()
+            for st, sv in zip(self.states, saved):           # warm-up and capture advanced the state: restore it
+                for a, b in zip(st, sv):
+                    if torch.is_tensor(a): a.copy_(b)
+            self.pos.copy_(pos); self.shift.copy_(shift)
+        self._graph.replay()
+        return self.logits
+
+    @staticmethod
+    def sample(lg: torch.Tensor, temp: float, g: Optional[torch.Generator]):
+        """Greedy at temp 0, else one draw from softmax(lg / temp) per row (src/bench.py:79-86 without min-p); on device."""
+        if temp == 0:
+            return lg.argmax(-1)
+        return torch.multinomial(torch.softmax(lg.float() / temp, -1), 1, generator=g).squeeze(-1)
+
+    @torch.no_grad()
+    def generate(self, prompt_ids: torch.Tensor, n: int, temp: float = 0.0, seed: int = 0):
+        """prompt_ids (B,Tp) -> sampled ids (B,n)."""
+        g = torch.Generator(device=self.dev).manual_seed(seed)
+        lg = self.prefill(prompt_ids)
+        out = torch.empty(self.B, n, dtype=torch.long, device=self.dev)
+        for i in range(n):
+            nxt = self.sample(lg, temp, g)
+            out[:, i] = nxt
+            lg = self.step(nxt)
+        return out

@@ -1,0 +1,163 @@
+"""Tensor-level wrappers of the C ABI: shape checks, output allocation (by torch), one library call each.
+
+All functions take CUDA tensors, launch on torch's current stream and never synchronise, so they can be captured in a
+CUDA graph. They raise on CPU tensors: there is no fallback path.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import check, dtype_code, lib, need_cuda, ptr, stream_of
+
+CHUNK = 64
+
+
+def _f32c(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    return None if t is None else t.to(torch.float32).contiguous()
+
+
+# ----------------------------------------------------------------------------------------------------------
+def lambda_scan(u: torch.Tensor, logmag: torch.Tensor, ang: torch.Tensor, h0=None, time_segments: int = 0):
+    """h_t = lambda_t h_{t-1} + u_t with lambda_t = exp(logmag_t + i ang_t); returns (Re h (B,T,D) fp32,
+    (Re h_T, Im h_T)).  `ang` may be an expanded view with zero batch/time strides (one angle per channel): it is
+    read as such, not materialised."""
+    need_cuda(u, logmag, ang)
+    B, T, D = u.shape
+    u32, lm32 = _f32c(u), _f32c(logmag)
+    a32 = ang if ang.dtype == torch.float32 else ang.to(torch.float32)
+    if a32.dim() == 1:
+        a32 = a32.expand(B, T, D)
+    if tuple(a32.shape) != (B, T, D) or tuple(lm32.shape) != (B, T, D):
+        raise ValueError("lambda_scan: u, logmag, ang must share the shape (B,T,D)")
+    if D > 1 and a32.stride(2) != 1:
+        a32 = a32.contiguous()
+    sb, st = (a32.stride(0) if B > 1 else 0), (a32.stride(1) if T > 1 else 0)
+    if not (sb == 0 and st == 0) and not (st == D and sb == T * D):
+        a32 = a32.contiguous(); sb, st = T * D, D
+    h0r = h0i = None
+    if h0 is not None:
+        h0r, h0i = _f32c(h0[0]), _f32c(h0[1])
+        need_cuda(h0r, h0i)
+    y = torch.empty(B, T, D, device=u.device, dtype=torch.float32)
+    hr = torch.empty(B, D, device=u.device, dtype=torch.float32)
+    hi = torch.empty_like(hr)
+    check(lib().pgb_lambda_scan_fwd_ex(ptr(u32), ptr(lm32), ptr(a32), sb, st, ptr(h0r), ptr(h0i), ptr(y), ptr(hr), ptr(hi),
+                                       B, T, D, time_segments, stream_of(u)), "pgb_lambda_scan_fwd")
+    return y, (hr, hi)
+
+
+# ----------------------------------------------------------------------------------------------------------
+def prep(qp, kp, vp, gate_logits, theta, pos, out_dtype=torch.bfloat16):
+    """Normalise / gate / rotate / cast / transpose: (B,T,H,D) projections -> (B,H,T,D) scan operands."""
+    need_cuda(qp, kp, vp, theta, pos)
+    B, T, H, D = qp.shape
+    if kp.shape != qp.shape or vp.shape != qp.shape:
+        raise ValueError("prep: qp, kp, vp must share the shape (B,T,H,D)")
+    if qp.dtype not in (torch.float32, torch.bfloat16):
+        qp, kp, vp = qp.float(), kp.float(), vp.float()
+    kp, vp = kp.to(qp.dtype), vp.to(qp.dtype)
+
+    def strided(t):
+        per = D // 32                                   # channels a lane moves in one access: strides must keep it aligned
+        ok = t.stride(3) == 1 and all(s % per == 0 for s in t.stride()[:3])
+        return t if ok else t.contiguous()
+    qp, kp, vp = strided(qp), strided(kp), strided(vp)
+    if kp.stride() != qp.stride() or vp.stride() != qp.stride():
+        qp, kp, vp = qp.contiguous(), kp.contiguous(), vp.contiguous()
+    gsb = gst = 0
+    if gate_logits is not None:
+        gate_logits = gate_logits.to(qp.dtype)
+        if gate_logits.stride(2) != 1:
+            gate_logits = gate_logits.contiguous()
+        gsb, gst = gate_logits.stride(0), gate_logits.stride(1)
+    theta = _f32c(theta)
+    pos = pos.to(torch.int64).contiguous()
+    q = torch.empty(B, H, T, D, device=qp.device, dtype=out_dtype)
+    k, v = torch.empty_like(q), torch.empty_like(q)
+    check(lib().pgb_aspin_prep_fwd(ptr(qp), ptr(kp), ptr(vp), dtype_code(qp), qp.stride(0), qp.stride(1), qp.stride(2),
+                                   ptr(gate_logits), gsb, gst, ptr(theta), ptr(pos), ptr(q), ptr(k), ptr(v), dtype_code(q),
+                                   B, T, H, D, stream_of(qp)), "pgb_aspin_prep_fwd")
+    return q, k, v
+
+
+# ----------------------------------------------------------------------------------------------------------
+def prefill(q, k, v, la, beta=None, S0=None, theta=None, shift=0.0, want_sent: bool = False,
+            precision: int = _lib.PREFILL_AUTO, out_dtype=None):
+    """Chunked prefill. q,k,v (B,H,T,D) fp32 or bf16 (same dtype); la (B,H,T); beta (B,H,T) or None (plain rule);
+    S0 (B,H,D,D) or None.  theta/shift: rebase S0's key axis by -shift*theta first (shift: number or 0-d CUDA tensor).
+    Returns (o in out_dtype (default q's dtype), S fp32, sent bf16 (B,H,NC,D,D) or None)."""
+    need_cuda(q, k, v, la)
+    B, H, T, D = q.shape
+    if q.dtype not in (torch.float32, torch.bfloat16):
+        q = q.float()
+    q, k, v = q.contiguous(), k.to(q.dtype).contiguous(), v.to(q.dtype).contiguous()
+    la, beta, S0 = _f32c(la), _f32c(beta), _f32c(S0)
+    shift_dev, shift_host = None, 0.0
+    if theta is not None and S0 is not None:
+        theta = _f32c(theta)
+        if torch.is_tensor(shift):
+            shift_dev = shift.to(torch.float32).reshape(())
+            need_cuda(shift_dev)
+        else:
+            shift_host = float(shift)
+            if shift_host == 0.0:
+                theta = None
+    else:
+        theta = None
+    o = torch.empty(B, H, T, D, device=q.device, dtype=out_dtype or q.dtype)
+    S = torch.empty(B, H, D, D, device=q.device, dtype=torch.float32)
+    NC = (T + CHUNK - 1) // CHUNK
+    sent = torch.empty(B, H, NC, D, D, device=q.device, dtype=torch.bfloat16) if want_sent else None
+    check(lib().pgb_aspin_prefill_fwd(ptr(q), ptr(k), ptr(v), dtype_code(q), ptr(la), ptr(beta), ptr(S0), ptr(theta),
+                                      ptr(shift_dev), shift_host, ptr(o), dtype_code(o), ptr(S), ptr(sent), B, H, T, D, precision,
+                                      stream_of(q)), "pgb_aspin_prefill_fwd")
+    return o, S, sent
+
+
+# ----------------------------------------------------------------------------------------------------------
+def rotate(x, theta, pos):
+    """Rotate channel pairs of x (B,H,T,D) by pos[t]*theta[h,i]."""
+    need_cuda(x, theta, pos)
+    B, H, T, D = x.shape
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        x = x.float()
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    check(lib().pgb_rotate_pairs(ptr(x), dtype_code(x), ptr(_f32c(theta)), ptr(_f32c(pos)), ptr(out), B, H, T, D,
+                                 stream_of(x)), "pgb_rotate_pairs")
+    return out
+
+
+# ----------------------------------------------------------------------------------------------------------
+def decode_step(qp, kp, vp, decay, S, theta, *, gate=None, delta: bool = False, gate_is_logit: bool = True,
+                decay_A=None, normalize: bool = True, shift=0.0, rms_weight=None, rms_eps: float = 0.0,
+                out: Optional[torch.Tensor] = None, S_out: Optional[torch.Tensor] = None, out_dtype=None):
+    """One fused recurrent step. qp,kp,vp: (B,H,D) views with unit strides over (H,D) and a common batch stride;
+    decay, gate: (B,H) views with unit stride over H.  S (B,H,D,D) fp32; S_out defaults to a new tensor (pass S itself
+    for an in-place update).  Returns (o (B,H,D), S_out)."""
+    need_cuda(qp, kp, vp, decay, S, theta)
+    B, H, D = qp.shape
+    for t in (qp, kp, vp):
+        if t.stride(2) != 1 or t.stride(1) != D or t.dtype != qp.dtype:
+            raise ValueError("decode_step: q,k,v must be (B,H,D) with unit strides over (H,D) and one dtype")
+    if kp.stride(0) != qp.stride(0) or vp.stride(0) != qp.stride(0):
+        raise ValueError("decode_step: q,k,v must share the batch stride")
+    if decay.dtype != qp.dtype or (gate is not None and gate.dtype != qp.dtype):
+        raise ValueError("decode_step: decay and gate must have q's dtype")
+    if S.dtype != torch.float32 or not S.is_contiguous():
+        raise ValueError("decode_step: the state must be contiguous fp32")
+    S_out = torch.empty_like(S) if S_out is None else S_out
+    out_dtype = out_dtype or qp.dtype
+    if out is None:
+        out = torch.empty(B, H, D, device=qp.device, dtype=out_dtype)
+    shift_dev, shift_host = (shift.to(torch.float32), 0.0) if torch.is_tensor(shift) else (None, float(shift))
+    sb = lambda t: t.stride(0) if B > 1 else max(t.stride(0), H * (t.shape[2] if t.dim() == 3 else 1))
+    check(lib().pgb_aspin_decode_step(
+        ptr(qp), ptr(kp), ptr(vp), dtype_code(qp), sb(qp), int(normalize), ptr(gate), 0 if gate is None else gate.stride(0),
+        int(gate_is_logit), int(delta), ptr(decay), decay.stride(0), ptr(_f32c(decay_A)), ptr(_f32c(theta)),
+        ptr(shift_dev), shift_host, ptr(S), ptr(S_out), ptr(_f32c(rms_weight)), float(rms_eps), ptr(out), dtype_code(out),
+        sb(out), B, H, D, stream_of(qp)), "pgb_aspin_decode_step")
+    return out, S_out

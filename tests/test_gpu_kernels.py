@@ -1,0 +1,281 @@
+"""Parity of the CUDA kernels (called through the C ABI) against the CPU oracle and the reference-generated fixtures."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+import oracle
+from oracle import rel_err
+from pragnosia_b200 import ops, synth, _lib
+
+pytestmark = pytest.mark.gpu
+torch.set_grad_enabled(False)
+DEV = "cuda"
+
+
+def cu(x):
+    if isinstance(x, (tuple, list)):
+        return type(x)(cu(t) for t in x)
+    return x.to(DEV) if torch.is_tensor(x) else x
+
+
+def close(a, b, tol, what=""):
+    a, b = a.detach().cpu(), b.detach().cpu()
+    assert a.shape == b.shape, (a.shape, b.shape)
+    assert torch.isfinite(a).all(), f"{what}: non-finite"
+    e = rel_err(a, b)
+    assert e <= tol, f"{what}: rel err {e:.3e} > {tol}"
+    return e
+
+
+# ------------------------------------------------------------------------------------------------ lambda scan
+@pytest.mark.parametrize("ts", [0, 1, 2, 4, 8, 16, 32])
+def test_lambda_scan_d300_carried_state(golden, ts):
+    """tests/test_spin.py:225-236 of the reference: B2 T45 D300, carried h0, vs the fp64 definition, < 1e-5 absolute."""
+    g = torch.Generator().manual_seed(6)
+    u = torch.randn(2, 45, 300, generator=g); lm = -torch.rand(2, 45, 300, generator=g) * 8; an = torch.randn(2, 45, 300, generator=g)
+    h0 = (torch.randn(2, 300, generator=g), torch.randn(2, 300, generator=g))
+    G = golden("lambda_scan")["d300"]
+    y, (hr, hi) = ops.lambda_scan(cu(u), cu(lm), cu(an), cu(h0), time_segments=ts)
+    assert (y.cpu() - G["y"].float()).abs().max().item() < 1e-5
+    assert (hr.cpu() - G["hr"].float()).abs().max().item() < 1e-5
+    assert (hi.cpu() - G["hi"].float()).abs().max().item() < 1e-5
+    y0, _ = ops.lambda_scan(cu(u), cu(lm), cu(an), None, time_segments=ts)
+    r0, _ = oracle.lambda_literal(u.double(), lm.double(), an.double())
+    assert (y0.cpu() - r0.float()).abs().max().item() < 1e-5
+
+
+@pytest.mark.parametrize("D,T", [(6, 45), (302, 17), (768, 1), (96, 2048), (768, 300)])
+def test_lambda_scan_shapes_and_broadcast_angle(D, T):
+    x = synth.lambda_scan_inputs(2, T, D, seed=4, with_state=True)
+    ref_y, (rr, ri) = oracle.lambda_literal(x["u"].double(), x["logmag"].double(), x["ang"].double(),
+                                            (x["h0"][0].double(), x["h0"][1].double()))
+    y, (hr, hi) = ops.lambda_scan(cu(x["u"]), cu(x["logmag"]), cu(x["ang"]), cu(x["h0"]))
+    close(y, ref_y.float(), 2e-5, "y"); close(hr, rr.float(), 2e-5, "hr"); close(hi, ri.float(), 2e-5, "hi")
+    # one angle per channel, passed as a zero-stride expanded view (what the fspin layer passes)
+    xb = synth.lambda_scan_inputs(2, T, D, seed=5, with_state=True, per_channel_angle=True)
+    ang_dev = cu(xb["ang"][0, 0].contiguous()).expand(2, T, D)
+    ref_y, (rr, ri) = oracle.lambda_literal(xb["u"].double(), xb["logmag"].double(), xb["ang"].double(),
+                                            (xb["h0"][0].double(), xb["h0"][1].double()))
+    y, (hr, hi) = ops.lambda_scan(cu(xb["u"]), cu(xb["logmag"]), ang_dev, cu(xb["h0"]))
+    close(y, ref_y.float(), 2e-5, "y bcast"); close(hi, ri.float(), 2e-5, "hi bcast")
+
+
+def test_lambda_scan_sequential_mode_and_windows():
+    """One time segment per warp is the literal recurrence; two carried windows equal one pass; extreme decay is finite."""
+    x = synth.lambda_scan_inputs(3, 333, 128, seed=9, with_state=True)
+    a = ops.lambda_scan(cu(x["u"]), cu(x["logmag"]), cu(x["ang"]), cu(x["h0"]), time_segments=1)
+    b = ops.lambda_scan(cu(x["u"]), cu(x["logmag"]), cu(x["ang"]), cu(x["h0"]), time_segments=1)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1][1], b[1][1])                       # deterministic
+    c = ops.lambda_scan(cu(x["u"]), cu(x["logmag"]), cu(x["ang"]), cu(x["h0"]), time_segments=8)
+    close(c[0], a[0], 1e-5, "parallel vs sequential")
+    w1 = ops.lambda_scan(cu(x["u"][:, :100]), cu(x["logmag"][:, :100]), cu(x["ang"][:, :100]), cu(x["h0"]))
+    w2 = ops.lambda_scan(cu(x["u"][:, 100:]), cu(x["logmag"][:, 100:]), cu(x["ang"][:, 100:]), w1[1])
+    close(torch.cat([w1[0], w2[0]], 1), a[0], 1e-5, "windows"); close(w2[1][1], a[1][1], 1e-5, "windows Im")
+    lmx = torch.full((2, 512, 8), -40.0)
+    yx, _ = ops.lambda_scan(cu(torch.randn(2, 512, 8)), cu(lmx), cu(torch.randn(2, 512, 8)))
+    assert torch.isfinite(yx).all()
+
+
+# ------------------------------------------------------------------------------------------------ prep, rotate
+def prep_ref(qp, kp, vp, gl, theta, pos):
+    q_, k_, v_ = [F.normalize(t.transpose(1, 2).float(), dim=-1) for t in (qp, kp, vp)]
+    if gl is not None:
+        k_ = k_ * torch.sigmoid(gl.float()).transpose(1, 2).unsqueeze(-1)
+    return oracle.rotate(q_, theta, pos), oracle.rotate(k_, theta, pos), v_
+
+
+@pytest.mark.parametrize("D,T,gate,p0", [(64, 2048, True, 0), (64, 333, False, 1000), (128, 512, True, 4096)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
+def test_prep_kernel(D, T, gate, p0, dt):
+    """tests/test_assoc.py:196-212 of the reference (forward part), bf16 outputs < 1e-2; fp32 in/out < 1e-5."""
+    g = torch.Generator().manual_seed(0)
+    H = 3
+    mk = lambda: (torch.randn(2, T, H, D, generator=g) * 3).to(dt)
+    qp, kp, vp = mk(), mk(), mk()
+    gl = (torch.randn(2, T, H, generator=g) * 2).to(dt) if gate else None
+    th = synth.rope_theta(H, D); pos = p0 + torch.arange(T)
+    refs = prep_ref(qp, kp, vp, gl, th, pos)
+    outs = ops.prep(cu(qp), cu(kp), cu(vp), cu(gl), cu(th), cu(pos), out_dtype=dt)
+    for o_, r_, n in zip(outs, refs, "qkv"):
+        assert o_.dtype == dt and tuple(o_.shape) == (2, H, T, D)
+        close(o_.float(), r_, 1e-2 if dt == torch.bfloat16 else 1e-5, n)
+    # the same through views into one fused projection (strided input)
+    fused = torch.cat([qp.flatten(2), kp.flatten(2), vp.flatten(2), torch.zeros(2, T, 8, dtype=dt)], -1).to(DEV)
+    d = H * D
+    views = [fused[..., i * d:(i + 1) * d].unflatten(-1, (H, D)) for i in range(3)]
+    outs2 = ops.prep(*views, cu(gl), cu(th), cu(pos), out_dtype=dt)
+    for a, b in zip(outs, outs2):
+        assert torch.equal(a, b)
+
+
+def test_rotate_matches_and_is_relative():
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(2, 3, 45, 64, generator=g); th = torch.rand(3, 32, generator=g) * 0.3
+    pos = torch.arange(1000, 1045)
+    close(ops.rotate(cu(x), cu(th), cu(pos)), oracle.rotate(x, th, pos), 1e-5, "rotate")
+    qq, kk, t1 = torch.randn(1, 1, 1, 8, generator=g), torch.randn(1, 1, 1, 8, generator=g), torch.rand(1, 4, generator=g) * 0.3
+    r = lambda v, p: ops.rotate(cu(v), cu(t1), cu(torch.tensor([p]))).cpu()
+    assert abs((r(qq, 10) * r(kk, 3)).sum().item() - (r(qq, 107) * r(kk, 100)).sum().item()) < 1e-4
+
+
+# ------------------------------------------------------------------------------------------------ chunked prefill
+def run_prefill(x, delta=False, dtype=torch.float32, S0=True, **kw):
+    qr, kr = oracle.rotate(x["q"], x["theta"], x["pos"]), oracle.rotate(x["k"], x["theta"], x["pos"])
+    q, k, v = (t.to(dtype) for t in (qr, kr, x["v"]))
+    beta = x.get("beta") if delta else None
+    s0 = x.get("S0") if S0 else None
+    out = ops.prefill(cu(q), cu(k), cu(v), cu(x["la"]), cu(beta), cu(s0), **kw)
+    ref = oracle.assoc_scan(q.float(), k.float(), v.float(), x["la"], s0, chunk=64, beta=beta)
+    return out, ref
+
+
+def test_prefill_cfg0_full_size_fp32(golden):
+    """Configuration 0: B2 T512 H12 D64, fp32: output (2,512,768) within 2e-3 and state within 1e-4 of the reference's CPU
+    result (measured far inside both)."""
+    G = golden("cfg0")
+    x = synth.assoc_op_inputs(2, 12, 512, 64, seed=0)
+    (o, S, _), _ = run_prefill(x, S0=False)
+    assert tuple(o.transpose(1, 2).reshape(2, 512, 768).shape) == (2, 512, 768)
+    e1 = close(o[:, :, ::8], G["o_sub"], 2e-3, "o"); e2 = close(S, G["S"], 1e-4, "S")
+    close(o[:, :, ::8], G["o_sub_literal"], 2e-3, "o vs literal"); close(S, G["S_literal"], 1e-4, "S vs literal")
+    assert e1 < 1e-5 and e2 < 1e-5, (e1, e2)                        # the fp32 kernel is an fp32 computation
+    (o2, S2, _), _ = run_prefill(x, S0=False)
+    assert torch.equal(o, o2) and torch.equal(S, S2)                # run twice, bit-identical
+
+
+def test_prefill_cfg0_bf16_inputs(golden):
+    """bf16 I/O: compared with the oracle on the same bf16-rounded inputs. The fp32 output of the kernel must be within
+    2e-3 (state 1e-4); the bf16 output must be exactly that result rounded to nearest."""
+    x = synth.assoc_op_inputs(2, 12, 512, 64, seed=0)
+    (o32, S, _), (ro, rS) = run_prefill(x, dtype=torch.bfloat16, S0=False, out_dtype=torch.float32)
+    close(o32, ro, 2e-3, "o"); close(S, rS, 1e-4, "S")
+    (o16, S16, _), _ = run_prefill(x, dtype=torch.bfloat16, S0=False)
+    assert o16.dtype == torch.bfloat16 and torch.equal(o16, o32.to(torch.bfloat16)) and torch.equal(S, S16)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("delta", [False, True])
+def test_prefill_ragged_carried(golden, D, delta):
+    """T=333 (partial last chunk), carried S0, both rules, both head dims: the reference's kernel tests
+    (tests/test_assoc.py:146-185) against its CPU two-pass form; here also against the literal recurrence."""
+    G = golden("ragged")[D]
+    x = synth.assoc_op_inputs(2, 3, 333, D, seed=10 + D, delta=True, with_state=True)
+    (o, S, sent), (ro, rS) = run_prefill(x, delta=delta, want_sent=True)
+    close(o[:, :, ::4], G["od" if delta else "o"], 2e-5, "o golden"); close(S, G["Sd" if delta else "S"], 2e-5, "S golden")
+    close(o, ro, 2e-5, "o oracle")
+    assert tuple(sent.shape) == (2, 3, 6, D, D) and sent.dtype == torch.bfloat16
+    # entering states: chunk 0 is S0; chunk c is the state after 64c tokens
+    close(sent[:, :, 0].float(), x["S0"].to(torch.bfloat16).float(), 1e-6, "sent[0]")
+    qr, kr = oracle.rotate(x["q"], x["theta"], x["pos"]), oracle.rotate(x["k"], x["theta"], x["pos"])
+    _, S128 = oracle.assoc_scan(qr[:, :, :128], kr[:, :, :128], x["v"][:, :, :128], x["la"][:, :, :128], x["S0"],
+                                beta=x["beta"][:, :, :128] if delta else None)
+    close(sent[:, :, 2].float(), S128, 1e-2, "sent[2]")
+    # bf16 inputs
+    (ob, Sb, _), (rob, rSb) = run_prefill(x, delta=delta, dtype=torch.bfloat16, out_dtype=torch.float32)
+    close(ob, rob, 2e-3, "o bf16-in"); close(Sb, rSb, 1e-4, "S bf16-in")
+
+
+@pytest.mark.parametrize("T", [1, 2, 63, 64, 65, 128, 200])
+@pytest.mark.parametrize("delta", [False, True])
+def test_prefill_lengths_and_windows(T, delta):
+    x = synth.assoc_op_inputs(2, 2, T, 64, seed=T, delta=True, with_state=True)
+    (o, S, _), (ro, rS) = run_prefill(x, delta=delta)
+    close(o, ro, 2e-5, "o"); close(S, rS, 2e-5, "S")
+    lo, lS = (oracle.delta_literal if delta else oracle.plain_literal)(
+        *[t.double() for t in (oracle.rotate(x["q"], x["theta"], x["pos"]), oracle.rotate(x["k"], x["theta"], x["pos"]),
+                               x["v"], x["la"])], *([x["beta"].double()] if delta else []), x["S0"].double())
+    close(o, lo.float(), 2e-5, "o literal"); close(S, lS.float(), 2e-5, "S literal")
+    if T >= 64:                                                      # two carried windows == one pass
+        cut = 40
+        qr, kr = oracle.rotate(x["q"], x["theta"], x["pos"]), oracle.rotate(x["k"], x["theta"], x["pos"])
+        be = x["beta"] if delta else None
+        a = ops.prefill(cu(qr[:, :, :cut]), cu(kr[:, :, :cut]), cu(x["v"][:, :, :cut]), cu(x["la"][:, :, :cut]),
+                        cu(be[:, :, :cut]) if delta else None, cu(x["S0"]))
+        b = ops.prefill(cu(qr[:, :, cut:]), cu(kr[:, :, cut:]), cu(x["v"][:, :, cut:]), cu(x["la"][:, :, cut:]),
+                        cu(be[:, :, cut:]) if delta else None, a[1])
+        close(torch.cat([a[0], b[0]], 2), o, 2e-5, "windows o"); close(b[1], S, 2e-5, "windows S")
+
+
+def test_prefill_rebase_rotates_the_carried_state():
+    x = synth.assoc_op_inputs(2, 3, 70, 64, seed=21, with_state=True)
+    th = torch.rand(3, 32) * 0.5
+    o, S, _ = ops.prefill(cu(x["q"]), cu(x["k"]), cu(x["v"]), cu(x["la"]), None, cu(x["S0"]), theta=cu(th), shift=37.0)
+    ro, rS = oracle.assoc_scan(x["q"], x["k"], x["v"], x["la"], oracle.decode_rebase(x["S0"], th, 37.0))
+    close(o, ro, 2e-5, "o"); close(S, rS, 2e-5, "S")
+    o2, S2, _ = ops.prefill(cu(x["q"]), cu(x["k"]), cu(x["v"]), cu(x["la"]), None, cu(x["S0"]), theta=cu(th),
+                            shift=torch.tensor(37.0, device=DEV))
+    assert torch.equal(o, o2) and torch.equal(S, S2)
+
+
+def test_delta_known_answers(golden):
+    """tests/test_assoc.py:118-139 of the reference: a key written twice reads back the second value; 256 correlated
+    writes with beta = 1 stay bounded; one key repeated 128 times with beta -> 1 (src/assoc_kernel.py:577-582)."""
+    G = golden("delta_kat")
+    K4, V4 = G["overwrite"]["K"].float(), G["overwrite"]["V"].float()
+    pad = lambda t: F.pad(t, (0, 60))
+    K, V = pad(K4), pad(V4)
+    z, one = torch.zeros(1, 1, 3), torch.ones(1, 1, 3)
+    od, _, _ = ops.prefill(cu(K), cu(K), cu(V), cu(z), cu(one), None)
+    op, _, _ = ops.prefill(cu(K), cu(K), cu(V), cu(z), None, None)
+    assert torch.allclose(od.cpu()[0, 0, 1, :4], V4[0, 0, 1], atol=1e-6)
+    assert torch.allclose(op.cpu()[0, 0, 1, :4], V4[0, 0, 0] + V4[0, 0, 1], atol=1e-6)
+    g = torch.Generator().manual_seed(1)
+    Kr = F.normalize(torch.randn(2, 4, 256, 64, generator=g), dim=-1); Vr = F.normalize(torch.randn(2, 4, 256, 64, generator=g), dim=-1)
+    y, S, _ = ops.prefill(cu(Kr), cu(Kr), cu(Vr), cu(torch.zeros(2, 4, 256)), cu(torch.ones(2, 4, 256)), None)
+    assert S.abs().max().item() < 2.0
+    close(y[:, :, ::8], G["correlated"]["y16"], 2e-5, "correlated y"); close(S, G["correlated"]["S16"], 2e-5, "correlated S")
+    R = G["repeated"]
+    k = R["k"].expand(1, 1, 128, 64).contiguous().float()
+    be = torch.full((1, 1, 128), 0.99999); la = torch.full((1, 1, 128), -1e-4)
+    o, S, _ = ops.prefill(cu(R["q"].float()), cu(k), cu(R["v"].float()), cu(la), cu(be), None)
+    close(o, R["o"].float(), 1e-4, "repeated o"); close(S, R["S"].float(), 1e-4, "repeated S")
+    assert S.abs().max().item() < 3.0
+
+
+def test_prefill_extreme_decay_is_finite():
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(2, 4, 512, 64, generator=g)
+    la = -torch.rand(2, 4, 512, generator=g) * 40
+    o, S, _ = ops.prefill(cu(q), cu(torch.randn(2, 4, 512, 64, generator=g)), cu(torch.randn(2, 4, 512, 64, generator=g)), cu(la))
+    assert torch.isfinite(o).all() and torch.isfinite(S).all()
+
+
+# ------------------------------------------------------------------------------------------------ decode step
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("delta", [False, True])
+@pytest.mark.parametrize("B", [1, 64])
+def test_decode_step_against_oracle(D, delta, B):
+    H = 3
+    g = torch.Generator().manual_seed(D + B)
+    qp, kp, vp = (torch.randn(B, H, D, generator=g) * 2 for _ in range(3))
+    gate = torch.randn(B, H, generator=g); araw = torch.randn(B, H, generator=g); A = torch.randn(H, generator=g) - 3
+    S = torch.randn(B, H, D, D, generator=g) * 0.2
+    th = torch.rand(H, D // 2, generator=g) * 0.4
+    w = torch.rand(D, generator=g) + 0.5
+    # oracle on prepared vectors
+    q, k, v = (F.normalize(t, dim=-1) for t in (qp, kp, vp))
+    la = -F.softplus(araw) * A.exp()
+    if delta:
+        o_ref, S_ref = oracle.decode_step(S, 29.0, q, k, v, la, th, torch.sigmoid(gate))
+    else:
+        o_ref, S_ref = oracle.decode_step(S, 29.0, q, k * torch.sigmoid(gate)[..., None], v, la, th)
+    eps = 1.1920929e-07
+    o_norm = o_ref * torch.rsqrt(o_ref.pow(2).mean(-1, keepdim=True) + eps) * w
+    Sd = cu(S)
+    o, S1 = ops.decode_step(cu(qp), cu(kp), cu(vp), cu(araw), Sd, cu(th), gate=cu(gate), delta=delta, decay_A=cu(A), shift=29.0)
+    close(o, o_ref, 1e-5, "o"); close(S1, S_ref, 1e-5, "S")
+    assert torch.equal(Sd.cpu(), S)                                  # functional by default: the input state is untouched
+    o2, _ = ops.decode_step(cu(qp), cu(kp), cu(vp), cu(araw), Sd, cu(th), gate=cu(gate), delta=delta, decay_A=cu(A),
+                            shift=torch.tensor(29.0, device=DEV), rms_weight=cu(w), rms_eps=eps)
+    close(o2, o_norm, 1e-5, "o rms")
+    # in place, bf16 vectors in a fused row (strided), log-decay given directly
+    row = torch.cat([qp.flatten(1), kp.flatten(1), vp.flatten(1), la, gate, torch.zeros(B, 2)], 1).to(torch.bfloat16).to(DEV)
+    d = H * D
+    views = [row[:, i * d:(i + 1) * d].unflatten(1, (H, D)) for i in range(3)]
+    o3, S3 = ops.decode_step(*views, row[:, 3 * d:3 * d + H], Sd, cu(th), gate=row[:, 3 * d + H:3 * d + 2 * H], delta=delta,
+                             shift=29.0, S_out=Sd, out_dtype=torch.float32)
+    assert S3.data_ptr() == Sd.data_ptr()
+    rq, rk, rv = (F.normalize(t.to(torch.bfloat16).float(), dim=-1) for t in (qp, kp, vp))
+    rg, rla = torch.sigmoid(gate.to(torch.bfloat16).float()), la.to(torch.bfloat16).float()
+    o_r, S_r = oracle.decode_step(S, 29.0, rq, rk if delta else rk * rg[..., None], rv, rla, th, rg if delta else None)
+    close(o3, o_r, 1e-5, "o in-place"); close(Sd, S_r, 1e-5, "S in-place")

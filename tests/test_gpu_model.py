@@ -1,0 +1,127 @@
+"""The carrier layers, the language model's carried-window pass and the graphed decode loop on the GPU, against the
+CPU oracle and the fixtures generated from the reference."""
+import pytest
+import torch
+
+import oracle
+from oracle import rel_err
+from pragnosia_b200 import synth
+from pragnosia_b200.assoc import AssocCarrier
+from pragnosia_b200.spin import SpinCarrier
+from pragnosia_b200.model import LM
+from pragnosia_b200.generate import Decoder
+
+pytestmark = pytest.mark.gpu
+torch.set_grad_enabled(False)
+DEV = "cuda"
+
+
+def close(a, b, tol, what=""):
+    a, b = a.detach().float().cpu(), b.detach().float().cpu()
+    assert a.shape == b.shape, (a.shape, b.shape)
+    assert torch.isfinite(a).all(), f"{what}: non-finite"
+    e = rel_err(a, b)
+    assert e <= tol, f"{what}: rel err {e:.3e} > {tol}"
+    return e
+
+
+LAYERS = (("plain_d64", 64, 1, False, None), ("delta_d128_h2", 128, 2, True, None),
+          ("plain_d128_hd128", 128, 1, False, 128), ("delta_d256_hd128", 256, 2, True, 128))
+
+
+@pytest.mark.parametrize("name,d,heads,delta,hd", LAYERS)
+def test_assoc_layer_matches_reference(golden, name, d, heads, delta, hd):
+    """tests/test_assoc.py:49-64 of the reference: shapes, p == 70, carried windows == one pass, strict causality; plus
+    values against the reference module's own CPU output, and ten T=1 steps through the fused decode kernel."""
+    G = golden("layers")[name]
+    g = torch.Generator().manual_seed(len(name))
+    P = oracle.init_assoc_params({}, "", d, heads, delta, g, jitter=0.3)
+    x = torch.randn(2, 70, d, generator=g)
+    m = AssocCarrier(d, heads=heads, delta=delta, head_dim=hd)
+    m.load_state_dict(P, strict=True)
+    m = m.to(DEV).eval()
+    xd = x.to(DEV)
+    y, (S, p) = m(xd)
+    assert tuple(y.shape) == (2, 70, d) and tuple(S.shape) == (2, heads, d // heads, d // heads) and p == 70
+    close(y, G["y"], 1e-4, "y"); close(S, G["S"], 1e-4, "S")
+    ya, sa = m(xd[:, :30]); yb, (Sb, pb) = m(xd[:, 30:], h0=sa)
+    close(torch.cat([ya, yb], 1), G["y_windows"], 1e-4, "windows"); close(Sb, G["S_windows"], 1e-4, "S windows")
+    assert pb == 40
+    close(torch.cat([ya, yb], 1), y, 1e-4, "carried windows == one pass")
+    st = sa; steps = []
+    for t in range(30, 40):
+        yt, st = m(xd[:, t:t + 1], h0=st); steps.append(yt)
+    close(torch.cat(steps, 1), G["y_steps"], 1e-4, "decode steps"); close(st[0], G["S_steps"], 1e-4, "decode state")
+    assert st[1] == 1
+    x2 = xd.clone(); x2[:, 50] += 3.0
+    y2, _ = m(x2)
+    assert torch.equal(y2[:, :50], y[:, :50])                                     # bit-equal before the edit
+    m.need_sent = True
+    m(xd); assert m.sent is not None and tuple(m.sent.shape) == (2, heads, 2, d // heads, d // heads)
+
+
+def test_fspin_layer_matches_reference(golden):
+    G = golden("layers")["fspin_d48"]
+    g = torch.Generator().manual_seed(48)
+    P = oracle.init_fspin_params({}, "", 48, g, jitter=0.3)
+    x = torch.randn(2, 70, 48, generator=g)
+    m = SpinCarrier(48, gated="rf"); m.load_state_dict(P, strict=True); m = m.to(DEV).eval()
+    y, h = m(x.to(DEV))
+    close(y, G["y"], 1e-5, "y"); close(h[0], G["h"][0], 1e-5, "hr"); close(h[1], G["h"][1], 1e-5, "hi")
+    ya, ha = m(x[:, :30].to(DEV)); yb, hb = m(x[:, 30:].to(DEV), ha)
+    close(torch.cat([ya, yb], 1), G["y_windows"], 1e-5, "windows"); close(hb[1], G["h_windows"][1], 1e-5, "hi windows")
+
+
+MODELS = [("aspin", "ln"), ("aspin", "rms"), ("dspin", "ln"), ("hspin", "rms"), ("hdspin", "ln"), ("fspin", "ln")]
+
+
+def small_lm(mixer, norm, dtype=torch.float32):
+    cfg = oracle.lm_config(vocab=256, d=128, layers=2, mlp_mult=2, ctx=32, mixer=mixer, norm=norm)
+    P = oracle.init_lm_params(cfg, seed=7, jitter=0.2)
+    m = LM(vocab=256, d=128, layers=2, mlp_mult=2, ctx=32, mixer=mixer, norm=norm)
+    m.load_state_dict(P, strict=True)
+    return m.to(DEV).to(dtype).eval(), P, cfg
+
+
+@pytest.mark.parametrize("mixer,norm", MODELS)
+def test_lm_forward_carried_and_decode(golden, mixer, norm):
+    """forward_carried over three 32-token windows (tests/test_assoc.py:80-81: shape (2,32,V)) and the decode loop of
+    src/bench.py:206-238, teacher-forced, against the reference model's CPU outputs."""
+    G = golden("lm")[f"{mixer}_{norm}"]
+    m, P, cfg = small_lm(mixer, norm)
+    ids = synth.token_ids(2, 96, 256, seed=11).to(DEV)
+    logits = m.forward_carried(ids)
+    assert tuple(logits.shape) == (2, 32, 256)
+    close(logits, G["logits"], 2e-4, "logits")
+    for use_graph in (False, True):
+        dec = Decoder(m, batch=2, use_graph=use_graph)
+        out = [dec.prefill(ids[:, :40])]
+        for t in range(40, 46):
+            out.append(dec.step(ids[:, t]).clone())
+        close(torch.stack(out, 1), G["decode_logits"], 2e-4, f"decode graph={use_graph}")
+        close(dec.states[0][0], G["state0"], 2e-4, "layer-0 state")
+    full = m(ids[:, :32])
+    close(full, oracle.lm_prefill(P, cfg, ids[:, :32].cpu())[0], 2e-4, "single window forward")
+
+
+def test_lm_bf16_weights_fp32_state():
+    """bf16 weights and activations, fp32 state (the timed configuration): logits against the fp32 oracle run on the
+    same bf16-rounded weights. bf16 activations bound this at ~1e-2, not the kernels."""
+    m, P, cfg = small_lm("aspin", "rms", torch.bfloat16)
+    Pb = {k: v.to(torch.bfloat16).float() for k, v in P.items()}
+    ids = synth.token_ids(2, 96, 256, seed=11)
+    lg, states = m.forward_carried(ids.to(DEV), return_states=True)
+    ref, rstates = oracle.lm_prefill(Pb, cfg, ids)
+    assert states[0][0].dtype == torch.float32
+    close(lg, ref, 3e-2, "bf16 logits"); close(states[0][0], rstates[0][0], 3e-2, "bf16-run state")
+
+
+def test_generate_runs_and_is_seeded():
+    m, _, _ = small_lm("aspin", "ln")
+    prompt = synth.token_ids(3, 40, 256, seed=2).to(DEV)
+    a = Decoder(m, batch=3).generate(prompt, 12, temp=1.0, seed=5)
+    b = Decoder(m, batch=3).generate(prompt, 12, temp=1.0, seed=5)
+    assert tuple(a.shape) == (3, 12) and torch.equal(a, b)
+    g1 = Decoder(m, batch=3, use_graph=False).generate(prompt, 12, temp=0.0)
+    g2 = Decoder(m, batch=3, use_graph=True).generate(prompt, 12, temp=0.0)
+    assert torch.equal(g1, g2)
