@@ -32,9 +32,11 @@ def _stale(src: Path, obj: Path, headers) -> bool:
 
 def build(verbose: bool = False, force: bool = False) -> Path:
     LIBDIR.mkdir(exist_ok=True)
+    headers = list(CSRC.glob("*.cuh")) + list((PKG.parent / "include").glob("*.h"))
+    if not force and LIB.exists() and all(f.stat().st_mtime <= LIB.stat().st_mtime for f in sources() + headers):
+        return LIB                                  # the prebuilt library is newer than every source: nothing to do
     objdir = PKG / "build"
     objdir.mkdir(exist_ok=True)
-    headers = list(CSRC.glob("*.cuh")) + list((PKG.parent / "include").glob("*.h"))
     jobs = []
     for src in sources():
         obj = objdir / (src.stem + ".o")

@@ -67,9 +67,10 @@ def test_fspin_layer_matches_reference(golden):
     x = torch.randn(2, 70, 48, generator=g)
     m = SpinCarrier(48, gated="rf"); m.load_state_dict(P, strict=True); m = m.to(DEV).eval()
     y, h = m(x.to(DEV))
-    close(y, G["y"], 1e-5, "y"); close(h[0], G["h"][0], 1e-5, "hr"); close(h[1], G["h"][1], 1e-5, "hi")
+    # fp32 projections on the GPU and on the CPU differ in summation order: a few 1e-5 on the carried state
+    close(y, G["y"], 5e-5, "y"); close(h[0], G["h"][0], 5e-5, "hr"); close(h[1], G["h"][1], 5e-5, "hi")
     ya, ha = m(x[:, :30].to(DEV)); yb, hb = m(x[:, 30:].to(DEV), ha)
-    close(torch.cat([ya, yb], 1), G["y_windows"], 1e-5, "windows"); close(hb[1], G["h_windows"][1], 1e-5, "hi windows")
+    close(torch.cat([ya, yb], 1), G["y_windows"], 5e-5, "windows"); close(hb[1], G["h_windows"][1], 5e-5, "hi windows")
 
 
 MODELS = [("aspin", "ln"), ("aspin", "rms"), ("dspin", "ln"), ("hspin", "rms"), ("hdspin", "ln"), ("fspin", "ln")]
