@@ -92,6 +92,11 @@ int pgb_aspin_prefill_fwd(const void *q, const void *k, const void *v, int io_dt
                           float shift_host, void *o, int o_dtype, float *S_out, void *sent, int B, int H, int T,
                           int D, int precision, void *stream);
 
+/* Health check of the tensor-core prefill kernel: every wait inside it is bounded, and a wait that runs out sets a
+ * device-side flag instead of hanging. This reads the flag into *out_host (0 = no wait ever ran out) and clears it.
+ * Unlike every other entry point it SYNCHRONISES the device. No counterpart in the reference. */
+int pgb_tc_error_flag(int *out_host);
+
 /* ---------------------------------------------------------------------------------------------------------
  * Rotation of channel pairs (2i, 2i+1) of x (B,H,T,D) by pos[t] * theta[h][i]; any even D.
  * Replaces src/assoc.py:34-39 rotate.   x, out: dtype, contiguous.  theta [H][D/2] fp32.  pos [T] fp32.

@@ -21,7 +21,11 @@ int prefill_fp32_launch(const PrefillArgs &, int, int, int, cudaStream_t);
 int prefill_tc_launch(const PrefillArgs &, int, int, cudaStream_t);
 bool prefill_tc_supported(int io_dtype, int D, bool delta);
 int decode_launch(const DecodeArgs &, int, int, int, int, cudaStream_t);
+int tc_error_flag(int *out);
 int rotate_launch(const void *, int, const float *, const float *, void *, int, int, int, int, cudaStream_t);
+
+// PGB_PREFILL_AUTO sends bf16 plain-rule work to the tensor-core kernel only once this is on
+static const bool kAutoUsesTensor = true;
 
 static inline size_t esize(int dt) { return dt == PGB_BF16 ? 2 : 4; }
 static inline bool dtype_ok(int dt) { return dt == PGB_F32 || dt == PGB_BF16; }
@@ -101,9 +105,14 @@ int pgb_aspin_prefill_fwd(const void *q, const void *k, const void *v, int io_dt
     PrefillArgs a{q, k, v, la, beta, S0, o, S_out, (__nv_bfloat16 *)sent, theta, shift_dev, shift_host, B, H, T};
     const bool tc_ok = prefill_tc_supported(io_dtype, D, beta != nullptr);
     if (precision == PGB_PREFILL_TENSOR && !tc_ok) return PGB_ERR_UNSUPPORTED_DIM;
-    if (precision == PGB_PREFILL_TENSOR || (precision == PGB_PREFILL_AUTO && tc_ok))
+    if (precision == PGB_PREFILL_TENSOR || (precision == PGB_PREFILL_AUTO && tc_ok && kAutoUsesTensor))
         return prefill_tc_launch(a, o_dtype, D, (cudaStream_t)stream);
     return prefill_fp32_launch(a, io_dtype, o_dtype, D, (cudaStream_t)stream);
+}
+
+int pgb_tc_error_flag(int *out_host) {
+    if (!out_host) return PGB_ERR_NULL_POINTER;
+    return tc_error_flag(out_host);
 }
 
 int pgb_rotate_pairs(const void *x, int dtype, const float *theta, const float *pos, void *out, int B, int H, int T, int D,

@@ -1,11 +1,496 @@
-// Tensor-core (tcgen05 / TMEM / TMA) chunked prefill. Placeholder translation unit until the kernel lands: reports
-// "not supported" so the C ABI routes nothing here.
+// Chunked prefill of the associative carrier on the 5th-generation tensor cores: tcgen05.mma with TMEM accumulators,
+// operands staged in shared memory by TMA, bf16 operands with fp32 accumulation and an fp32 state.
+//
+// One CTA walks the 64-token chunks of one (sequence, head). Per chunk c, with L the within-chunk cumulative log-decay:
+//   P  = Q K^T                                   (M=64 tokens, N=64 tokens, K=D)        state-independent
+//   U  = (K*w)^T V,  w_s = exp(L_C - L_s)        (M=D, N=D, K=64 tokens)               state-independent
+//   O2 = Q S_c                                   (M=64, N=D, K=D)                       reads the entering state
+//   A  = P * exp(min(L_t - L_s, 0)) [s<=t]       in registers (tcgen05.ld), written back to shared memory
+//   O1 = A V                                     (M=64, N=D, K=64)
+//   o_t = O1_t + exp(L_t) O2_t ;   S_{c+1} = exp(L_C) S_c + U      (fp32, in registers)
+// Only the last line is sequential across chunks, and it is one FMA per state element.
+//
+// Precision. Every fp32 operand that has to re-enter the tensor core (A, K*w, S) is split into a bf16 head and a bf16
+// tail (x = hi + lo to 2^-17) and multiplied as two MMAs into the same accumulator, so the only roundings left are the
+// callers' bf16 q, k, v. The row scaling exp(L_t) of the state read is applied to the fp32 accumulator, not the operand.
+// This is HBM-bound work (64 FLOP/B at D=64), so the second MMA per product is free.
+//
+// Shared-memory operand layouts (all 128-byte swizzled, tiles 1024-byte aligned):
+//   Q, K   [64 tokens][D]  rows of 128 B, K-major operands (K = head dim); D=128 is two 64-column sub-tiles.  From TMA.
+//   V      [64 tokens][D]  the same bytes read as an MN-major B operand (N = value dim contiguous).            From TMA.
+//   KW     like K, rows scaled by w, hi and lo copies: MN-major A operand (M = key dim contiguous).           Threads.
+//   A      [64 t][64 s]    K-major A operand, hi and lo.                                                      Threads.
+//   S      [D key][D value] MN-major B operand (rows = key index = K), hi and lo; D=128: two value sub-tiles. Threads.
+// TMEM (columns): P 64 | U D | O1 D | O2 D.  M=64 accumulators live in lanes 0-15 of each 32-lane subpartition.
+//
+// Every mbarrier wait is bounded; a wait that runs out sets g_tc_error, and the CTA still frees its TMEM and returns.
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace pgb {
 
-bool prefill_tc_supported(int, int, bool) { return false; }
+constexpr int TC_C = 64;
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
 
-int prefill_tc_launch(const PrefillArgs &, int, int, cudaStream_t) { return PGB_ERR_UNSUPPORTED_DIM; }
+__device__ int g_tc_error = 0;
+
+// ---------------------------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: false (and the error flag set) if the barrier never flips
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
+    for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i)
+        if (mbar_try(bar, parity)) return true;
+    atomicExch(&g_tc_error, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 32 lanes x 32 columns of 32-bit: thread i of the warp gets lane (base lane + i), columns col .. col+31
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t *r = reinterpret_cast<uint32_t *>(v);
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------------------------- descriptors
+// Shared-memory matrix descriptor, 128-byte swizzle. lbo / sbo in bytes.
+//   K-major:  sbo = bytes between 8-row groups (1024); lbo unused (set 16).
+//   MN-major: sbo = bytes between 8-row (K) groups (1024); lbo = bytes between 64-element groups along M/N.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3fff);
+    d |= (uint64_t)((lbo >> 4) & 0x3fff) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3fff) << 32;
+    d |= (uint64_t)1 << 46;                       // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor for kind::f16 with bf16 operands and an fp32 accumulator.
+__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int a_mn_major, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// byte offset of the 16-byte chunk (row r, chunk j) in a [rows][128 B] tile with the 128-byte swizzle
+__device__ __forceinline__ uint32_t swz(int r, int j) { return (uint32_t)(r * 128 + ((j ^ (r & 7)) << 4)); }
+
+__device__ __forceinline__ void split_bf16(float x, __nv_bfloat16 &hi, __nv_bfloat16 &lo) {
+    hi = __float2bfloat16_rn(x);
+    lo = __float2bfloat16_rn(x - __bfloat162float(hi));
+}
+// 8 fp32 -> one 16-byte chunk of bf16 heads and one of tails
+__device__ __forceinline__ void split8(const float (&x)[8], uint4 &hi, uint4 &lo) {
+    __nv_bfloat16 h[8], l[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) split_bf16(x[i], h[i], l[i]);
+    hi = *reinterpret_cast<uint4 *>(h);
+    lo = *reinterpret_cast<uint4 *>(l);
+}
+
+struct TcParams {
+    const float *la, *S0, *theta, *shift_dev;
+    float shift_host;
+    void *o; float *S_out; __nv_bfloat16 *sent;
+    int H, T, o_is_f32;
+};
+
+template <int D>
+struct TcSmem {
+    static constexpr int TILE = TC_C * D * 2;                         // one Q / K / V tile, bytes
+    static constexpr int off_q = 0;                                   // [2 stages]
+    static constexpr int off_k = off_q + 2 * TILE;
+    static constexpr int off_v = off_k + 2 * TILE;
+    static constexpr int off_kwh = off_v + 2 * TILE;
+    static constexpr int off_kwl = off_kwh + TILE;
+    static constexpr int off_ah = off_kwl + TILE;                     // [64][64] bf16
+    static constexpr int off_al = off_ah + TC_C * TC_C * 2;
+    static constexpr int off_sh = off_al + TC_C * TC_C * 2;           // [D][D] bf16
+    static constexpr int off_sl = off_sh + D * D * 2;
+    static constexpr int off_misc = off_sl + D * D * 2;               // barriers, tmem base, L / eL / w
+    static constexpr int bytes = off_misc + 1024 + 1024;              // + slack for the 1024-byte alignment
+};
+
+template <int D>
+__global__ void __launch_bounds__(2 * D) prefill_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
+                                                           const __grid_constant__ CUtensorMap mv, TcParams p) {
+    using SM = TcSmem<D>;
+    constexpr int NT = 2 * D;                                         // 128 threads at D=64, 256 at D=128
+    constexpr int NWG = D / 64;
+    constexpr int SUB = D / 64;                                       // 64-column sub-tiles per Q/K/V tile
+    constexpr int PCOLS = 64 / NWG;                                   // score columns a thread handles
+    constexpr uint32_t TM_P = 0, TM_U = 64, TM_O1 = 64 + D, TM_O2 = 64 + 2 * D;
+    constexpr uint32_t TM_COLS = (D == 64) ? 256 : 512;
+    constexpr uint32_t STAGE_BYTES = 3 * SM::TILE;
+    constexpr float LOG2E = 1.4426950408889634f;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *sm = smem_raw + (base - smem_u32(smem_raw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + SM::off_misc);          // full[0], full[1], bar_a, bar_b
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + SM::off_misc + 64);
+    float *Ls = reinterpret_cast<float *>(sm + SM::off_misc + 128);            // L[64]
+    float *eLs = Ls + 64, *wts = eLs + 64;
+    const uint32_t bar_full0 = base + SM::off_misc, bar_full1 = bar_full0 + 8, bar_a = bar_full0 + 16, bar_b = bar_full0 + 24;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, wg = warp >> 2, sub = warp & 3;
+    const int bh = blockIdx.x, h = bh % p.H;
+    const int T = p.T, NC = (T + TC_C - 1) / TC_C;
+    const float *la = p.la + (size_t)bh * T;
+
+    if (tid == 0) {
+        mbar_init(bar_full0, 1); mbar_init(bar_full1, 1); mbar_init(bar_a, 1); mbar_init(bar_b, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) tmem_alloc(smem_u32(tmem_slot), TM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    // ---- who owns which rows
+    // M=64 accumulators (P, O1, O2; U at D=64): row 16*sub + lane, lanes 0-15 only.  M=128 (U at D=128): row 32*sub + lane.
+    const bool tok_active = lane < 16;
+    const int trow = 16 * sub + (lane & 15);                          // token row in the chunk
+    const bool st_active = (D == 128) || tok_active;
+    const int srow = (D == 128) ? 32 * sub + lane : trow;             // key row of the state
+    const int scol0 = 64 * wg;                                        // first value column of this thread's state slice
+    const uint32_t lane_base = (uint32_t)(32 * sub) << 16;
+
+    // ---- entering state: row srow, columns scol0 .. scol0+63, rotated back by shift*theta (rows 2i, 2i+1 pair up)
+    float S[64];
+#pragma unroll
+    for (int j = 0; j < 64; ++j) S[j] = 0.f;
+    if (p.S0 != nullptr) {
+        if (st_active) {
+            const float4 *src = reinterpret_cast<const float4 *>(p.S0 + ((size_t)bh * D + srow) * D + scol0);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { float4 t = src[j]; S[4 * j] = t.x; S[4 * j + 1] = t.y; S[4 * j + 2] = t.z; S[4 * j + 3] = t.w; }
+        }
+        const float shift = p.theta == nullptr ? 0.f : (p.shift_dev != nullptr ? *p.shift_dev : p.shift_host);
+        if (shift != 0.f) {                                           // uniform across the CTA
+            float sn, cs;
+            sincosf(-shift * p.theta[(size_t)h * (D / 2) + (srow >> 1)], &sn, &cs);
+            const bool odd = srow & 1;
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
+                const float other = __shfl_xor_sync(0xffffffffu, S[j], 1);
+                // even row: x0 c - x1 s ; odd row: x0 s + x1 c, with (x0, x1) = (even row, odd row)
+                S[j] = odd ? other * sn + S[j] * cs : S[j] * cs - other * sn;
+            }
+        }
+    }
+
+    bool ok = true;
+    if (tid == 0) {                                                   // first chunk's tiles
+        mbar_expect_tx(bar_full0, STAGE_BYTES);
+#pragma unroll
+        for (int s = 0; s < SUB; ++s) {
+            tma_load_3d(base + SM::off_q + s * 8192, &mq, bar_full0, 64 * s, 0, bh);
+            tma_load_3d(base + SM::off_k + s * 8192, &mk, bar_full0, 64 * s, 0, bh);
+            tma_load_3d(base + SM::off_v + s * 8192, &mv, bar_full0, 64 * s, 0, bh);
+        }
+    }
+
+    for (int c = 0; c < NC && ok; ++c) {
+        const int t0 = c * TC_C, st = c & 1;
+        const uint32_t qs = base + SM::off_q + st * SM::TILE, ks = base + SM::off_k + st * SM::TILE, vs = base + SM::off_v + st * SM::TILE;
+        uint8_t *ks_ptr = sm + SM::off_k + st * SM::TILE;
+        if (tid == 0 && c + 1 < NC) {                                 // next chunk's tiles into the other stage
+            const uint32_t nb = (st ? bar_full0 : bar_full1), o2 = (st ^ 1) * SM::TILE;
+            mbar_expect_tx(nb, STAGE_BYTES);
+#pragma unroll
+            for (int s = 0; s < SUB; ++s) {
+                tma_load_3d(base + SM::off_q + o2 + s * 8192, &mq, nb, 64 * s, t0 + TC_C, bh);
+                tma_load_3d(base + SM::off_k + o2 + s * 8192, &mk, nb, 64 * s, t0 + TC_C, bh);
+                tma_load_3d(base + SM::off_v + o2 + s * 8192, &mv, nb, 64 * s, t0 + TC_C, bh);
+            }
+        }
+        // ---- decay statistics of the chunk (left-to-right cumulative sum, as the reference's cumsum)
+        if (tid < TC_C) {
+            float L = 0.f;
+            for (int r = 0; r <= tid; ++r) L += (t0 + r < T) ? la[t0 + r] : 0.f;
+            Ls[tid] = L;
+            eLs[tid] = expf(L);
+        }
+        __syncthreads();
+        if (tid < TC_C) wts[tid] = (t0 + tid < T) ? expf(fminf(Ls[TC_C - 1] - Ls[tid], 0.f)) : 0.f;
+        const float aC = expf(Ls[TC_C - 1]);
+        // ---- the entering state as an operand (and to HBM if asked for)
+        if (st_active) {
+            uint8_t *sh = sm + SM::off_sh + wg * (D * 128), *sl = sm + SM::off_sl + wg * (D * 128);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float x[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[i] = S[8 * j + i];
+                uint4 hi, lo;
+                split8(x, hi, lo);
+                *reinterpret_cast<uint4 *>(sh + swz(srow, j)) = hi;
+                *reinterpret_cast<uint4 *>(sl + swz(srow, j)) = lo;
+                if (p.sent != nullptr)
+                    *reinterpret_cast<uint4 *>(p.sent + (((size_t)bh * NC + c) * D + srow) * D + scol0 + 8 * j) = hi;
+            }
+        }
+        if (!mbar_wait(st ? bar_full1 : bar_full0, (c >> 1) & 1, 1)) { ok = false; }
+        __syncthreads();                                              // w is visible; K tile has landed for everyone
+        // ---- K * w, hi and lo, in K's own layout
+        if (ok) {
+            for (int idx = tid; idx < TC_C * (D / 8); idx += NT) {
+                const int r = idx / (D / 8), jj = idx % (D / 8);
+                const uint32_t off = (uint32_t)(jj >> 3) * 8192u + swz(r, jj & 7);
+                const uint4 raw = *reinterpret_cast<const uint4 *>(ks_ptr + off);
+                const __nv_bfloat162 *b2 = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+                const float w = wts[r];
+                float x[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(b2[i]); x[2 * i] = f.x * w; x[2 * i + 1] = f.y * w; }
+                uint4 hi, lo;
+                split8(x, hi, lo);
+                *reinterpret_cast<uint4 *>(sm + SM::off_kwh + off) = hi;
+                *reinterpret_cast<uint4 *>(sm + SM::off_kwl + off) = lo;
+            }
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncthreads();
+        // ---- P, U, O2
+        if (tid == 0 && ok) {
+            tc_fence_after();
+            constexpr uint32_t I_P = idesc_bf16(64, 64, 0, 0), I_U = idesc_bf16(D, D, 1, 1), I_O = idesc_bf16(64, D, 0, 1);
+#pragma unroll
+            for (int k = 0; k < D / 16; ++k) {                        // P = Q K^T, K-major steps of 32 B inside a sub-tile
+                const uint32_t ko = (uint32_t)(k >> 2) * 8192u + (uint32_t)(k & 3) * 32u;
+                mma_bf16(tmem + TM_P, smem_desc(qs + ko, 16, 1024), smem_desc(ks + ko, 16, 1024), I_P, k > 0);
+            }
+#pragma unroll
+            for (int k = 0; k < TC_C / 16; ++k) {                     // U = (K w)^T V over the 64 tokens, 16 rows (2048 B) a step
+                const uint32_t ko = (uint32_t)k * 2048u;
+                mma_bf16(tmem + TM_U, smem_desc(base + SM::off_kwh + ko, 8192, 1024), smem_desc(vs + ko, 8192, 1024), I_U, k > 0);
+            }
+#pragma unroll
+            for (int k = 0; k < TC_C / 16; ++k) {
+                const uint32_t ko = (uint32_t)k * 2048u;
+                mma_bf16(tmem + TM_U, smem_desc(base + SM::off_kwl + ko, 8192, 1024), smem_desc(vs + ko, 8192, 1024), I_U, 1);
+            }
+#pragma unroll
+            for (int k = 0; k < D / 16; ++k) {                        // O2 = Q S (hi then lo); S rows are the key index
+                const uint32_t qo = (uint32_t)(k >> 2) * 8192u + (uint32_t)(k & 3) * 32u, so = (uint32_t)k * 2048u;
+                mma_bf16(tmem + TM_O2, smem_desc(qs + qo, 16, 1024), smem_desc(base + SM::off_sh + so, D * 128, 1024), I_O, k > 0);
+            }
+#pragma unroll
+            for (int k = 0; k < D / 16; ++k) {
+                const uint32_t qo = (uint32_t)(k >> 2) * 8192u + (uint32_t)(k & 3) * 32u, so = (uint32_t)k * 2048u;
+                mma_bf16(tmem + TM_O2, smem_desc(qs + qo, 16, 1024), smem_desc(base + SM::off_sl + so, D * 128, 1024), I_O, 1);
+            }
+            mma_commit(bar_a);
+        }
+        if (ok && !mbar_wait(bar_a, c & 1, 2)) ok = false;
+        tc_fence_after();
+        // ---- A = P * decay, causal; hi and lo rows of the K-major A operand
+        if (ok) {
+            float pv[32];
+#pragma unroll
+            for (int half = 0; half < PCOLS / 32; ++half) {
+                const int c0 = wg * PCOLS + 32 * half;
+                tmem_ld32(tmem + lane_base + TM_P + c0, pv);
+                if (tok_active) {
+                    const float Lt = Ls[trow] * LOG2E;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float x[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int s = c0 + 8 * j + i;
+                            const float dec = (s <= trow) ? exp2f(fminf(Lt - Ls[s] * LOG2E, 0.f)) : 0.f;
+                            x[i] = pv[8 * j + i] * dec;
+                        }
+                        uint4 hi, lo;
+                        split8(x, hi, lo);
+                        *reinterpret_cast<uint4 *>(sm + SM::off_ah + swz(trow, (c0 >> 3) + j)) = hi;
+                        *reinterpret_cast<uint4 *>(sm + SM::off_al + swz(trow, (c0 >> 3) + j)) = lo;
+                    }
+                }
+            }
+            // ---- the state leaving the chunk: S <- e^{L_C} S + U
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                tmem_ld32(tmem + lane_base + TM_U + scol0 + 32 * half, pv);
+                if (st_active) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) S[32 * half + j] = fmaf(aC, S[32 * half + j], pv[j]);
+                }
+            }
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncthreads();
+        // ---- O1 = A V
+        if (tid == 0 && ok) {
+            tc_fence_after();
+            constexpr uint32_t I_O = idesc_bf16(64, D, 0, 1);
+#pragma unroll
+            for (int k = 0; k < TC_C / 16; ++k)
+                mma_bf16(tmem + TM_O1, smem_desc(base + SM::off_ah + k * 32, 16, 1024), smem_desc(vs + k * 2048, 8192, 1024), I_O, k > 0);
+#pragma unroll
+            for (int k = 0; k < TC_C / 16; ++k)
+                mma_bf16(tmem + TM_O1, smem_desc(base + SM::off_al + k * 32, 16, 1024), smem_desc(vs + k * 2048, 8192, 1024), I_O, 1);
+            mma_commit(bar_b);
+        }
+        if (ok && !mbar_wait(bar_b, c & 1, 3)) ok = false;
+        tc_fence_after();
+        // ---- o = O1 + e^{L_t} O2, written straight from registers
+        if (ok) {
+            const float eL = eLs[trow];
+            const bool store = tok_active && (t0 + trow < T);
+            float o1[32], o2[32];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int c0 = scol0 + 32 * half;
+                tmem_ld32(tmem + lane_base + TM_O1 + c0, o1);
+                tmem_ld32(tmem + lane_base + TM_O2 + c0, o2);
+                if (store) {
+                    const size_t off = ((size_t)bh * T + t0 + trow) * D + c0;
+                    if (p.o_is_f32) {
+                        float4 *dst = reinterpret_cast<float4 *>((float *)p.o + off);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            dst[j] = make_float4(fmaf(eL, o2[4 * j], o1[4 * j]), fmaf(eL, o2[4 * j + 1], o1[4 * j + 1]),
+                                                 fmaf(eL, o2[4 * j + 2], o1[4 * j + 2]), fmaf(eL, o2[4 * j + 3], o1[4 * j + 3]));
+                    } else {
+                        uint4 *dst = reinterpret_cast<uint4 *>((__nv_bfloat16 *)p.o + off);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            __nv_bfloat162 b[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                b[i] = __floats2bfloat162_rn(fmaf(eL, o2[8 * j + 2 * i], o1[8 * j + 2 * i]),
+                                                             fmaf(eL, o2[8 * j + 2 * i + 1], o1[8 * j + 2 * i + 1]));
+                            dst[j] = *reinterpret_cast<uint4 *>(b);
+                        }
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+        __syncthreads();                                              // every TMEM read of this chunk is done before the next MMAs
+    }
+    // ---- final state
+    if (st_active && ok) {
+        float4 *dst = reinterpret_cast<float4 *>(p.S_out + ((size_t)bh * D + srow) * D + scol0);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) dst[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, TM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// [BH][T][D] bf16, box = 64 columns x 64 tokens x 1, 128-byte swizzle, zero fill past T
+bool make_map(CUtensorMap *m, const void *ptr, int BH, int T, int D) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)T, (cuuint64_t)BH};
+    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)T * D * 2};
+    cuuint32_t box[3] = {64, 64, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int D>
+int tc_go(const PrefillArgs &a, int o_dtype, cudaStream_t stream) {
+    using SM = TcSmem<D>;
+    CUtensorMap mq, mk, mv;
+    const int BH = a.B * a.H;
+    if (!make_map(&mq, a.q, BH, a.T, D) || !make_map(&mk, a.k, BH, a.T, D) || !make_map(&mv, a.v, BH, a.T, D)) {
+        set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
+        return PGB_ERR_CUDA;
+    }
+    auto kern = prefill_tc_kernel<D>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::bytes);
+    if (e != cudaSuccess) { set_cuda_error(e, "prefill_tc smem attribute"); return PGB_ERR_CUDA; }
+    TcParams p{a.la, a.S0, a.theta, a.shift_dev, a.shift_host, a.o, a.S_out, a.sent, a.H, a.T, o_dtype == PGB_F32};
+    kern<<<(unsigned)BH, 2 * D, SM::bytes, stream>>>(mq, mk, mv, p);
+    return check_launch("prefill_tc_kernel");
+}
+
+}  // namespace
+
+// bf16 inputs, plain rule. (The delta rule runs in the fp32 kernel.)
+bool prefill_tc_supported(int io_dtype, int D, bool delta) { return io_dtype == PGB_BF16 && !delta && (D == 64 || D == 128); }
+
+int prefill_tc_launch(const PrefillArgs &a, int o_dtype, int D, cudaStream_t stream) {
+    return D == 64 ? tc_go<64>(a, o_dtype, stream) : tc_go<128>(a, o_dtype, stream);
+}
+
+// Reads and clears the device-side flag a timed-out wait sets (0 = none). Synchronises the device.
+int tc_error_flag(int *out) {
+    int zero = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_tc_error, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
+    if (e != cudaSuccess) { set_cuda_error(e, "tc_error_flag"); return PGB_ERR_CUDA; }
+    return PGB_OK;
+}
 
 }  // namespace pgb

@@ -1,0 +1,99 @@
+"""The tcgen05 / TMEM / TMA chunked-prefill kernel (bf16 inputs, plain rule) against the CPU oracle on the same
+bf16-rounded inputs, and against the fp32 kernel. Tolerances: output 2e-3, carried state 1e-4 (max|d| / max|ref|)."""
+import ctypes
+
+import pytest
+import torch
+
+import oracle
+from oracle import rel_err
+from pragnosia_b200 import ops, synth, _lib
+
+pytestmark = pytest.mark.gpu
+torch.set_grad_enabled(False)
+DEV = "cuda"
+TC = _lib.PREFILL_TENSOR
+
+
+def flag():
+    out = ctypes.c_int(-1)
+    _lib.check(_lib.lib().pgb_tc_error_flag(ctypes.byref(out)), "pgb_tc_error_flag")
+    return out.value
+
+
+def inputs(B, H, T, D, seed, with_state=True):
+    x = synth.assoc_op_inputs(B, H, T, D, seed=seed, with_state=with_state)
+    q = oracle.rotate(x["q"], x["theta"], x["pos"]).to(torch.bfloat16)
+    k = oracle.rotate(x["k"], x["theta"], x["pos"]).to(torch.bfloat16)
+    return q, k, x["v"].to(torch.bfloat16), x["la"], x.get("S0")
+
+
+def run(q, k, v, la, S0, **kw):
+    d = lambda t: None if t is None else t.to(DEV)
+    return ops.prefill(d(q), d(k), d(v), d(la), None, d(S0), precision=TC, **kw)
+
+
+def check(o, S, ro, rS, what):
+    assert torch.isfinite(o).all() and torch.isfinite(S).all(), what
+    eo, es = rel_err(o.float().cpu(), ro), rel_err(S.cpu(), rS)
+    assert eo <= 2e-3 and es <= 1e-4, f"{what}: o {eo:.2e} S {es:.2e}"
+    return eo, es
+
+
+def test_cfg0_shape_bf16_tensor_cores():
+    q, k, v, la, _ = inputs(2, 12, 512, 64, seed=0, with_state=False)
+    ro, rS = oracle.assoc_scan(q.float(), k.float(), v.float(), la, None)
+    o, S, _ = run(q, k, v, la, None, out_dtype=torch.float32)
+    eo, es = check(o, S, ro, rS, "cfg0")
+    assert eo < 2e-4, eo                                     # hi/lo operand splitting: far inside the bf16 budget
+    o16, S16, _ = run(q, k, v, la, None)
+    assert o16.dtype == torch.bfloat16 and torch.equal(o16, o.to(torch.bfloat16)) and torch.equal(S, S16)
+    o2, S2, _ = run(q, k, v, la, None, out_dtype=torch.float32)
+    assert torch.equal(o, o2) and torch.equal(S, S2)         # deterministic
+    assert flag() == 0
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("T", [1, 63, 64, 65, 200, 333, 512])
+def test_lengths_states_and_sent(D, T):
+    q, k, v, la, S0 = inputs(2, 3, T, D, seed=100 + T + D)
+    ro, rS = oracle.assoc_scan(q.float(), k.float(), v.float(), la, S0)
+    o, S, sent = run(q, k, v, la, S0, out_dtype=torch.float32, want_sent=True)
+    check(o, S, ro, rS, f"D{D} T{T}")
+    NC = (T + 63) // 64
+    assert tuple(sent.shape) == (2, 3, NC, D, D)
+    assert torch.equal(sent[:, :, 0].cpu(), S0.to(torch.bfloat16))
+    if NC > 1:
+        _, S64 = oracle.assoc_scan(q[:, :, :64].float(), k[:, :, :64].float(), v[:, :, :64].float(), la[:, :, :64], S0)
+        assert rel_err(sent[:, :, 1].float().cpu(), S64) < 1e-2
+    # against the fp32 kernel on the same inputs
+    of, Sf, _ = ops.prefill(q.to(DEV), k.to(DEV), v.to(DEV), la.to(DEV), None, S0.to(DEV), precision=_lib.PREFILL_FP32,
+                            out_dtype=torch.float32)
+    assert rel_err(o.cpu(), of.cpu()) < 2e-4 and rel_err(S.cpu(), Sf.cpu()) < 1e-4
+    assert flag() == 0
+
+
+def test_rebase_and_windows():
+    q, k, v, la, S0 = inputs(2, 3, 300, 64, seed=7)
+    th = torch.rand(3, 32) * 0.5
+    o, S, _ = run(q, k, v, la, S0, theta=th.to(DEV), shift=41.0, out_dtype=torch.float32)
+    ro, rS = oracle.assoc_scan(q.float(), k.float(), v.float(), la, oracle.decode_rebase(S0, th, 41.0))
+    check(o, S, ro, rS, "rebase")
+    a = run(q[:, :, :130], k[:, :, :130], v[:, :, :130], la[:, :, :130], S0, out_dtype=torch.float32)
+    b = ops.prefill(q[:, :, 130:].to(DEV), k[:, :, 130:].to(DEV), v[:, :, 130:].to(DEV), la[:, :, 130:].to(DEV), None, a[1],
+                    precision=TC, out_dtype=torch.float32)
+    r2, rS2 = oracle.assoc_scan(q.float(), k.float(), v.float(), la, S0)
+    check(torch.cat([a[0], b[0]], 2), b[1], r2, rS2, "two windows")
+    assert flag() == 0
+
+
+def test_extreme_decay_and_many_chains():
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(4, 12, 512, 64, generator=g).to(torch.bfloat16)
+    k = torch.randn(4, 12, 512, 64, generator=g).to(torch.bfloat16)
+    v = torch.randn(4, 12, 512, 64, generator=g).to(torch.bfloat16)
+    la = -torch.rand(4, 12, 512, generator=g) * 40
+    o, S, _ = run(q, k, v, la, None, out_dtype=torch.float32)
+    ro, rS = oracle.assoc_scan(q.float(), k.float(), v.float(), la, None)
+    check(o, S, ro, rS, "extreme decay")
+    assert flag() == 0
