@@ -92,6 +92,36 @@ int pgb_aspin_prefill_fwd(const void *q, const void *k, const void *v, int io_dt
                           float shift_host, void *o, int o_dtype, float *S_out, void *sent, int B, int H, int T,
                           int D, int precision, void *stream);
 
+/* ---------------------------------------------------------------------------------------------------------
+ * The same chunked prefill (plain rule, bf16 operands, tensor cores) with the layer's neighbouring elementwise steps
+ * fused in, so a layer's prefill is: projection GEMM -> prep -> THIS -> output GEMM.
+ * Replaces, in src/assoc.py AssocCarrier.forward: the decay gate (:355-356, :467), the scan (:498-499), the per-head
+ * RMS norm and the (B,H,T,D)->(B,T,H*D) transpose (:505).
+ *   q, k, v [B][H][T][D] bf16 as produced by pgb_aspin_prep_fwd.
+ *   decay_logits: bf16 view (B,T,H) with element strides (decay_stride_b, decay_stride_t), unit over H: the output of
+ *   the decay gate's linear layer; log alpha = -softplus(logit) * exp(decay_A[h]).  decay_A [H] fp32.
+ *   S0, theta, shift_dev, shift_host, S_out, sent: as in pgb_aspin_prefill_fwd.
+ *   rms_weight [D] fp32, rms_eps: o <- o * rsqrt(mean_D(o^2) + eps) * w per (token, head); NULL = no norm.
+ *   o: o_dtype, TOKEN-major [B][T][H][D].     D in {64,128}.
+ * ------------------------------------------------------------------------------------------------------- */
+int pgb_aspin_prefill_fused_fwd(const void *q, const void *k, const void *v, const void *decay_logits,
+                                long long decay_stride_b, long long decay_stride_t, const float *decay_A,
+                                const float *S0, const float *theta, const float *shift_dev, float shift_host,
+                                const float *rms_weight, float rms_eps, void *o, int o_dtype, float *S_out,
+                                void *sent, int B, int H, int T, int D, void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Residual add fused with the norm that follows it:  y = x + delta ;  z = norm(y) * weight (+ bias).
+ * Replaces, across the layer stack, the residual adds of src/assoc.py:511 and src/model.py:560 together with the norms
+ * at src/assoc.py:388, src/model.py:560 (MLP.n) and the final norm (:863).
+ *   x, delta, y, z: [rows][d], dtype (fp32 or bf16), contiguous.  delta may be NULL (norm only; y is then unused).
+ *   y may be NULL (the sum is not kept).  weight, bias: [d], same dtype; bias only for kind 1.
+ *   kind 0: RMS norm (eps inside the square root, as torch.nn.RMSNorm);  kind 1: layer norm.
+ *   d must be a multiple of 8 (bf16) / 4 (fp32) and at most 2048 (bf16) / 1024 (fp32).
+ * ------------------------------------------------------------------------------------------------------- */
+int pgb_add_norm(const void *x, const void *delta, const void *weight, const void *bias, float eps, int kind, void *y,
+                 void *z, long long rows, int d, int dtype, void *stream);
+
 /* Health check of the tensor-core prefill kernel: every wait inside it is bounded, and a wait that runs out sets a
  * device-side flag instead of hanging. This reads the flag into *out_host (0 = no wait ever ran out) and clears it.
  * Unlike every other entry point it SYNCHRONISES the device. No counterpart in the reference. */

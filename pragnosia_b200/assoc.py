@@ -57,6 +57,7 @@ class AssocCarrier(nn.Module):
         self.gate = nn.Parameter(torch.zeros(()))
         self.sent = None
         self._fused = None
+        self._pos = None
 
     def spectral_parameters(self):
         return [self.A, self.theta, self.gate]
@@ -89,45 +90,64 @@ class AssocCarrier(nn.Module):
         """x (B,T,d) on CUDA; h0 = (S (B,H,dk,dk) fp32, p0) from the previous window or step, or None.
         Returns (out (B,T,d), (S, T)): positions restart at every call and the carried state is rotated back by the
         previous call's length instead (the reference's rebase, src/assoc.py:394-405)."""
-        B, T, D = x.shape
+        delta, st = self.mix(self.ln(x), h0)
+        return x + delta, st
+
+    def mix(self, z, h0=None):
+        """The layer without its input norm and residual add: z = ln(x) in, (what is added to x, new state) out. The
+        language model fuses the norm and the add of neighbouring blocks into one kernel and calls this directly."""
+        B, T, D = z.shape
         H, dk = self.h, self.dk
         S0, p0 = (None, 0) if h0 is None else (h0[0], h0[1])
         if h0 is not None and len(h0) == 3:
             raise NotImplementedError("short-convolution state is outside the carrier hot path built here")
         c = self._consts()
-        z = self.ln(x)
         y = F.linear(z, c["W"], c["b"])                               # (B,T,3d+2h[+pad])
         d = self.d
         zero_shift = (not torch.is_tensor(p0)) and p0 == 0
         if T == 1:
             y2 = y.view(B, -1)
             if S0 is None:
-                S0 = torch.zeros(B, H, dk, dk, device=x.device, dtype=torch.float32)
-            o = torch.empty(B, 1, d, device=x.device, dtype=x.dtype)
+                S0 = torch.zeros(B, H, dk, dk, device=z.device, dtype=torch.float32)
+            o = torch.empty(B, 1, d, device=z.device, dtype=z.dtype)
             _, S = ops.decode_step(
                 y2[:, 0:d].unflatten(1, (H, dk)), y2[:, d:2 * d].unflatten(1, (H, dk)), y2[:, 2 * d:3 * d].unflatten(1, (H, dk)),
                 y2[:, 3 * d:3 * d + H], S0, c["theta"], gate=y2[:, 3 * d + H:3 * d + 2 * H], delta=self.delta,
                 gate_is_logit=True, decay_A=c["A"], normalize=True, shift=0.0 if zero_shift else p0,
-                rms_weight=c["onw"], rms_eps=self._rms_eps(x.dtype), out=o.view(B, H, dk),
+                rms_weight=c["onw"], rms_eps=self._rms_eps(z.dtype), out=o.view(B, H, dk),
                 S_out=S0 if self.inplace_state else None)
             self.sent = None
         else:
             qp, kp, vp = (y[..., i * d:(i + 1) * d].unflatten(-1, (H, dk)) for i in range(3))
-            la = (-F.softplus(y[..., 3 * d:3 * d + H].float()) * c["expA"]).transpose(1, 2).contiguous()
             g = y[..., 3 * d + H:3 * d + 2 * H]
-            beta = torch.sigmoid(g.float()).transpose(1, 2).contiguous() if self.delta else None
-            pos = torch.arange(T, device=x.device)
+            pos = self._positions(T, z.device)
+            bf16 = z.dtype == torch.bfloat16
             q, k, v = ops.prep(qp, kp, vp, None if self.delta else g, c["theta"], pos,
-                               out_dtype=torch.bfloat16 if x.dtype == torch.bfloat16 else torch.float32)
-            o, S, sent = ops.prefill(q, k, v, la, beta, S0, theta=c["theta"], shift=0.0 if zero_shift else p0,
-                                     want_sent=self.need_sent)
+                               out_dtype=torch.bfloat16 if bf16 else torch.float32)
+            shift = 0.0 if zero_shift else p0
+            S_out = S0 if (self.inplace_state and S0 is not None) else None
+            if bf16 and not self.delta:
+                # tensor-core kernel with the decay gate, the per-head RMS norm and the transpose fused in
+                o, S, sent = ops.prefill_fused(q, k, v, y[..., 3 * d:3 * d + H], c["A"], S0, theta=c["theta"], shift=shift,
+                                               rms_weight=c["onw"], rms_eps=self._rms_eps(z.dtype), want_sent=self.need_sent,
+                                               S_out=S_out)
+            else:
+                la = (-F.softplus(y[..., 3 * d:3 * d + H].float()) * c["expA"]).transpose(1, 2).contiguous()
+                beta = torch.sigmoid(g.float()).transpose(1, 2).contiguous() if self.delta else None
+                o, S, sent = ops.prefill(q, k, v, la, beta, S0, theta=c["theta"], shift=shift, want_sent=self.need_sent,
+                                         S_out=S_out)
+                o = self.on(o.to(z.dtype)).transpose(1, 2).reshape(B, T, D)
             self.sent = sent
-            o = self.on(o.to(x.dtype)).transpose(1, 2).reshape(B, T, D)
-        out = x + F.linear(o, c["ow"])
+        delta = F.linear(o, c["ow"])
         if torch.is_tensor(p0):
             # a device-side position (graphed decode): with inplace_state the caller owns and updates it
-            return out, (S, p0 if self.inplace_state else p0 * 0 + T)
-        return out, (S, T)
+            return delta, (S, p0 if self.inplace_state else p0 * 0 + T)
+        return delta, (S, T)
+
+    def _positions(self, T, device):
+        if self._pos is None or self._pos.numel() < T or self._pos.device != device:
+            self._pos = torch.arange(max(T, 512), device=device)
+        return self._pos[:T]
 
     def _rms_eps(self, dtype):
         return self.on.eps if self.on.eps is not None else torch.finfo(dtype).eps

@@ -22,6 +22,8 @@ int prefill_tc_launch(const PrefillArgs &, int, int, cudaStream_t);
 bool prefill_tc_supported(int io_dtype, int D, bool delta);
 int decode_launch(const DecodeArgs &, int, int, int, int, cudaStream_t);
 int tc_error_flag(int *out);
+int add_norm_launch(const void *, const void *, const void *, const void *, float, int, void *, void *, long long, int, int,
+                    cudaStream_t);
 int rotate_launch(const void *, int, const float *, const float *, void *, int, int, int, int, cudaStream_t);
 
 // PGB_PREFILL_AUTO sends bf16 plain-rule work to the tensor-core kernel only once this is on
@@ -108,6 +110,39 @@ int pgb_aspin_prefill_fwd(const void *q, const void *k, const void *v, int io_dt
     if (precision == PGB_PREFILL_TENSOR || (precision == PGB_PREFILL_AUTO && tc_ok && kAutoUsesTensor))
         return prefill_tc_launch(a, o_dtype, D, (cudaStream_t)stream);
     return prefill_fp32_launch(a, io_dtype, o_dtype, D, (cudaStream_t)stream);
+}
+
+int pgb_aspin_prefill_fused_fwd(const void *q, const void *k, const void *v, const void *decay_logits,
+                                long long decay_stride_b, long long decay_stride_t, const float *decay_A, const float *S0,
+                                const float *theta, const float *shift_dev, float shift_host, const float *rms_weight,
+                                float rms_eps, void *o, int o_dtype, float *S_out, void *sent, int B, int H, int T, int D,
+                                void *stream) {
+    if (!q || !k || !v || !decay_logits || !decay_A || !o || !S_out) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(o_dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || H <= 0 || T <= 0 || (long long)B * H > 0x7fffffffLL || decay_stride_b < 0 || decay_stride_t < H)
+        return PGB_ERR_BAD_SHAPE;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(o, 16) || !aligned(S_out, 16) ||
+        (S0 && !aligned(S0, 16)) || (sent && !aligned(sent, 16)) || !aligned(decay_logits, 2))
+        return PGB_ERR_MISALIGNED;
+    PrefillArgs a{q, k, v, nullptr, nullptr, S0, o, S_out, (__nv_bfloat16 *)sent, theta, shift_dev, shift_host, B, H, T};
+    a.la_raw = decay_logits; a.la_sb = decay_stride_b; a.la_st = decay_stride_t; a.decay_A = decay_A;
+    a.rms_w = rms_weight; a.rms_eps = rms_eps; a.o_token_major = 1;
+    return prefill_tc_launch(a, o_dtype, D, (cudaStream_t)stream);
+}
+
+int pgb_add_norm(const void *x, const void *delta, const void *weight, const void *bias, float eps, int kind, void *y, void *z,
+                 long long rows, int d, int dtype, void *stream) {
+    if (!x || !weight || !z || (kind == 1 && !bias)) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(dtype)) return PGB_ERR_BAD_DTYPE;
+    if (kind != 0 && kind != 1) return PGB_ERR_BAD_SHAPE;
+    const int n = dtype == PGB_BF16 ? 8 : 4;
+    if (rows <= 0 || d <= 0 || d % n) return PGB_ERR_BAD_SHAPE;
+    if (d > 32 * 8 * n) return PGB_ERR_TOO_LARGE;
+    if (!aligned(x, 16) || !aligned(z, 16) || !aligned(weight, 16) || (delta && !aligned(delta, 16)) || (y && !aligned(y, 16)) ||
+        (bias && !aligned(bias, 16)))
+        return PGB_ERR_MISALIGNED;
+    return add_norm_launch(x, delta, weight, bias, eps, kind, y, z, rows, d, dtype, (cudaStream_t)stream);
 }
 
 int pgb_tc_error_flag(int *out_host) {

@@ -43,6 +43,9 @@ struct PrefillArgs {
     const void *q, *k, *v; const float *la, *beta, *S0; void *o; float *S_out; __nv_bfloat16 *sent;
     const float *theta; const float *shift_dev; float shift_host;      // rebase of S0's key axis (theta NULL: none)
     int B, H, T;
+    // fused layer pieces, tensor-core kernel only (zero / NULL = off)
+    const void *la_raw = nullptr; long long la_sb = 0, la_st = 0; const float *decay_A = nullptr;
+    const float *rms_w = nullptr; float rms_eps = 0.f; int o_token_major = 0;
 };
 struct DecodeArgs {
     const void *qp, *kp, *vp; long long in_sb; int normalize;

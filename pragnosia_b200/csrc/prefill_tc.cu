@@ -121,9 +121,13 @@ __device__ __forceinline__ void split_bf16(float x, __nv_bfloat16 &hi, __nv_bflo
 }
 // 8 fp32 -> one 16-byte chunk of bf16 heads and one of tails
 __device__ __forceinline__ void split8(const float (&x)[8], uint4 &hi, uint4 &lo) {
-    __nv_bfloat16 h[8], l[8];
+    __nv_bfloat162 h[4], l[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) split_bf16(x[i], h[i], l[i]);
+    for (int i = 0; i < 4; ++i) {
+        h[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);         // one packed convert for two heads
+        const float2 hf = __bfloat1622float2(h[i]);
+        l[i] = __floats2bfloat162_rn(x[2 * i] - hf.x, x[2 * i + 1] - hf.y);
+    }
     hi = *reinterpret_cast<uint4 *>(h);
     lo = *reinterpret_cast<uint4 *>(l);
 }
@@ -133,6 +137,10 @@ struct TcParams {
     float shift_host;
     void *o; float *S_out; __nv_bfloat16 *sent;
     int H, T, o_is_f32;
+    // fused layer pieces (all optional): decay gate logits instead of log-decays, per-head RMS norm of the read,
+    // token-major output
+    const __nv_bfloat16 *la_raw; long long la_sb, la_st; const float *decay_A;
+    const float *rms_w; float rms_eps; int o_token_major;
 };
 
 template <int D>
@@ -148,7 +156,7 @@ struct TcSmem {
     static constexpr int off_sh = off_al + TC_C * TC_C * 2;           // [D][D] bf16
     static constexpr int off_sl = off_sh + D * D * 2;
     static constexpr int off_misc = off_sl + D * D * 2;               // barriers, tmem base, L / eL / w
-    static constexpr int bytes = off_misc + 1024 + 1024;              // + slack for the 1024-byte alignment
+    static constexpr int bytes = off_misc + 2048 + 1024;              // + slack for the 1024-byte alignment
 };
 
 template <int D>
@@ -170,7 +178,7 @@ __global__ void __launch_bounds__(2 * D) prefill_tc_kernel(const __grid_constant
     uint64_t *bars = reinterpret_cast<uint64_t *>(sm + SM::off_misc);          // full[0], full[1], bar_a, bar_b
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + SM::off_misc + 64);
     float *Ls = reinterpret_cast<float *>(sm + SM::off_misc + 128);            // L[64]
-    float *eLs = Ls + 64, *wts = eLs + 64;
+    float *eLs = Ls + 64, *wts = eLs + 64, *red = wts + 64, *rmsw = red + 128; // red[2][64], rmsw[D]
     const uint32_t bar_full0 = base + SM::off_misc, bar_full1 = bar_full0 + 8, bar_a = bar_full0 + 16, bar_b = bar_full0 + 24;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, wg = warp >> 2, sub = warp & 3;
@@ -183,6 +191,7 @@ __global__ void __launch_bounds__(2 * D) prefill_tc_kernel(const __grid_constant
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) tmem_alloc(smem_u32(tmem_slot), TM_COLS);
+    if (p.rms_w != nullptr && tid < D) rmsw[tid] = p.rms_w[tid];
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -246,16 +255,30 @@ __global__ void __launch_bounds__(2 * D) prefill_tc_kernel(const __grid_constant
                 tma_load_3d(base + SM::off_v + o2 + s * 8192, &mv, nb, 64 * s, t0 + TC_C, bh);
             }
         }
-        // ---- decay statistics of the chunk (left-to-right cumulative sum, as the reference's cumsum)
-        if (tid < TC_C) {
-            float L = 0.f;
-            for (int r = 0; r <= tid; ++r) L += (t0 + r < T) ? la[t0 + r] : 0.f;
+        // ---- decay statistics of the chunk: warps 0 and 1 each scan their 32 tokens and reduce the other half
+        if (warp < 2) {
+            auto log_decay = [&](int r) -> float {
+                const int t = t0 + r;
+                if (t >= T) return 0.f;                               // padding tokens: alpha = 1
+                if (p.la_raw != nullptr) {                            // -softplus(gate logit) * exp(A_h)   (src/assoc.py:355-356)
+                    const float x = __bfloat162float(p.la_raw[(size_t)(bh / p.H) * p.la_sb + (size_t)t * p.la_st + h]);
+                    return -softplusf_(x) * expf(p.decay_A[h]);
+                }
+                return la[t];
+            };
+            const float own = log_decay(tid), other = log_decay(tid ^ 32);
+            float sc = own;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float n = __shfl_up_sync(0xffffffffu, sc, o);
+                if (lane >= o) sc += n;
+            }
+            const float sum_other = warp_sum(other), sum_own = __shfl_sync(0xffffffffu, sc, 31);
+            const float L = sc + (warp == 1 ? sum_other : 0.f), Ltot = sum_own + sum_other;
             Ls[tid] = L;
             eLs[tid] = expf(L);
+            wts[tid] = (t0 + tid < T) ? expf(fminf(Ltot - L, 0.f)) : 0.f;
         }
-        __syncthreads();
-        if (tid < TC_C) wts[tid] = (t0 + tid < T) ? expf(fminf(Ls[TC_C - 1] - Ls[tid], 0.f)) : 0.f;
-        const float aC = expf(Ls[TC_C - 1]);
         // ---- the entering state as an operand (and to HBM if asked for)
         if (st_active) {
             uint8_t *sh = sm + SM::off_sh + wg * (D * 128), *sl = sm + SM::off_sl + wg * (D * 128);
@@ -273,7 +296,8 @@ __global__ void __launch_bounds__(2 * D) prefill_tc_kernel(const __grid_constant
             }
         }
         if (!mbar_wait(st ? bar_full1 : bar_full0, (c >> 1) & 1, 1)) { ok = false; }
-        __syncthreads();                                              // w is visible; K tile has landed for everyone
+        __syncthreads();                                              // L, e^L, w are visible; K tile has landed for everyone
+        const float aC = expf(Ls[TC_C - 1]);
         // ---- K * w, hi and lo, in K's own layout
         if (ok) {
             for (int idx = tid; idx < TC_C * (D / 8); idx += NT) {
@@ -379,9 +403,29 @@ __global__ void __launch_bounds__(2 * D) prefill_tc_kernel(const __grid_constant
         }
         if (ok && !mbar_wait(bar_b, c & 1, 3)) ok = false;
         tc_fence_after();
-        // ---- o = O1 + e^{L_t} O2, written straight from registers
+        // ---- o = O1 + e^{L_t} O2 [* rsqrt(mean(o^2) + eps) * w], written straight from registers
+        const float eL = eLs[trow];
+        float scale = 1.f;
+        if (p.rms_w != nullptr) {                                     // uniform: first pass over TMEM for the row's mean square
+            float ss = 0.f;
+            if (ok) {
+                float o1[32], o2[32];
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    tmem_ld32(tmem + lane_base + TM_O1 + scol0 + 32 * half, o1);
+                    tmem_ld32(tmem + lane_base + TM_O2 + scol0 + 32 * half, o2);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) { const float x = fmaf(eL, o2[j], o1[j]); ss = fmaf(x, x, ss); }
+                }
+            }
+            if constexpr (D == 128) {                                 // a row is split over the two warpgroups
+                if (tok_active) red[wg * 64 + trow] = ss;
+                __syncthreads();
+                ss = red[trow] + red[64 + trow];
+            }
+            scale = rsqrtf(ss * (1.0f / D) + p.rms_eps);
+        }
         if (ok) {
-            const float eL = eLs[trow];
             const bool store = tok_active && (t0 + trow < T);
             float o1[32], o2[32];
 #pragma unroll
@@ -390,22 +434,24 @@ __global__ void __launch_bounds__(2 * D) prefill_tc_kernel(const __grid_constant
                 tmem_ld32(tmem + lane_base + TM_O1 + c0, o1);
                 tmem_ld32(tmem + lane_base + TM_O2 + c0, o2);
                 if (store) {
-                    const size_t off = ((size_t)bh * T + t0 + trow) * D + c0;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        o1[j] = fmaf(eL, o2[j], o1[j]) * scale;
+                        if (p.rms_w != nullptr) o1[j] *= rmsw[c0 + j];
+                    }
+                    const size_t row = p.o_token_major ? ((size_t)(bh / p.H) * T + t0 + trow) * p.H + h : (size_t)bh * T + t0 + trow;
+                    const size_t off = row * D + c0;
                     if (p.o_is_f32) {
                         float4 *dst = reinterpret_cast<float4 *>((float *)p.o + off);
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            dst[j] = make_float4(fmaf(eL, o2[4 * j], o1[4 * j]), fmaf(eL, o2[4 * j + 1], o1[4 * j + 1]),
-                                                 fmaf(eL, o2[4 * j + 2], o1[4 * j + 2]), fmaf(eL, o2[4 * j + 3], o1[4 * j + 3]));
+                        for (int j = 0; j < 8; ++j) dst[j] = make_float4(o1[4 * j], o1[4 * j + 1], o1[4 * j + 2], o1[4 * j + 3]);
                     } else {
                         uint4 *dst = reinterpret_cast<uint4 *>((__nv_bfloat16 *)p.o + off);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             __nv_bfloat162 b[4];
 #pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                b[i] = __floats2bfloat162_rn(fmaf(eL, o2[8 * j + 2 * i], o1[8 * j + 2 * i]),
-                                                             fmaf(eL, o2[8 * j + 2 * i + 1], o1[8 * j + 2 * i + 1]));
+                            for (int i = 0; i < 4; ++i) b[i] = __floats2bfloat162_rn(o1[8 * j + 2 * i], o1[8 * j + 2 * i + 1]);
                             dst[j] = *reinterpret_cast<uint4 *>(b);
                         }
                     }
@@ -470,7 +516,8 @@ int tc_go(const PrefillArgs &a, int o_dtype, cudaStream_t stream) {
     auto kern = prefill_tc_kernel<D>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::bytes);
     if (e != cudaSuccess) { set_cuda_error(e, "prefill_tc smem attribute"); return PGB_ERR_CUDA; }
-    TcParams p{a.la, a.S0, a.theta, a.shift_dev, a.shift_host, a.o, a.S_out, a.sent, a.H, a.T, o_dtype == PGB_F32};
+    TcParams p{a.la, a.S0, a.theta, a.shift_dev, a.shift_host, a.o, a.S_out, a.sent, a.H, a.T, o_dtype == PGB_F32,
+               (const __nv_bfloat16 *)a.la_raw, a.la_sb, a.la_st, a.decay_A, a.rms_w, a.rms_eps, a.o_token_major};
     kern<<<(unsigned)BH, 2 * D, SM::bytes, stream>>>(mq, mk, mv, p);
     return check_launch("prefill_tc_kernel");
 }

@@ -38,7 +38,7 @@ class Decoder:
         h = None; n = 0
         for s in range(0, ids.shape[1], w):
             xw = ids[:, s:s + w]; n = xw.shape[1]
-            h = m._layers(m._embed(xw), states)
+            h = m._add_norm(*m._layers(m._embed(xw), states), m.n)[1]
         pw = n % w
         new = []
         for st in states:                                   # own, contiguous copies the graph can update in place
@@ -51,25 +51,27 @@ class Decoder:
                     if torch.is_tensor(a): a.copy_(b)
         self.pos.fill_(pw)
         self.shift.fill_(float(n))                           # the last window's length (src/assoc.py:512 returns p0 + T)
-        return F.linear(m.n(h[:, -1:]), m.e.weight)[:, -1].float()
+        return F.linear(h[:, -1:], m.e.weight)[:, -1].float()
 
     # ---- one token
     def _step(self):
         m = self.m
-        h = m.e(self.tok) + m.p(self.pos)
+        x, delta = m.e(self.tok) + m.p(self.pos), None
         for i, (mx, mp) in enumerate(zip(m.mix, m.mlp)):
             st = self.states[i]
+            x, z = m._add_norm(x, delta, mx.ln)
             if isinstance(mx, AssocCarrier):
                 mx.inplace_state = True
-                h, _ = mx(h, (st[0], self.shift))
+                delta, _ = mx.mix(z, (st[0], self.shift))
                 mx.inplace_state = False
             else:
-                h, new = mx(h, st)
+                delta, new = mx.mix(z, st)
                 for a, b in zip(st, new): a.copy_(b)
-            h = mp(h)
+            x, z = m._add_norm(x, delta, mp.n)
+            delta = mp.ff(z)
         self.shift.fill_(1.0)
         self.pos.copy_((self.pos + 1) % self.w)
-        return F.linear(m.n(h), m.e.weight)[:, -1].float()
+        return F.linear(m._add_norm(x, delta, m.n)[1], m.e.weight)[:, -1].float()
 
     @torch.no_grad()
     def step(self, tok: torch.Tensor):

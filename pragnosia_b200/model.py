@@ -7,6 +7,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from . import ops
 from .assoc import AssocCarrier
 from .spin import SpinCarrier
 
@@ -21,7 +22,11 @@ class MLP(nn.Module):
         self.b = nn.Linear(mult * d, d)
 
     def forward(self, x):
-        return x + self.b(F.gelu(self.a(self.n(x))))
+        return x + self.ff(self.n(x))
+
+    def ff(self, z):
+        """The block without its norm and residual add."""
+        return self.b(F.gelu(self.a(z)))
 
 
 _MIXERS = {
@@ -42,6 +47,8 @@ class LM(nn.Module):
         self.mix = nn.ModuleList([_MIXERS[mixer](d) for _ in range(layers)])
         self.mlp = nn.ModuleList([MLP(d, mlp_mult) for _ in range(layers)])
         self.n = nn.LayerNorm(d)
+        self.use_graphs = True          # CUDA: replay one captured graph per window in forward_carried
+        self._graphs = {}
         if norm == "rms":                      # every residual-stream LayerNorm becomes an RMSNorm of the same width
             for mod in list(self.modules()):
                 for nm, child in list(mod.named_children()):
@@ -59,16 +66,32 @@ class LM(nn.Module):
     def _embed(self, x):
         return self.e(x) + self.p(torch.arange(x.shape[1], device=x.device) % self.p.num_embeddings)
 
+    @staticmethod
+    def _add_norm(x, delta, norm):
+        """y = x + delta, z = norm(y) in one kernel where the row length allows it; else the two torch ops."""
+        d = x.shape[-1]
+        lim = (2048, 8) if x.dtype == torch.bfloat16 else (1024, 4)
+        if x.dtype in (torch.bfloat16, torch.float32) and d <= lim[0] and d % lim[1] == 0 and not torch.is_grad_enabled():
+            return ops.add_norm(x, delta, norm)
+        y = x if delta is None else x + delta
+        return y, norm(y)
+
     def _layers(self, h, states):
+        """Every (mixer, MLP) pair over h. Returns (x, delta): the residual stream and the last block's not-yet-added
+        output, so the caller's final norm fuses that add as well. Each block's input norm is fused with the previous
+        block's residual add."""
+        x, delta = h, None
         for i, (mx, mp) in enumerate(zip(self.mix, self.mlp)):
-            h, states[i] = mx(h, states[i])
-            h = mp(h)
-        return h
+            x, z = self._add_norm(x, delta, mx.ln)
+            delta, states[i] = mx.mix(z, states[i])
+            x, z = self._add_norm(x, delta, mp.n)
+            delta = mp.ff(z)
+        return x, delta
 
     def trunk(self, x, states=None, carry=False):
         """Everything but the output head; with carry=True also takes / returns the per-layer states."""
         new = list(states) if states is not None else [None] * self.layers
-        h = self.n(self._layers(self._embed(x), new))
+        h = self._add_norm(*self._layers(self._embed(x), new), self.n)[1]
         return (h, new) if carry else h
 
     def forward(self, x, return_hidden=False):
@@ -80,11 +103,79 @@ class LM(nn.Module):
     def forward_carried(self, x, window=None, return_states=False):
         """A sequence longer than ctx, window by window with the carrier state carried; logits of the FINAL window only
         (src/model.py:843-864). The head runs once, on the last window (the reference computes and discards it for every
-        window)."""
+        window). On CUDA, with use_graphs set and whole windows, each window pass is one CUDA-graph replay."""
         window = window or self.ctx
-        states = [None] * self.layers
-        h = None
-        for s in range(0, x.shape[1], window):
-            h = self._layers(self._embed(x[:, s:s + window]), states)
-        logits = F.linear(self.n(h), self.e.weight)
+        B, T = x.shape
+        if self.use_graphs and x.is_cuda and T % window == 0 and T >= window:
+            key = (B, window, x.device, self.e.weight.dtype)
+            run = self._graphs.get(key)
+            if run is None:
+                run = self._graphs[key] = _WindowGraphs(self, B, window, x.device)
+            last = None
+            for s in range(0, T, window):
+                last = run(x[:, s:s + window], first=(s == 0))
+            states = run.states
+        else:
+            states = [None] * self.layers
+            last = None
+            for s in range(0, T, window):
+                last = self._layers(self._embed(x[:, s:s + window]), states)
+        logits = F.linear(self._add_norm(*last, self.n)[1], self.e.weight)
         return (logits, states) if return_states else logits
+
+
+class _WindowGraphs:
+    """Two CUDA graphs of one window pass (embedding and every layer over a static (B,Tw) block of ids): one for a
+    sequence's first window (no entering state) and one for every later window, which updates the per-layer state
+    buffers in place. The reference runs this loop eagerly (src/model.py:857-863); at small batch it is launch-bound."""
+
+    def __init__(self, model, B, Tw, device):
+        self.m, self.B, self.Tw = model, B, Tw
+        self.ids = torch.zeros(B, Tw, dtype=torch.long, device=device)
+        self.states = None
+        self.first = self.later = None
+        self.out_first = self.out_later = None
+
+    def _pass(self, states, inplace):
+        m = self.m
+        for mx in m.mix:
+            if isinstance(mx, AssocCarrier):
+                mx.inplace_state = inplace
+        try:
+            new = list(states)
+            out = m._layers(m._embed(self.ids), new)
+            if inplace:                        # states that came back as new tensors (the diagonal carrier) are copied home
+                for old, cur in zip(states, new):
+                    for a, b in zip(old, cur):
+                        if torch.is_tensor(a) and a.data_ptr() != b.data_ptr():
+                            a.copy_(b)
+            return out, new
+        finally:
+            for mx in m.mix:
+                if isinstance(mx, AssocCarrier):
+                    mx.inplace_state = False
+
+    def _capture(self):
+        none = [None] * self.m.layers
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):                                  # warm-up: library workspaces, cached constants
+            _, st = self._pass(none, False)
+            self._pass(st, True)
+        torch.cuda.current_stream().wait_stream(side)
+        self.first = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.first):
+            self.out_first, self.states = self._pass(none, False)
+        self.later = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.later, pool=self.first.pool()):
+            self.out_later, _ = self._pass(self.states, True)
+
+    def __call__(self, ids, first):
+        if self.first is None:
+            self._capture()
+        self.ids.copy_(ids)
+        if first:
+            self.first.replay()
+            return self.out_first
+        self.later.replay()
+        return self.out_later

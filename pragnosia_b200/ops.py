@@ -19,6 +19,16 @@ def _f32c(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     return None if t is None else t.to(torch.float32).contiguous()
 
 
+def _state_out(S_out, B, H, D, device):
+    """The tensor the final state is written to: a new one, or the caller's (which may be the S0 it passed: every
+    (sequence, head) reads its entering state before it writes its final one)."""
+    if S_out is None:
+        return torch.empty(B, H, D, D, device=device, dtype=torch.float32)
+    if S_out.dtype != torch.float32 or not S_out.is_contiguous() or tuple(S_out.shape) != (B, H, D, D):
+        raise ValueError("S_out must be a contiguous fp32 (B,H,D,D) tensor")
+    return S_out
+
+
 # ----------------------------------------------------------------------------------------------------------
 def lambda_scan(u: torch.Tensor, logmag: torch.Tensor, ang: torch.Tensor, h0=None, time_segments: int = 0):
     """h_t = lambda_t h_{t-1} + u_t with lambda_t = exp(logmag_t + i ang_t); returns (Re h (B,T,D) fp32,
@@ -85,7 +95,7 @@ def prep(qp, kp, vp, gate_logits, theta, pos, out_dtype=torch.bfloat16):
 
 # ----------------------------------------------------------------------------------------------------------
 def prefill(q, k, v, la, beta=None, S0=None, theta=None, shift=0.0, want_sent: bool = False,
-            precision: int = _lib.PREFILL_AUTO, out_dtype=None):
+            precision: int = _lib.PREFILL_AUTO, out_dtype=None, S_out=None):
     """Chunked prefill. q,k,v (B,H,T,D) fp32 or bf16 (same dtype); la (B,H,T); beta (B,H,T) or None (plain rule);
     S0 (B,H,D,D) or None.  theta/shift: rebase S0's key axis by -shift*theta first (shift: number or 0-d CUDA tensor).
     Returns (o in out_dtype (default q's dtype), S fp32, sent bf16 (B,H,NC,D,D) or None)."""
@@ -108,12 +118,48 @@ def prefill(q, k, v, la, beta=None, S0=None, theta=None, shift=0.0, want_sent: b
     else:
         theta = None
     o = torch.empty(B, H, T, D, device=q.device, dtype=out_dtype or q.dtype)
-    S = torch.empty(B, H, D, D, device=q.device, dtype=torch.float32)
+    S = _state_out(S_out, B, H, D, q.device)
     NC = (T + CHUNK - 1) // CHUNK
     sent = torch.empty(B, H, NC, D, D, device=q.device, dtype=torch.bfloat16) if want_sent else None
     check(lib().pgb_aspin_prefill_fwd(ptr(q), ptr(k), ptr(v), dtype_code(q), ptr(la), ptr(beta), ptr(S0), ptr(theta),
                                       ptr(shift_dev), shift_host, ptr(o), dtype_code(o), ptr(S), ptr(sent), B, H, T, D, precision,
                                       stream_of(q)), "pgb_aspin_prefill_fwd")
+    return o, S, sent
+
+
+# ----------------------------------------------------------------------------------------------------------
+def prefill_fused(q, k, v, decay_logits, decay_A, S0=None, theta=None, shift=0.0, rms_weight=None, rms_eps=0.0,
+                  want_sent: bool = False, out_dtype=None, S_out=None):
+    """Plain-rule prefill on the tensor cores with the decay gate, the per-head RMS norm and the transpose fused in.
+    q,k,v (B,H,T,D) bf16 from prep(); decay_logits: bf16 (B,T,H) view with unit stride over H (the decay gate's linear
+    output); decay_A (H,) fp32.  Returns (o (B,T,H*D) token-major, S fp32, sent or None)."""
+    need_cuda(q, k, v, decay_logits)
+    B, H, T, D = q.shape
+    if q.dtype != torch.bfloat16 or decay_logits.dtype != torch.bfloat16:
+        raise TypeError("prefill_fused takes bf16 operands")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    if decay_logits.stride(2) != 1:
+        decay_logits = decay_logits.contiguous()
+    S0 = _f32c(S0)
+    shift_dev, shift_host = None, 0.0
+    if theta is not None and S0 is not None:
+        theta = _f32c(theta)
+        if torch.is_tensor(shift):
+            shift_dev = shift.to(torch.float32).reshape(())
+        else:
+            shift_host = float(shift)
+            if shift_host == 0.0:
+                theta = None
+    else:
+        theta = None
+    o = torch.empty(B, T, H * D, device=q.device, dtype=out_dtype or q.dtype)
+    S = _state_out(S_out, B, H, D, q.device)
+    NC = (T + CHUNK - 1) // CHUNK
+    sent = torch.empty(B, H, NC, D, D, device=q.device, dtype=torch.bfloat16) if want_sent else None
+    check(lib().pgb_aspin_prefill_fused_fwd(
+        ptr(q), ptr(k), ptr(v), ptr(decay_logits), decay_logits.stride(0), decay_logits.stride(1), ptr(_f32c(decay_A)),
+        ptr(S0), ptr(theta), ptr(shift_dev), shift_host, ptr(_f32c(rms_weight)), float(rms_eps), ptr(o), dtype_code(o),
+        ptr(S), ptr(sent), B, H, T, D, stream_of(q)), "pgb_aspin_prefill_fused_fwd")
     return o, S, sent
 
 
@@ -161,3 +207,23 @@ def decode_step(qp, kp, vp, decay, S, theta, *, gate=None, delta: bool = False, 
         ptr(shift_dev), shift_host, ptr(S), ptr(S_out), ptr(_f32c(rms_weight)), float(rms_eps), ptr(out), dtype_code(out),
         sb(out), B, H, D, stream_of(qp)), "pgb_aspin_decode_step")
     return out, S_out
+
+
+# ----------------------------------------------------------------------------------------------------------
+def add_norm(x, delta, norm: torch.nn.Module):
+    """y = x + delta (delta may be None); z = norm(y) with norm an nn.RMSNorm or nn.LayerNorm over the last dim.
+    Returns (y, z); y is x itself when delta is None."""
+    need_cuda(x)
+    d = x.shape[-1]
+    x = x.contiguous()
+    if delta is not None:
+        delta = delta.to(x.dtype).contiguous()
+    rms = isinstance(norm, torch.nn.RMSNorm)
+    w = norm.weight.to(x.dtype)
+    b = None if rms else norm.bias.to(x.dtype)
+    eps = (norm.eps if norm.eps is not None else torch.finfo(x.dtype).eps) if rms else norm.eps
+    y = torch.empty_like(x) if delta is not None else None
+    z = torch.empty_like(x)
+    check(lib().pgb_add_norm(ptr(x), ptr(delta), ptr(w), ptr(b), float(eps), 0 if rms else 1, ptr(y), ptr(z),
+                             x.numel() // d, d, dtype_code(x), stream_of(x)), "pgb_add_norm")
+    return (x if delta is None else y), z

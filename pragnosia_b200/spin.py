@@ -40,10 +40,14 @@ class SpinCarrier(nn.Module):
         return scan_cuda(u, logmag, ang, h0)
 
     def forward(self, x, h0=None):
-        z = self.ln(x)
+        delta, h = self.mix(self.ln(x), h0)
+        return x + delta, h
+
+    def mix(self, z, h0=None):
+        """The layer without its input norm and residual add (see AssocCarrier.mix)."""
         nu = (self.NU_MIN + F.softplus(self.nu_raw.float()))
         logmag = -self.gate_c * torch.sigmoid(self.Wr(z).float()) * nu
         gam = torch.sqrt((1.0 - torch.exp(2.0 * logmag)).clamp_min(1e-6))
         u = self.B(z).float() * gam * torch.sigmoid(self.Wi(z).float())
         y, h = scan_cuda(u, logmag, self.theta.float().expand_as(logmag), h0)
-        return x + torch.sigmoid(self.gate) * self.C(y.to(x.dtype)), h
+        return torch.sigmoid(self.gate) * self.C(y.to(z.dtype)), h

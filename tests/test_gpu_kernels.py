@@ -279,3 +279,49 @@ def test_decode_step_against_oracle(D, delta, B):
     rg, rla = torch.sigmoid(gate.to(torch.bfloat16).float()), la.to(torch.bfloat16).float()
     o_r, S_r = oracle.decode_step(S, 29.0, rq, rk if delta else rk * rg[..., None], rv, rla, th, rg if delta else None)
     close(o3, o_r, 1e-5, "o in-place"); close(Sd, S_r, 1e-5, "S in-place")
+
+
+# ------------------------------------------------------------------------------------------------ fused pieces
+@pytest.mark.parametrize("D", [64, 128])
+def test_prefill_fused_epilogue_and_decay_gate(D):
+    """Decay gate from logits, per-head RMS norm and token-major output fused into the tensor-core prefill."""
+    B, H, T = 2, 3, 200
+    x = synth.assoc_op_inputs(B, H, T, D, seed=31 + D, with_state=True)
+    q, k, v = (t.to(torch.bfloat16) for t in (x["q"], x["k"], x["v"]))
+    g = torch.Generator().manual_seed(5)
+    logits = torch.randn(B, T, H + 3, generator=g).to(torch.bfloat16)           # a view with a padded last dim
+    A = torch.randn(H, generator=g) - 2
+    w = torch.rand(D, generator=g) + 0.5
+    la = (-F.softplus(logits[..., :H].float()) * A.exp()).transpose(1, 2)
+    ro, rS = oracle.assoc_scan(q.float(), k.float(), v.float(), la, x["S0"])
+    eps = 1e-6
+    rn = ro * torch.rsqrt(ro.pow(2).mean(-1, keepdim=True) + eps) * w
+    o, S, _ = ops.prefill_fused(cu(q), cu(k), cu(v), cu(logits)[..., :H], cu(A), cu(x["S0"]), rms_weight=cu(w), rms_eps=eps,
+                                out_dtype=torch.float32)
+    assert tuple(o.shape) == (B, T, H * D)
+    close(o.view(B, T, H, D).transpose(1, 2), rn, 2e-3, "fused o"); close(S, rS, 1e-4, "fused S")
+    o2, S2, _ = ops.prefill_fused(cu(q), cu(k), cu(v), cu(logits)[..., :H], cu(A), cu(x["S0"]), out_dtype=torch.float32)
+    close(o2.view(B, T, H, D).transpose(1, 2), ro, 2e-3, "fused o, no norm")
+    Sd = cu(x["S0"]).clone()
+    _, S3, _ = ops.prefill_fused(cu(q), cu(k), cu(v), cu(logits)[..., :H], cu(A), Sd, S_out=Sd)
+    assert S3.data_ptr() == Sd.data_ptr() and torch.equal(Sd, S)                 # in-place state update
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("d", [64, 768, 1024])
+def test_add_norm(dt, d):
+    g = torch.Generator().manual_seed(d)
+    x = (torch.randn(5, 37, d, generator=g) * 2).to(dt); dl = torch.randn(5, 37, d, generator=g).to(dt)
+    for norm in (torch.nn.RMSNorm(d), torch.nn.LayerNorm(d)):
+        norm.weight.data = torch.rand(d, generator=g) + 0.5
+        if hasattr(norm, "bias") and norm.bias is not None:
+            norm.bias.data = torch.randn(d, generator=g) * 0.1
+        norm = norm.to(dt)
+        y_ref = x + dl
+        z_ref = norm(y_ref)
+        y, z = ops.add_norm(cu(x), cu(dl), norm.to(DEV))
+        assert torch.equal(y.cpu(), y_ref)
+        close(z.float(), z_ref.float(), 1e-2 if dt == torch.bfloat16 else 1e-5, f"z {type(norm).__name__}")
+        y0, z0 = ops.add_norm(cu(x), None, norm)
+        assert y0.data_ptr() == cu(x).data_ptr() or torch.equal(y0.cpu(), x)
+        close(z0.float(), norm.cpu()(x).float(), 1e-2 if dt == torch.bfloat16 else 1e-5, "z without delta")
