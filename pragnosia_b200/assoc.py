@@ -150,4 +150,5 @@ class AssocCarrier(nn.Module):
         return self._pos[:T]
 
     def _rms_eps(self, dtype):
-        return self.on.eps if self.on.eps is not None else torch.finfo(dtype).eps
+        # nn.RMSNorm(eps=None) uses the epsilon of the ARITHMETIC type: fp32's for bf16 / fp16 / fp32 inputs
+        return self.on.eps if self.on.eps is not None else torch.finfo(torch.float32).eps

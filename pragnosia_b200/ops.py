@@ -221,7 +221,8 @@ def add_norm(x, delta, norm: torch.nn.Module):
     rms = isinstance(norm, torch.nn.RMSNorm)
     w = norm.weight.to(x.dtype)
     b = None if rms else norm.bias.to(x.dtype)
-    eps = (norm.eps if norm.eps is not None else torch.finfo(x.dtype).eps) if rms else norm.eps
+    # nn.RMSNorm(eps=None) means the epsilon of the arithmetic type, which is fp32 for every dtype these kernels take
+    eps = (norm.eps if norm.eps is not None else torch.finfo(torch.float32).eps) if rms else norm.eps
     y = torch.empty_like(x) if delta is not None else None
     z = torch.empty_like(x)
     check(lib().pgb_add_norm(ptr(x), ptr(delta), ptr(w), ptr(b), float(eps), 0 if rms else 1, ptr(y), ptr(z),
