@@ -111,6 +111,29 @@ int pgb_aspin_prefill_fused_fwd(const void *q, const void *k, const void *v, con
                                 void *sent, int B, int H, int T, int D, void *stream);
 
 /* ---------------------------------------------------------------------------------------------------------
+ * A layer's whole prefill between its two GEMMs in ONE kernel (plain rule, bf16, tensor cores): the plumbing of
+ * pgb_aspin_prep_fwd is done in shared memory on the tiles the TMA brings in, then pgb_aspin_prefill_fused_fwd.
+ * Replaces src/assoc.py:440-451 (prep_kernel), :355-356/:467 (decay gate), :498-499 (scan), :505 (norm, transpose).
+ *   qp, kp, vp: bf16 views (B,T,H*D) of the projection GEMM's output with element strides (in_stride_b, in_stride_t),
+ *   unit stride inside a row; 16-byte aligned, strides multiples of 8.
+ *   gate_logits (write gate, may be NULL) and decay_logits: bf16 views (B,T,H) with strides (aux_stride_b, aux_stride_t).
+ *   rot_table: [H][rot_T][D/2] pairs (cos, sin) of position * theta from pgb_rot_table_build, rot_T >= T.
+ *   Everything else as in pgb_aspin_prefill_fused_fwd.  o is token-major [B][T][H][D].
+ * ------------------------------------------------------------------------------------------------------- */
+int pgb_aspin_layer_prefill_fwd(const void *qp, const void *kp, const void *vp, long long in_stride_b,
+                                long long in_stride_t, const void *gate_logits, const void *decay_logits,
+                                long long aux_stride_b, long long aux_stride_t, const float *decay_A,
+                                const float *rot_table, int rot_T, const float *S0, const float *theta,
+                                const float *shift_dev, float shift_host, const float *rms_weight, float rms_eps,
+                                void *o, int o_dtype, float *S_out, void *sent, int B, int H, int T, int D,
+                                void *stream);
+
+/* table[h][t][i] = (cos, sin)(t * theta[h][i]), t in [0,T): the rotation phases of one layer (src/assoc.py:34-39 with
+ * positions 0..T-1), built once per layer and reused by every pgb_aspin_layer_prefill_fwd call.
+ *   theta [H][D/2] fp32;  table [H][T][D/2][2] fp32. */
+int pgb_rot_table_build(const float *theta, float *table, int H, int T, int D, void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
  * Residual add fused with the norm that follows it:  y = x + delta ;  z = norm(y) * weight (+ bias).
  * Replaces, across the layer stack, the residual adds of src/assoc.py:511 and src/model.py:560 together with the norms
  * at src/assoc.py:388, src/model.py:560 (MLP.n) and the final norm (:863).

@@ -26,6 +26,9 @@ SIGNATURES = {
     "pgb_aspin_prefill_fwd": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "pgb_aspin_prefill_fused_fwd": [_vp, _vp, _vp, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _f, _vp, _f, _vp, _i, _vp, _vp,
                                     _i, _i, _i, _i, _vp],
+    "pgb_aspin_layer_prefill_fwd": [_vp, _vp, _vp, _ll, _ll, _vp, _vp, _ll, _ll, _vp, _vp, _i, _vp, _vp, _vp, _f, _vp, _f,
+                                    _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp],
+    "pgb_rot_table_build": [_vp, _vp, _i, _i, _i, _vp],
     "pgb_add_norm": [_vp, _vp, _vp, _vp, _f, _i, _vp, _vp, _ll, _i, _i, _vp],
     "pgb_tc_error_flag": [_vp],
     "pgb_rotate_pairs": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp],

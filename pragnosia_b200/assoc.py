@@ -58,6 +58,7 @@ class AssocCarrier(nn.Module):
         self.sent = None
         self._fused = None
         self._pos = None
+        self._rot = None
 
     def spectral_parameters(self):
         return [self.A, self.theta, self.gate]
@@ -120,18 +121,18 @@ class AssocCarrier(nn.Module):
         else:
             qp, kp, vp = (y[..., i * d:(i + 1) * d].unflatten(-1, (H, dk)) for i in range(3))
             g = y[..., 3 * d + H:3 * d + 2 * H]
-            pos = self._positions(T, z.device)
             bf16 = z.dtype == torch.bfloat16
-            q, k, v = ops.prep(qp, kp, vp, None if self.delta else g, c["theta"], pos,
-                               out_dtype=torch.bfloat16 if bf16 else torch.float32)
             shift = 0.0 if zero_shift else p0
             S_out = S0 if (self.inplace_state and S0 is not None) else None
             if bf16 and not self.delta:
-                # tensor-core kernel with the decay gate, the per-head RMS norm and the transpose fused in
-                o, S, sent = ops.prefill_fused(q, k, v, y[..., 3 * d:3 * d + H], c["A"], S0, theta=c["theta"], shift=shift,
-                                               rms_weight=c["onw"], rms_eps=self._rms_eps(z.dtype), want_sent=self.need_sent,
-                                               S_out=S_out)
+                # one kernel between the two GEMMs: plumbing (normalise, gate, rotate) on the TMA tiles, decay gate, scan on
+                # the tensor cores, per-head RMS norm, token-major output
+                o, S, sent = ops.layer_prefill(qp, kp, vp, g, y[..., 3 * d:3 * d + H], c["A"], self._rot_table(T, c), S0,
+                                               theta=c["theta"], shift=shift, rms_weight=c["onw"],
+                                               rms_eps=self._rms_eps(z.dtype), want_sent=self.need_sent, S_out=S_out)
             else:
+                q, k, v = ops.prep(qp, kp, vp, None if self.delta else g, c["theta"], self._positions(T, z.device),
+                                   out_dtype=torch.bfloat16 if bf16 else torch.float32)
                 la = (-F.softplus(y[..., 3 * d:3 * d + H].float()) * c["expA"]).transpose(1, 2).contiguous()
                 beta = torch.sigmoid(g.float()).transpose(1, 2).contiguous() if self.delta else None
                 o, S, sent = ops.prefill(q, k, v, la, beta, S0, theta=c["theta"], shift=shift, want_sent=self.need_sent,
@@ -143,6 +144,13 @@ class AssocCarrier(nn.Module):
             # a device-side position (graphed decode): with inplace_state the caller owns and updates it
             return delta, (S, p0 if self.inplace_state else p0 * 0 + T)
         return delta, (S, T)
+
+    def _rot_table(self, T, c):
+        """(cos, sin) of position * theta for this layer's window positions; rebuilt when theta changes or T grows."""
+        key = c["theta"].data_ptr()
+        if self._rot is None or self._rot[0] != key or self._rot[1].shape[1] < T:
+            self._rot = (key, ops.rot_table(c["theta"], max(T, 64)))
+        return self._rot[1]
 
     def _positions(self, T, device):
         if self._pos is None or self._pos.numel() < T or self._pos.device != device:

@@ -22,6 +22,7 @@ int prefill_tc_launch(const PrefillArgs &, int, int, cudaStream_t);
 bool prefill_tc_supported(int io_dtype, int D, bool delta);
 int decode_launch(const DecodeArgs &, int, int, int, int, cudaStream_t);
 int tc_error_flag(int *out);
+int rot_table_launch(const float *, float *, int, int, int, cudaStream_t);
 int add_norm_launch(const void *, const void *, const void *, const void *, float, int, void *, void *, long long, int, int,
                     cudaStream_t);
 int rotate_launch(const void *, int, const float *, const float *, void *, int, int, int, int, cudaStream_t);
@@ -129,6 +130,35 @@ int pgb_aspin_prefill_fused_fwd(const void *q, const void *k, const void *v, con
     a.la_raw = decay_logits; a.la_sb = decay_stride_b; a.la_st = decay_stride_t; a.decay_A = decay_A;
     a.rms_w = rms_weight; a.rms_eps = rms_eps; a.o_token_major = 1;
     return prefill_tc_launch(a, o_dtype, D, (cudaStream_t)stream);
+}
+
+int pgb_aspin_layer_prefill_fwd(const void *qp, const void *kp, const void *vp, long long in_stride_b, long long in_stride_t,
+                                const void *gate_logits, const void *decay_logits, long long aux_stride_b,
+                                long long aux_stride_t, const float *decay_A, const float *rot_table, int rot_T,
+                                const float *S0, const float *theta, const float *shift_dev, float shift_host,
+                                const float *rms_weight, float rms_eps, void *o, int o_dtype, float *S_out, void *sent,
+                                int B, int H, int T, int D, void *stream) {
+    if (!qp || !kp || !vp || !decay_logits || !decay_A || !rot_table || !o || !S_out) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(o_dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || H <= 0 || T <= 0 || (long long)B * H > 0x7fffffffLL || aux_stride_b < 0 || aux_stride_t < H ||
+        in_stride_t < (long long)H * D || in_stride_b < 0 || rot_T < T)
+        return PGB_ERR_BAD_SHAPE;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    if (!aligned(qp, 16) || !aligned(kp, 16) || !aligned(vp, 16) || in_stride_b % 8 || in_stride_t % 8 || !aligned(o, 16) ||
+        !aligned(S_out, 16) || (S0 && !aligned(S0, 16)) || (sent && !aligned(sent, 16)) || !aligned(rot_table, 16))
+        return PGB_ERR_MISALIGNED;
+    PrefillArgs a{qp, kp, vp, nullptr, nullptr, S0, o, S_out, (__nv_bfloat16 *)sent, theta, shift_dev, shift_host, B, H, T};
+    a.la_raw = decay_logits; a.la_sb = aux_stride_b; a.la_st = aux_stride_t; a.decay_A = decay_A;
+    a.rms_w = rms_weight; a.rms_eps = rms_eps; a.o_token_major = 1;
+    a.raw = 1; a.raw_sb = in_stride_b; a.raw_st = in_stride_t; a.gate_raw = gate_logits; a.rot = rot_table; a.rot_T = rot_T;
+    return prefill_tc_launch(a, o_dtype, D, (cudaStream_t)stream);
+}
+
+int pgb_rot_table_build(const float *theta, float *table, int H, int T, int D, void *stream) {
+    if (!theta || !table) return PGB_ERR_NULL_POINTER;
+    if (H <= 0 || T <= 0 || D <= 0 || (D & 1)) return PGB_ERR_BAD_SHAPE;
+    if (!aligned(table, 16)) return PGB_ERR_MISALIGNED;
+    return rot_table_launch(theta, table, H, T, D, (cudaStream_t)stream);
 }
 
 int pgb_add_norm(const void *x, const void *delta, const void *weight, const void *bias, float eps, int kind, void *y, void *z,

@@ -46,6 +46,9 @@ struct PrefillArgs {
     // fused layer pieces, tensor-core kernel only (zero / NULL = off)
     const void *la_raw = nullptr; long long la_sb = 0, la_st = 0; const float *decay_A = nullptr;
     const float *rms_w = nullptr; float rms_eps = 0.f; int o_token_major = 0;
+    // raw mode: q, k, v are (B,T,H*D) views of the projection output with strides (raw_sb, raw_st); the kernel does the
+    // normalise / gate / rotate itself (gate_raw: write-gate logits with la_raw's strides; rot: table [H][rot_T][D/2])
+    int raw = 0; long long raw_sb = 0, raw_st = 0; const void *gate_raw = nullptr; const float *rot = nullptr; int rot_T = 0;
 };
 struct DecodeArgs {
     const void *qp, *kp, *vp; long long in_sb; int normalize;

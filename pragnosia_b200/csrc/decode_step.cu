@@ -32,6 +32,26 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_step_kernel(DecodeArgs a) 
     const TIN *kp = (const TIN *)a.kp + (size_t)b * a.in_sb + (size_t)h * D;
     const TIN *vp = (const TIN *)a.vp + (size_t)b * a.in_sb + (size_t)h * D;
 
+    // ---- the state slice first: its loads are the long latency, everything below overlaps with them
+    const int cg = tid % NCG, rg = tid / NCG;
+    const int col = cg * 4;
+    const float *Sin = a.S_in + (size_t)blockIdx.x * D * D;
+    float *Sout = a.S_out + (size_t)blockIdx.x * D * D;
+    float4 s0[NPAIR], s1[NPAIR];
+#pragma unroll
+    for (int p = 0; p < NPAIR; ++p) {
+        const int pr = rg + p * NRG;                                 // pair index: rows 2pr, 2pr+1
+        s0[p] = __ldcs(reinterpret_cast<const float4 *>(Sin + (size_t)(2 * pr) * D + col));
+        s1[p] = __ldcs(reinterpret_cast<const float4 *>(Sin + (size_t)(2 * pr + 1) * D + col));
+    }
+    const float shift = a.shift_dev != nullptr ? *a.shift_dev : a.shift_host;
+    float rcs[NPAIR], rsn[NPAIR];                                    // rebase rotation of this thread's row pairs
+#pragma unroll
+    for (int p = 0; p < NPAIR; ++p) {
+        rcs[p] = 1.f; rsn[p] = 0.f;
+        if (shift != 0.f) sincosf(-shift * a.theta[(size_t)h * (D / 2) + rg + p * NRG], &rsn[p], &rcs[p]);
+    }
+
     // ---- vectors: load, normalise (warps 0,1,2 take q,k,v), scalars (warp 3)
     if (warp < 3) {
         const TIN *src = warp == 0 ? qp : (warp == 1 ? kp : vp);
@@ -59,30 +79,13 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_step_kernel(DecodeArgs a) 
     const float g = sc[1];
     // plain rule: the write gate scales k.  delta rule: g is beta.
     const float kscale = DELTA ? 1.f : g;
-    const float shift = a.shift_dev != nullptr ? *a.shift_dev : a.shift_host;
 
-    const int cg = tid % NCG, rg = tid / NCG;
-    const int col = cg * 4;
-    const float *Sin = a.S_in + (size_t)blockIdx.x * D * D;
-    float *Sout = a.S_out + (size_t)blockIdx.x * D * D;
-
-    float4 s0[NPAIR], s1[NPAIR];
-#pragma unroll
-    for (int p = 0; p < NPAIR; ++p) {
-        const int pr = rg + p * NRG;                                 // pair index: rows 2pr, 2pr+1
-        s0[p] = *reinterpret_cast<const float4 *>(Sin + (size_t)(2 * pr) * D + col);
-        s1[p] = *reinterpret_cast<const float4 *>(Sin + (size_t)(2 * pr + 1) * D + col);
-    }
     const float4 vv = *reinterpret_cast<const float4 *>(sv + col);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);                    // delta: sum_r k_r Sd[r][j];  plain: sum_r q_r S'[r][j]
 #pragma unroll
     for (int p = 0; p < NPAIR; ++p) {
         const int pr = rg + p * NRG;
-        float cs = alpha, sn = 0.f;
-        if (shift != 0.f) {
-            sincosf(-shift * a.theta[(size_t)h * (D / 2) + pr], &sn, &cs);
-            cs *= alpha; sn *= alpha;
-        }
+        const float cs = alpha * rcs[p], sn = alpha * rsn[p];
         const float4 x0 = s0[p], x1 = s1[p];
         float4 d0, d1;                                               // alpha * rotated rows
         d0.x = x0.x * cs - x1.x * sn; d1.x = x0.x * sn + x1.x * cs;

@@ -21,7 +21,13 @@
 //   KW     like K, rows scaled by w, hi and lo copies: MN-major A operand (M = key dim contiguous).           Threads.
 //   A      [64 t][64 s]    K-major A operand, hi and lo.                                                      Threads.
 //   S      [D key][D value] MN-major B operand (rows = key index = K), hi and lo; D=128: two value sub-tiles. Threads.
-// TMEM (columns): P 64 | U D | O1 D | O2 D.  M=64 accumulators live in lanes 0-15 of each 32-lane subpartition.
+// TMEM (columns): P 64 | U D | O1 D | O2 D.  M=64 accumulators live in lanes 0-15 of each 32-lane subpartition; they are
+// read with 16x256b loads, so all 32 threads of a warp share those 16 rows (thread: rows l/4 and l/4+8, column pairs).
+// 8 warps: warp%4 picks the subpartition (rows), warp/4 the column half.
+//
+// RAW mode takes the layer's projections as they leave the GEMM ((B,T,H,D) views) and does the plumbing in place in
+// shared memory after the TMA lands: L2-normalise q, k, v, scale k by the write gate, rotate q and k (cos/sin from a
+// per-layer table), so the separate prep pass and its HBM round trip disappear.
 //
 // Every mbarrier wait is bounded; a wait that runs out sets g_tc_error, and the CTA still frees its TMEM and returns.
 #include <cuda.h>
@@ -93,6 +99,34 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// 16 lanes x 256 bits per repetition: thread l of the warp gets, for block j of 8 columns,
+//   v[4j+0], v[4j+1] = lane (base + l/4),     columns 8j + 2(l%4), +1
+//   v[4j+2], v[4j+3] = lane (base + l/4 + 8), same columns
+__device__ __forceinline__ void tmem_ld_frag4(uint32_t taddr, float (&v)[16]) {
+    uint32_t *r = reinterpret_cast<uint32_t *>(v);
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_frag8(uint32_t taddr, float (&v)[32]) {
+    uint32_t *r = reinterpret_cast<uint32_t *>(v);
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+template <int NB>
+__device__ __forceinline__ void tmem_ld_frag(uint32_t taddr, float (&v)[4 * NB]) {
+    if constexpr (NB == 4) tmem_ld_frag4(taddr, v); else tmem_ld_frag8(taddr, v);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor, 128-byte swizzle. lbo / sbo in bytes.
 //   K-major:  sbo = bytes between 8-row groups (1024); lbo unused (set 16).
@@ -132,6 +166,15 @@ __device__ __forceinline__ void split8(const float (&x)[8], uint4 &hi, uint4 &lo
     lo = *reinterpret_cast<uint4 *>(l);
 }
 
+// two fp32 -> packed bf16 heads and packed bf16 tails
+__device__ __forceinline__ void split2(float a, float b, uint32_t &hi, uint32_t &lo) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    const float2 hf = __bfloat1622float2(h);
+    const __nv_bfloat162 l = __floats2bfloat162_rn(a - hf.x, b - hf.y);
+    hi = *reinterpret_cast<const uint32_t *>(&h);
+    lo = *reinterpret_cast<const uint32_t *>(&l);
+}
+
 struct TcParams {
     const float *la, *S0, *theta, *shift_dev;
     float shift_host;
@@ -139,8 +182,10 @@ struct TcParams {
     int H, T, o_is_f32;
     // fused layer pieces (all optional): decay gate logits instead of log-decays, per-head RMS norm of the read,
     // token-major output
-    const __nv_bfloat16 *la_raw; long long la_sb, la_st; const float *decay_A;
+    const __nv_bfloat16 *la_raw; long long aux_sb, aux_st; const float *decay_A;
     const float *rms_w; float rms_eps; int o_token_major;
+    // RAW mode: write-gate logits (same strides as la_raw) and the rotation table [H][rot_T][D/2] of (cos, sin)
+    const __nv_bfloat16 *gate_raw; const float2 *rot; int rot_T;
 };
 
 template <int D>
@@ -155,18 +200,21 @@ struct TcSmem {
     static constexpr int off_al = off_ah + TC_C * TC_C * 2;
     static constexpr int off_sh = off_al + TC_C * TC_C * 2;           // [D][D] bf16
     static constexpr int off_sl = off_sh + D * D * 2;
-    static constexpr int off_misc = off_sl + D * D * 2;               // barriers, tmem base, L / eL / w
+    static constexpr int off_misc = off_sl + D * D * 2;               // barriers, tmem base, L / eL / w, ...
     static constexpr int bytes = off_misc + 2048 + 1024;              // + slack for the 1024-byte alignment
 };
 
-template <int D>
-__global__ void __launch_bounds__(2 * D) prefill_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
+constexpr int TC_NT = 256;
+
+template <int D, bool RAW>
+__global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
                                                            const __grid_constant__ CUtensorMap mv, TcParams p) {
     using SM = TcSmem<D>;
-    constexpr int NT = 2 * D;                                         // 128 threads at D=64, 256 at D=128
-    constexpr int NWG = D / 64;
+    constexpr int NT = TC_NT;
     constexpr int SUB = D / 64;                                       // 64-column sub-tiles per Q/K/V tile
-    constexpr int PCOLS = 64 / NWG;                                   // score columns a thread handles
+    constexpr int HALF = D / 2;                                       // accumulator columns one warp reads (N = D)
+    constexpr int NBO = HALF / 8;                                     // 8-column blocks per thread for O1 / O2 / U
+    constexpr int NSG = D / 64;                                       // 16-row groups of the state per warp
     constexpr uint32_t TM_P = 0, TM_U = 64, TM_O1 = 64 + D, TM_O2 = 64 + 2 * D;
     constexpr uint32_t TM_COLS = (D == 64) ? 256 : 512;
     constexpr uint32_t STAGE_BYTES = 3 * SM::TILE;
@@ -175,16 +223,16 @@ __global__ void __launch_bounds__(2 * D) prefill_tc_kernel(const __grid_constant
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *sm = smem_raw + (base - smem_u32(smem_raw));
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + SM::off_misc);          // full[0], full[1], bar_a, bar_b
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + SM::off_misc + 64);
     float *Ls = reinterpret_cast<float *>(sm + SM::off_misc + 128);            // L[64]
     float *eLs = Ls + 64, *wts = eLs + 64, *red = wts + 64, *rmsw = red + 128; // red[2][64], rmsw[D]
     const uint32_t bar_full0 = base + SM::off_misc, bar_full1 = bar_full0 + 8, bar_a = bar_full0 + 16, bar_b = bar_full0 + 24;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, wg = warp >> 2, sub = warp & 3;
-    const int bh = blockIdx.x, h = bh % p.H;
+    const int bh = blockIdx.x, h = bh % p.H, b = bh / p.H;
     const int T = p.T, NC = (T + TC_C - 1) / TC_C;
-    const float *la = p.la + (size_t)bh * T;
+    const float *la = p.la != nullptr ? p.la + (size_t)bh * T : nullptr;
+    const int tma_c0 = RAW ? h * D : 0, tma_c2 = RAW ? b : bh;
 
     if (tid == 0) {
         mbar_init(bar_full0, 1); mbar_init(bar_full1, 1); mbar_init(bar_a, 1); mbar_init(bar_b, 1);
@@ -197,37 +245,43 @@ __global__ void __launch_bounds__(2 * D) prefill_tc_kernel(const __grid_constant
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    // ---- who owns which rows
-    // M=64 accumulators (P, O1, O2; U at D=64): row 16*sub + lane, lanes 0-15 only.  M=128 (U at D=128): row 32*sub + lane.
-    const bool tok_active = lane < 16;
-    const int trow = 16 * sub + (lane & 15);                          // token row in the chunk
-    const bool st_active = (D == 128) || tok_active;
-    const int srow = (D == 128) ? 32 * sub + lane : trow;             // key row of the state
-    const int scol0 = 64 * wg;                                        // first value column of this thread's state slice
+    // ---- fragment geometry (16x256b loads): rows l/4 and l/4+8 of the warp's 16-row group, column pairs 2(l%4)
+    const int fr = lane >> 2, fq = lane & 3;
+    const int trow0 = 16 * sub + fr, trow1 = trow0 + 8;               // token rows of the M=64 accumulators
     const uint32_t lane_base = (uint32_t)(32 * sub) << 16;
+    const int pcol0 = 32 * wg;                                        // first score column of this warp
+    const int ocol0 = HALF * wg;                                      // first value column of this warp (O1, O2, U, S)
+    auto state_row = [&](int g, int hi8) { return (D == 128 ? 32 * sub + 16 * g : 16 * sub) + fr + 8 * hi8; };
 
-    // ---- entering state: row srow, columns scol0 .. scol0+63, rotated back by shift*theta (rows 2i, 2i+1 pair up)
-    float S[64];
+    // ---- entering state in fragment order, rotated back by shift*theta (key rows 2i, 2i+1 are lanes l, l^4)
+    float S[NSG][4 * NBO];
 #pragma unroll
-    for (int j = 0; j < 64; ++j) S[j] = 0.f;
+    for (int g = 0; g < NSG; ++g)
+#pragma unroll
+        for (int j = 0; j < 4 * NBO; ++j) S[g][j] = 0.f;
     if (p.S0 != nullptr) {
-        if (st_active) {
-            const float4 *src = reinterpret_cast<const float4 *>(p.S0 + ((size_t)bh * D + srow) * D + scol0);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) { float4 t = src[j]; S[4 * j] = t.x; S[4 * j + 1] = t.y; S[4 * j + 2] = t.z; S[4 * j + 3] = t.w; }
-        }
         const float shift = p.theta == nullptr ? 0.f : (p.shift_dev != nullptr ? *p.shift_dev : p.shift_host);
-        if (shift != 0.f) {                                           // uniform across the CTA
-            float sn, cs;
-            sincosf(-shift * p.theta[(size_t)h * (D / 2) + (srow >> 1)], &sn, &cs);
-            const bool odd = srow & 1;
 #pragma unroll
-            for (int j = 0; j < 64; ++j) {
-                const float other = __shfl_xor_sync(0xffffffffu, S[j], 1);
-                // even row: x0 c - x1 s ; odd row: x0 s + x1 c, with (x0, x1) = (even row, odd row)
-                S[j] = odd ? other * sn + S[j] * cs : S[j] * cs - other * sn;
+        for (int g = 0; g < NSG; ++g)
+#pragma unroll
+            for (int hi8 = 0; hi8 < 2; ++hi8) {
+                const int row = state_row(g, hi8);
+                const float *src = p.S0 + ((size_t)bh * D + row) * D + ocol0 + 2 * fq;
+                float sn = 0.f, cs = 1.f;
+                if (shift != 0.f) sincosf(-shift * p.theta[(size_t)h * (D / 2) + (row >> 1)], &sn, &cs);
+#pragma unroll
+                for (int j = 0; j < NBO; ++j) {
+                    const float2 t = *reinterpret_cast<const float2 *>(src + 8 * j);
+                    float x0 = t.x, x1 = t.y;
+                    if (shift != 0.f) {                               // uniform across the CTA
+                        const float y0 = __shfl_xor_sync(0xffffffffu, x0, 4), y1 = __shfl_xor_sync(0xffffffffu, x1, 4);
+                        // even key row: x c - partner s ; odd key row: partner s + x c
+                        x0 = (row & 1) ? y0 * sn + x0 * cs : x0 * cs - y0 * sn;
+                        x1 = (row & 1) ? y1 * sn + x1 * cs : x1 * cs - y1 * sn;
+                    }
+                    S[g][4 * j + 2 * hi8] = x0; S[g][4 * j + 2 * hi8 + 1] = x1;
+                }
             }
-        }
     }
 
     bool ok = true;
@@ -235,24 +289,24 @@ __global__ void __launch_bounds__(2 * D) prefill_tc_kernel(const __grid_constant
         mbar_expect_tx(bar_full0, STAGE_BYTES);
 #pragma unroll
         for (int s = 0; s < SUB; ++s) {
-            tma_load_3d(base + SM::off_q + s * 8192, &mq, bar_full0, 64 * s, 0, bh);
-            tma_load_3d(base + SM::off_k + s * 8192, &mk, bar_full0, 64 * s, 0, bh);
-            tma_load_3d(base + SM::off_v + s * 8192, &mv, bar_full0, 64 * s, 0, bh);
+            tma_load_3d(base + SM::off_q + s * 8192, &mq, bar_full0, tma_c0 + 64 * s, 0, tma_c2);
+            tma_load_3d(base + SM::off_k + s * 8192, &mk, bar_full0, tma_c0 + 64 * s, 0, tma_c2);
+            tma_load_3d(base + SM::off_v + s * 8192, &mv, bar_full0, tma_c0 + 64 * s, 0, tma_c2);
         }
     }
 
     for (int c = 0; c < NC && ok; ++c) {
         const int t0 = c * TC_C, st = c & 1;
         const uint32_t qs = base + SM::off_q + st * SM::TILE, ks = base + SM::off_k + st * SM::TILE, vs = base + SM::off_v + st * SM::TILE;
-        uint8_t *ks_ptr = sm + SM::off_k + st * SM::TILE;
+        uint8_t *qs_ptr = sm + SM::off_q + st * SM::TILE, *ks_ptr = sm + SM::off_k + st * SM::TILE, *vs_ptr = sm + SM::off_v + st * SM::TILE;
         if (tid == 0 && c + 1 < NC) {                                 // next chunk's tiles into the other stage
             const uint32_t nb = (st ? bar_full0 : bar_full1), o2 = (st ^ 1) * SM::TILE;
             mbar_expect_tx(nb, STAGE_BYTES);
 #pragma unroll
             for (int s = 0; s < SUB; ++s) {
-                tma_load_3d(base + SM::off_q + o2 + s * 8192, &mq, nb, 64 * s, t0 + TC_C, bh);
-                tma_load_3d(base + SM::off_k + o2 + s * 8192, &mk, nb, 64 * s, t0 + TC_C, bh);
-                tma_load_3d(base + SM::off_v + o2 + s * 8192, &mv, nb, 64 * s, t0 + TC_C, bh);
+                tma_load_3d(base + SM::off_q + o2 + s * 8192, &mq, nb, tma_c0 + 64 * s, t0 + TC_C, tma_c2);
+                tma_load_3d(base + SM::off_k + o2 + s * 8192, &mk, nb, tma_c0 + 64 * s, t0 + TC_C, tma_c2);
+                tma_load_3d(base + SM::off_v + o2 + s * 8192, &mv, nb, tma_c0 + 64 * s, t0 + TC_C, tma_c2);
             }
         }
         // ---- decay statistics of the chunk: warps 0 and 1 each scan their 32 tokens and reduce the other half
@@ -261,7 +315,7 @@ __global__ void __launch_bounds__(2 * D) prefill_tc_kernel(const __grid_constant
                 const int t = t0 + r;
                 if (t >= T) return 0.f;                               // padding tokens: alpha = 1
                 if (p.la_raw != nullptr) {                            // -softplus(gate logit) * exp(A_h)   (src/assoc.py:355-356)
-                    const float x = __bfloat162float(p.la_raw[(size_t)(bh / p.H) * p.la_sb + (size_t)t * p.la_st + h]);
+                    const float x = __bfloat162float(p.la_raw[(size_t)b * p.aux_sb + (size_t)t * p.aux_st + h]);
                     return -softplusf_(x) * expf(p.decay_A[h]);
                 }
                 return la[t];
@@ -279,40 +333,110 @@ __global__ void __launch_bounds__(2 * D) prefill_tc_kernel(const __grid_constant
             eLs[tid] = expf(L);
             wts[tid] = (t0 + tid < T) ? expf(fminf(Ltot - L, 0.f)) : 0.f;
         }
-        // ---- the entering state as an operand (and to HBM if asked for)
-        if (st_active) {
-            uint8_t *sh = sm + SM::off_sh + wg * (D * 128), *sl = sm + SM::off_sl + wg * (D * 128);
+        // ---- the entering state as an MN-major B operand, hi and lo (and to HBM if asked for)
+        {
+            uint8_t *sh = sm + SM::off_sh + (D == 128 ? wg * (D * 128) : 0), *sl = sm + SM::off_sl + (D == 128 ? wg * (D * 128) : 0);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float x[8];
+            for (int g = 0; g < NSG; ++g)
 #pragma unroll
-                for (int i = 0; i < 8; ++i) x[i] = S[8 * j + i];
-                uint4 hi, lo;
-                split8(x, hi, lo);
-                *reinterpret_cast<uint4 *>(sh + swz(srow, j)) = hi;
-                *reinterpret_cast<uint4 *>(sl + swz(srow, j)) = lo;
-                if (p.sent != nullptr)
-                    *reinterpret_cast<uint4 *>(p.sent + (((size_t)bh * NC + c) * D + srow) * D + scol0 + 8 * j) = hi;
-            }
+                for (int hi8 = 0; hi8 < 2; ++hi8) {
+                    const int row = state_row(g, hi8);
+#pragma unroll
+                    for (int j = 0; j < NBO; ++j) {
+                        uint32_t hi, lo;
+                        split2(S[g][4 * j + 2 * hi8], S[g][4 * j + 2 * hi8 + 1], hi, lo);
+                        const uint32_t off = swz(row, (D == 128 ? j : 4 * wg + j)) + 4 * fq;
+                        *reinterpret_cast<uint32_t *>(sh + off) = hi;
+                        *reinterpret_cast<uint32_t *>(sl + off) = lo;
+                        if (p.sent != nullptr)
+                            *reinterpret_cast<uint32_t *>(p.sent + (((size_t)bh * NC + c) * D + row) * D + ocol0 + 8 * j + 2 * fq) = hi;
+                    }
+                }
         }
         if (!mbar_wait(st ? bar_full1 : bar_full0, (c >> 1) & 1, 1)) { ok = false; }
-        __syncthreads();                                              // L, e^L, w are visible; K tile has landed for everyone
+        __syncthreads();                                              // L, e^L, w are visible; the tiles have landed for everyone
         const float aC = expf(Ls[TC_C - 1]);
-        // ---- K * w, hi and lo, in K's own layout
         if (ok) {
-            for (int idx = tid; idx < TC_C * (D / 8); idx += NT) {
-                const int r = idx / (D / 8), jj = idx % (D / 8);
-                const uint32_t off = (uint32_t)(jj >> 3) * 8192u + swz(r, jj & 7);
-                const uint4 raw = *reinterpret_cast<const uint4 *>(ks_ptr + off);
-                const __nv_bfloat162 *b2 = reinterpret_cast<const __nv_bfloat162 *>(&raw);
-                const float w = wts[r];
-                float x[8];
+            if constexpr (RAW) {
+                // ---- plumbing in place: 8 lanes share a token row (one 16-byte piece per 64-column sub-tile each)
+                const int cp = lane & 7;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(b2[i]); x[2 * i] = f.x * w; x[2 * i + 1] = f.y * w; }
-                uint4 hi, lo;
-                split8(x, hi, lo);
-                *reinterpret_cast<uint4 *>(sm + SM::off_kwh + off) = hi;
-                *reinterpret_cast<uint4 *>(sm + SM::off_kwl + off) = lo;
+                for (int which = 0; which < 3; ++which) {
+                    uint8_t *tile = which == 0 ? qs_ptr : (which == 1 ? ks_ptr : vs_ptr);
+#pragma unroll
+                    for (int pass = 0; pass < 2; ++pass) {
+                        const int row = 32 * pass + 4 * warp + (lane >> 3);
+                        float x[SUB][8];
+                        float ss = 0.f;
+#pragma unroll
+                        for (int s2 = 0; s2 < SUB; ++s2) {
+                            const uint4 raw = *reinterpret_cast<const uint4 *>(tile + s2 * 8192 + swz(row, cp));
+                            const __nv_bfloat162 *b2 = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float2 f = __bfloat1622float2(b2[i]);
+                                x[s2][2 * i] = f.x; x[s2][2 * i + 1] = f.y;
+                                ss = fmaf(f.x, f.x, fmaf(f.y, f.y, ss));
+                            }
+                        }
+                        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+                        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+                        ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+                        float inv = 1.0f / fmaxf(sqrtf(ss), 1e-12f);
+                        const int t = min(t0 + row, T - 1);
+                        if (which == 1 && p.gate_raw != nullptr)
+                            inv *= sigmoidf_(__bfloat162float(p.gate_raw[(size_t)b * p.aux_sb + (size_t)t * p.aux_st + h]));
+                        const float w = wts[row];
+#pragma unroll
+                        for (int s2 = 0; s2 < SUB; ++s2) {
+                            float y[8];
+                            if (which < 2) {
+                                const float4 *rt = reinterpret_cast<const float4 *>(
+                                    p.rot + ((size_t)h * p.rot_T + min(t, p.rot_T - 1)) * (D / 2) + s2 * 32 + cp * 4);
+                                const float4 r01 = __ldg(rt), r23 = __ldg(rt + 1);     // (c0,s0,c1,s1), (c2,s2,c3,s3)
+                                const float cs[4] = {r01.x, r01.z, r23.x, r23.z}, sn[4] = {r01.y, r01.w, r23.y, r23.w};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    y[2 * i] = (x[s2][2 * i] * cs[i] - x[s2][2 * i + 1] * sn[i]) * inv;
+                                    y[2 * i + 1] = (x[s2][2 * i] * sn[i] + x[s2][2 * i + 1] * cs[i]) * inv;
+                                }
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) y[i] = x[s2][i] * inv;
+                            }
+                            __nv_bfloat162 o2[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
+                            const uint32_t off = s2 * 8192 + swz(row, cp);
+                            *reinterpret_cast<uint4 *>(tile + off) = *reinterpret_cast<uint4 *>(o2);
+                            if (which == 1) {                         // K * w from the ROUNDED k, hi and lo
+                                float kw[8];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(o2[i]); kw[2 * i] = f.x * w; kw[2 * i + 1] = f.y * w; }
+                                uint4 hi, lo;
+                                split8(kw, hi, lo);
+                                *reinterpret_cast<uint4 *>(sm + SM::off_kwh + off) = hi;
+                                *reinterpret_cast<uint4 *>(sm + SM::off_kwl + off) = lo;
+                            }
+                        }
+                    }
+                }
+            } else {
+                // ---- K * w, hi and lo, in K's own layout
+                for (int idx = tid; idx < TC_C * (D / 8); idx += NT) {
+                    const int r = idx / (D / 8), jj = idx % (D / 8);
+                    const uint32_t off = (uint32_t)(jj >> 3) * 8192u + swz(r, jj & 7);
+                    const uint4 raw = *reinterpret_cast<const uint4 *>(ks_ptr + off);
+                    const __nv_bfloat162 *b2 = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+                    const float w = wts[r];
+                    float x[8];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(b2[i]); x[2 * i] = f.x * w; x[2 * i + 1] = f.y * w; }
+                    uint4 hi, lo;
+                    split8(x, hi, lo);
+                    *reinterpret_cast<uint4 *>(sm + SM::off_kwh + off) = hi;
+                    *reinterpret_cast<uint4 *>(sm + SM::off_kwl + off) = lo;
+                }
             }
         }
         fence_proxy_async();
@@ -351,40 +475,36 @@ __global__ void __launch_bounds__(2 * D) prefill_tc_kernel(const __grid_constant
         }
         if (ok && !mbar_wait(bar_a, c & 1, 2)) ok = false;
         tc_fence_after();
-        // ---- A = P * decay, causal; hi and lo rows of the K-major A operand
         if (ok) {
-            float pv[32];
+            // ---- A = P * decay, causal; hi and lo rows of the K-major A operand
+            float pv[16];
+            tmem_ld_frag4(tmem + lane_base + TM_P + pcol0, pv);
+            // ---- and the state leaving the chunk: S <- e^{L_C} S + U
+            float uv[NSG][4 * NBO];
 #pragma unroll
-            for (int half = 0; half < PCOLS / 32; ++half) {
-                const int c0 = wg * PCOLS + 32 * half;
-                tmem_ld32(tmem + lane_base + TM_P + c0, pv);
-                if (tok_active) {
-                    const float Lt = Ls[trow] * LOG2E;
+            for (int g = 0; g < NSG; ++g) tmem_ld_frag<NBO>(tmem + lane_base + ((uint32_t)(16 * g) << 16) + TM_U + ocol0, uv[g]);
+            tmem_ld_wait();
+            const float Lt0 = Ls[trow0] * LOG2E, Lt1 = Ls[trow1] * LOG2E;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        float x[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int s = c0 + 8 * j + i;
-                            const float dec = (s <= trow) ? exp2f(fminf(Lt - Ls[s] * LOG2E, 0.f)) : 0.f;
-                            x[i] = pv[8 * j + i] * dec;
-                        }
-                        uint4 hi, lo;
-                        split8(x, hi, lo);
-                        *reinterpret_cast<uint4 *>(sm + SM::off_ah + swz(trow, (c0 >> 3) + j)) = hi;
-                        *reinterpret_cast<uint4 *>(sm + SM::off_al + swz(trow, (c0 >> 3) + j)) = lo;
-                    }
-                }
+            for (int j = 0; j < 4; ++j) {
+                const int s0 = pcol0 + 8 * j + 2 * fq;
+                const float Ls0 = Ls[s0] * LOG2E, Ls1 = Ls[s0 + 1] * LOG2E;
+                const float a00 = (s0 <= trow0) ? pv[4 * j] * exp2f(fminf(Lt0 - Ls0, 0.f)) : 0.f;
+                const float a01 = (s0 + 1 <= trow0) ? pv[4 * j + 1] * exp2f(fminf(Lt0 - Ls1, 0.f)) : 0.f;
+                const float a10 = (s0 <= trow1) ? pv[4 * j + 2] * exp2f(fminf(Lt1 - Ls0, 0.f)) : 0.f;
+                const float a11 = (s0 + 1 <= trow1) ? pv[4 * j + 3] * exp2f(fminf(Lt1 - Ls1, 0.f)) : 0.f;
+                uint32_t hi, lo;
+                split2(a00, a01, hi, lo);
+                *reinterpret_cast<uint32_t *>(sm + SM::off_ah + swz(trow0, 4 * wg + j) + 4 * fq) = hi;
+                *reinterpret_cast<uint32_t *>(sm + SM::off_al + swz(trow0, 4 * wg + j) + 4 * fq) = lo;
+                split2(a10, a11, hi, lo);
+                *reinterpret_cast<uint32_t *>(sm + SM::off_ah + swz(trow1, 4 * wg + j) + 4 * fq) = hi;
+                *reinterpret_cast<uint32_t *>(sm + SM::off_al + swz(trow1, 4 * wg + j) + 4 * fq) = lo;
             }
-            // ---- the state leaving the chunk: S <- e^{L_C} S + U
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                tmem_ld32(tmem + lane_base + TM_U + scol0 + 32 * half, pv);
-                if (st_active) {
+            for (int g = 0; g < NSG; ++g)
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) S[32 * half + j] = fmaf(aC, S[32 * half + j], pv[j]);
-                }
-            }
+                for (int j = 0; j < 4 * NBO; ++j) S[g][j] = fmaf(aC, S[g][j], uv[g][j]);
         }
         fence_proxy_async();
         tc_fence_before();
@@ -403,57 +523,51 @@ __global__ void __launch_bounds__(2 * D) prefill_tc_kernel(const __grid_constant
         }
         if (ok && !mbar_wait(bar_b, c & 1, 3)) ok = false;
         tc_fence_after();
-        // ---- o = O1 + e^{L_t} O2 [* rsqrt(mean(o^2) + eps) * w], written straight from registers
-        const float eL = eLs[trow];
-        float scale = 1.f;
-        if (p.rms_w != nullptr) {                                     // uniform: first pass over TMEM for the row's mean square
-            float ss = 0.f;
+        // ---- o = O1 + e^{L_t} O2 [* rsqrt(mean(o^2) + eps) * w]
+        float ov[4 * NBO];
+        {
+            float o2v[4 * NBO];
             if (ok) {
-                float o1[32], o2[32];
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    tmem_ld32(tmem + lane_base + TM_O1 + scol0 + 32 * half, o1);
-                    tmem_ld32(tmem + lane_base + TM_O2 + scol0 + 32 * half, o2);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) { const float x = fmaf(eL, o2[j], o1[j]); ss = fmaf(x, x, ss); }
-                }
+                tmem_ld_frag<NBO>(tmem + lane_base + TM_O1 + ocol0, ov);
+                tmem_ld_frag<NBO>(tmem + lane_base + TM_O2 + ocol0, o2v);
+                tmem_ld_wait();
             }
-            if constexpr (D == 128) {                                 // a row is split over the two warpgroups
-                if (tok_active) red[wg * 64 + trow] = ss;
-                __syncthreads();
-                ss = red[trow] + red[64 + trow];
+            const float e0 = eLs[trow0], e1 = eLs[trow1];
+#pragma unroll
+            for (int j = 0; j < NBO; ++j) {
+                ov[4 * j] = fmaf(e0, o2v[4 * j], ov[4 * j]);         ov[4 * j + 1] = fmaf(e0, o2v[4 * j + 1], ov[4 * j + 1]);
+                ov[4 * j + 2] = fmaf(e1, o2v[4 * j + 2], ov[4 * j + 2]); ov[4 * j + 3] = fmaf(e1, o2v[4 * j + 3], ov[4 * j + 3]);
             }
-            scale = rsqrtf(ss * (1.0f / D) + p.rms_eps);
+        }
+        float sc0 = 1.f, sc1 = 1.f;
+        if (p.rms_w != nullptr) {                                     // uniform
+            float ss0 = 0.f, ss1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < NBO; ++j) {
+                ss0 = fmaf(ov[4 * j], ov[4 * j], fmaf(ov[4 * j + 1], ov[4 * j + 1], ss0));
+                ss1 = fmaf(ov[4 * j + 2], ov[4 * j + 2], fmaf(ov[4 * j + 3], ov[4 * j + 3], ss1));
+            }
+            ss0 += __shfl_xor_sync(0xffffffffu, ss0, 1); ss0 += __shfl_xor_sync(0xffffffffu, ss0, 2);
+            ss1 += __shfl_xor_sync(0xffffffffu, ss1, 1); ss1 += __shfl_xor_sync(0xffffffffu, ss1, 2);
+            if (fq == 0) { red[wg * 64 + trow0] = ss0; red[wg * 64 + trow1] = ss1; }
+            __syncthreads();                                          // a row's other half belongs to the other warpgroup
+            sc0 = rsqrtf((red[trow0] + red[64 + trow0]) * (1.0f / D) + p.rms_eps);
+            sc1 = rsqrtf((red[trow1] + red[64 + trow1]) * (1.0f / D) + p.rms_eps);
         }
         if (ok) {
-            const bool store = tok_active && (t0 + trow < T);
-            float o1[32], o2[32];
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const int c0 = scol0 + 32 * half;
-                tmem_ld32(tmem + lane_base + TM_O1 + c0, o1);
-                tmem_ld32(tmem + lane_base + TM_O2 + c0, o2);
-                if (store) {
+            for (int hi8 = 0; hi8 < 2; ++hi8) {
+                const int trow = hi8 ? trow1 : trow0;
+                if (t0 + trow < T) {
+                    const float sc = hi8 ? sc1 : sc0;
+                    const size_t row = p.o_token_major ? ((size_t)b * T + t0 + trow) * p.H + h : (size_t)bh * T + t0 + trow;
+                    const size_t off = row * D + ocol0 + 2 * fq;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        o1[j] = fmaf(eL, o2[j], o1[j]) * scale;
-                        if (p.rms_w != nullptr) o1[j] *= rmsw[c0 + j];
-                    }
-                    const size_t row = p.o_token_major ? ((size_t)(bh / p.H) * T + t0 + trow) * p.H + h : (size_t)bh * T + t0 + trow;
-                    const size_t off = row * D + c0;
-                    if (p.o_is_f32) {
-                        float4 *dst = reinterpret_cast<float4 *>((float *)p.o + off);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) dst[j] = make_float4(o1[4 * j], o1[4 * j + 1], o1[4 * j + 2], o1[4 * j + 3]);
-                    } else {
-                        uint4 *dst = reinterpret_cast<uint4 *>((__nv_bfloat16 *)p.o + off);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            __nv_bfloat162 b[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) b[i] = __floats2bfloat162_rn(o1[8 * j + 2 * i], o1[8 * j + 2 * i + 1]);
-                            dst[j] = *reinterpret_cast<uint4 *>(b);
-                        }
+                    for (int j = 0; j < NBO; ++j) {
+                        float x0 = ov[4 * j + 2 * hi8] * sc, x1 = ov[4 * j + 2 * hi8 + 1] * sc;
+                        if (p.rms_w != nullptr) { x0 *= rmsw[ocol0 + 8 * j + 2 * fq]; x1 *= rmsw[ocol0 + 8 * j + 2 * fq + 1]; }
+                        if (p.o_is_f32) *reinterpret_cast<float2 *>((float *)p.o + off + 8 * j) = make_float2(x0, x1);
+                        else *reinterpret_cast<__nv_bfloat162 *>((__nv_bfloat16 *)p.o + off + 8 * j) = __floats2bfloat162_rn(x0, x1);
                     }
                 }
             }
@@ -462,10 +576,16 @@ __global__ void __launch_bounds__(2 * D) prefill_tc_kernel(const __grid_constant
         __syncthreads();                                              // every TMEM read of this chunk is done before the next MMAs
     }
     // ---- final state
-    if (st_active && ok) {
-        float4 *dst = reinterpret_cast<float4 *>(p.S_out + ((size_t)bh * D + srow) * D + scol0);
+    if (ok) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) dst[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+        for (int g = 0; g < NSG; ++g)
+#pragma unroll
+            for (int hi8 = 0; hi8 < 2; ++hi8) {
+                float *dst = p.S_out + ((size_t)bh * D + state_row(g, hi8)) * D + ocol0 + 2 * fq;
+#pragma unroll
+                for (int j = 0; j < NBO; ++j)
+                    *reinterpret_cast<float2 *>(dst + 8 * j) = make_float2(S[g][4 * j + 2 * hi8], S[g][4 * j + 2 * hi8 + 1]);
+            }
     }
     tc_fence_before();
     __syncthreads();
@@ -491,12 +611,13 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// [BH][T][D] bf16, box = 64 columns x 64 tokens x 1, 128-byte swizzle, zero fill past T
-bool make_map(CUtensorMap *m, const void *ptr, int BH, int T, int D) {
+// bf16 [n2][T][cols] with the given row / slab strides (elements); box = 64 columns x 64 tokens x 1, 128-byte swizzle,
+// zero fill past T
+bool make_map(CUtensorMap *m, const void *ptr, long long n2, int T, long long cols, long long stride_t, long long stride_2) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return false;
-    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)T, (cuuint64_t)BH};
-    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)T * D * 2};
+    cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)T, (cuuint64_t)n2};
+    cuuint64_t strides[2] = {(cuuint64_t)stride_t * 2, (cuuint64_t)stride_2 * 2};
     cuuint32_t box[3] = {64, 64, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr,
@@ -504,21 +625,30 @@ bool make_map(CUtensorMap *m, const void *ptr, int BH, int T, int D) {
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int D>
+template <int D, bool RAW>
 int tc_go(const PrefillArgs &a, int o_dtype, cudaStream_t stream) {
     using SM = TcSmem<D>;
     CUtensorMap mq, mk, mv;
     const int BH = a.B * a.H;
-    if (!make_map(&mq, a.q, BH, a.T, D) || !make_map(&mk, a.k, BH, a.T, D) || !make_map(&mv, a.v, BH, a.T, D)) {
+    bool made;
+    if (RAW)       // (B,T,H*D) views into the projection GEMM's output
+        made = make_map(&mq, a.q, a.B, a.T, (long long)a.H * D, a.raw_st, a.raw_sb) &&
+               make_map(&mk, a.k, a.B, a.T, (long long)a.H * D, a.raw_st, a.raw_sb) &&
+               make_map(&mv, a.v, a.B, a.T, (long long)a.H * D, a.raw_st, a.raw_sb);
+    else           // contiguous (B*H, T, D)
+        made = make_map(&mq, a.q, BH, a.T, D, D, (long long)a.T * D) && make_map(&mk, a.k, BH, a.T, D, D, (long long)a.T * D) &&
+               make_map(&mv, a.v, BH, a.T, D, D, (long long)a.T * D);
+    if (!made) {
         set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
         return PGB_ERR_CUDA;
     }
-    auto kern = prefill_tc_kernel<D>;
+    auto kern = prefill_tc_kernel<D, RAW>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::bytes);
     if (e != cudaSuccess) { set_cuda_error(e, "prefill_tc smem attribute"); return PGB_ERR_CUDA; }
     TcParams p{a.la, a.S0, a.theta, a.shift_dev, a.shift_host, a.o, a.S_out, a.sent, a.H, a.T, o_dtype == PGB_F32,
-               (const __nv_bfloat16 *)a.la_raw, a.la_sb, a.la_st, a.decay_A, a.rms_w, a.rms_eps, a.o_token_major};
-    kern<<<(unsigned)BH, 2 * D, SM::bytes, stream>>>(mq, mk, mv, p);
+               (const __nv_bfloat16 *)a.la_raw, a.la_sb, a.la_st, a.decay_A, a.rms_w, a.rms_eps, a.o_token_major,
+               (const __nv_bfloat16 *)a.gate_raw, (const float2 *)a.rot, a.rot_T};
+    kern<<<(unsigned)BH, TC_NT, SM::bytes, stream>>>(mq, mk, mv, p);
     return check_launch("prefill_tc_kernel");
 }
 
@@ -528,7 +658,24 @@ int tc_go(const PrefillArgs &a, int o_dtype, cudaStream_t stream) {
 bool prefill_tc_supported(int io_dtype, int D, bool delta) { return io_dtype == PGB_BF16 && !delta && (D == 64 || D == 128); }
 
 int prefill_tc_launch(const PrefillArgs &a, int o_dtype, int D, cudaStream_t stream) {
-    return D == 64 ? tc_go<64>(a, o_dtype, stream) : tc_go<128>(a, o_dtype, stream);
+    if (a.raw) return D == 64 ? tc_go<64, true>(a, o_dtype, stream) : tc_go<128, true>(a, o_dtype, stream);
+    return D == 64 ? tc_go<64, false>(a, o_dtype, stream) : tc_go<128, false>(a, o_dtype, stream);
+}
+
+// table[h][t][i] = (cos, sin)(t * theta[h][i]) for t in [0, T): the rotation phases of one layer, built once
+__global__ void rot_table_kernel(const float *__restrict__ theta, float2 *__restrict__ table, int H, int T, int half) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)H * T * half) return;
+    const int pi = (int)(i % half), t = (int)((i / half) % T), h = (int)(i / ((long long)half * T));
+    float sn, cs;
+    sincosf((float)t * theta[(size_t)h * half + pi], &sn, &cs);
+    table[i] = make_float2(cs, sn);
+}
+
+int rot_table_launch(const float *theta, float *table, int H, int T, int D, cudaStream_t stream) {
+    const long long n = (long long)H * T * (D / 2);
+    rot_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(theta, reinterpret_cast<float2 *>(table), H, T, D / 2);
+    return check_launch("rot_table_kernel");
 }
 
 // Reads and clears the device-side flag a timed-out wait sets (0 = none). Synchronises the device.

@@ -1,0 +1,125 @@
+"""Each hand-written kernel alone on a fixed synthetic case: what bench.py times for its roofline entries and what the
+ncu captures summarised under profiles/ run.
+
+    python -m pragnosia_b200.kernel_bench NAME [--launches N] [--time]
+
+NAME is one of CASES. Without --time it just launches the kernel N times (the form to put under ncu); with --time it
+prints the CUDA-event time per launch (L2 flushed before each) and the achieved algorithmic GB/s.
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+
+import torch
+
+from . import _lib, ops, synth
+
+
+def _prefill(B, H, T, D, fused=False):
+    dev = "cuda"
+    x = synth.assoc_op_inputs(B, H, T, D, seed=1, with_state=True)
+    q, k, v = (x[n].to(dev).to(torch.bfloat16) for n in "qkv")
+    la, S0 = x["la"].to(dev), x["S0"].to(dev)
+    alg = B * H * T * (4 * D * 2 + 4) + 2 * B * H * D * D * 4          # q,k,v,o bf16 + log-decay; state in and out
+    return (lambda: ops.prefill(q, k, v, la, None, S0, precision=_lib.PREFILL_TENSOR)), alg
+
+
+def _prefill_delta(B, H, T, D):
+    dev = "cuda"
+    x = synth.assoc_op_inputs(B, H, T, D, seed=1, delta=True, with_state=True)
+    q, k, v = (x[n].to(dev).to(torch.bfloat16) for n in "qkv")
+    la, be, S0 = x["la"].to(dev), x["beta"].to(dev), x["S0"].to(dev)
+    alg = B * H * T * (4 * D * 2 + 8) + 2 * B * H * D * D * 4
+    return (lambda: ops.prefill(q, k, v, la, be, S0)), alg
+
+
+def _prep(B, T, H, D):
+    dev = "cuda"
+    d = H * D
+    proj = torch.randn(B, T, 3 * d + 2 * H, device=dev, dtype=torch.bfloat16)
+    views = [proj[..., i * d:(i + 1) * d].unflatten(-1, (H, D)) for i in range(3)]
+    th, pos = synth.rope_theta(H, D).to(dev), torch.arange(T, device=dev)
+    gate = proj[..., 3 * d + H:3 * d + 2 * H]
+    return (lambda: ops.prep(*views, gate, th, pos)), B * T * H * D * 2 * 6
+
+
+def _decode(B, H, D, delta=False):
+    dev = "cuda"
+    d = H * D
+    S = torch.randn(B, H, D, D, device=dev) * 0.1
+    row = torch.randn(B, 3 * d + 2 * H, device=dev, dtype=torch.bfloat16)
+    vs = [row[:, i * d:(i + 1) * d].unflatten(1, (H, D)) for i in range(3)]
+    A, th = torch.zeros(H, device=dev) - 5, synth.rope_theta(H, D).to(dev)
+    fn = lambda: ops.decode_step(*vs, row[:, 3 * d:3 * d + H], S, th, gate=row[:, 3 * d + H:], decay_A=A, shift=1.0, S_out=S,
+                                 delta=delta)
+    return fn, 2 * B * H * D * D * 4 + B * H * D * 2 * 4               # state read + write, q,k,v in and o out (bf16)
+
+
+def _lambda(B, T, D, bcast=False):
+    dev = "cuda"
+    xs = synth.lambda_scan_inputs(B, T, D, seed=4, per_channel_angle=bcast)
+    u, lm = xs["u"].to(dev), xs["logmag"].to(dev)
+    an = xs["ang"][0, 0].contiguous().to(dev).expand(B, T, D) if bcast else xs["ang"].to(dev)
+    return (lambda: ops.lambda_scan(u, lm, an)), u.numel() * (12 if bcast else 16)
+
+
+def _add_norm(rows, d):
+    dev = "cuda"
+    x = torch.randn(rows, d, device=dev, dtype=torch.bfloat16); dl = torch.randn_like(x)
+    n = torch.nn.RMSNorm(d).to(dev).to(torch.bfloat16)
+    return (lambda: ops.add_norm(x, dl, n)), rows * d * 2 * 4
+
+
+CASES = {
+    # name: (builder, what it is)
+    "prefill": (lambda: _prefill(64, 12, 1024, 64), "aspin chunked prefill, plain rule, tensor cores: B64 H12 T1024 D64 bf16"),
+    "prefill_cfg1": (lambda: _prefill(16, 12, 512, 64), "the same at one configuration-1 window: B16 H12 T512 D64"),
+    "prefill_d128": (lambda: _prefill(8, 16, 2048, 128), "the same at head dim 128: B8 H16 T2048 D128"),
+    "prefill_delta": (lambda: _prefill_delta(8, 16, 1024, 128), "delta-rule chunked prefill: B8 H16 T1024 D128 bf16 I/O"),
+    "prep": (lambda: _prep(16, 512, 12, 64), "normalise / gate / rotate / transpose: B16 T512 H12 D64 bf16"),
+    "decode": (lambda: _decode(64, 12, 64), "fused recurrent decode step, plain rule, in place: B64 H12 D64"),
+    "decode_delta": (lambda: _decode(64, 12, 64, True), "fused recurrent decode step, delta rule, in place: B64 H12 D64"),
+    "lambda": (lambda: _lambda(64, 1024, 768), "per-token lambda scan, per-token angle: B64 T1024 D768 fp32"),
+    "lambda_bcast": (lambda: _lambda(64, 1024, 768, True), "per-token lambda scan, one angle per channel: B64 T1024 D768 fp32"),
+    "add_norm": (lambda: _add_norm(8192, 768), "residual add + RMS norm: 8192 rows of 768 bf16"),
+}
+
+
+def time_case(name: str, iters: int = 20, flush_mb: int = 256):
+    """(microseconds per launch, algorithmic bytes) with the L2 flushed before every timed launch."""
+    fn, alg = CASES[name][0]()
+    flush = torch.empty(flush_mb << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(3):
+        fn()
+    tot = 0.0
+    for _ in range(iters):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fn(); b.record(); b.synchronize()
+        tot += a.elapsed_time(b)
+    return tot / iters * 1e3, alg
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("name", choices=sorted(CASES) + ["all"])
+    ap.add_argument("--launches", type=int, default=2)
+    ap.add_argument("--time", action="store_true")
+    a = ap.parse_args(argv)
+    names = sorted(CASES) if a.name == "all" else [a.name]
+    with torch.no_grad():
+        for n in names:
+            if a.time:
+                us, alg = time_case(n)
+                print(f"{n:14s} {us:9.1f} us/launch  {alg / us / 1e3:8.0f} GB/s algorithmic   ({CASES[n][1]})")
+            else:
+                fn, _ = CASES[n][0]()
+                for _ in range(a.launches):
+                    fn()
+                torch.cuda.synchronize()
+                print(f"{n}: {a.launches} launches done")
+
+
+if __name__ == "__main__":
+    main()

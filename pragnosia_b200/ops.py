@@ -164,6 +164,59 @@ def prefill_fused(q, k, v, decay_logits, decay_A, S0=None, theta=None, shift=0.0
 
 
 # ----------------------------------------------------------------------------------------------------------
+def rot_table(theta, T: int):
+    """(H, T, D/2, 2) fp32 table of (cos, sin)(t * theta[h, i]) for positions 0..T-1."""
+    need_cuda(theta)
+    theta = _f32c(theta)
+    H, half = theta.shape
+    table = torch.empty(H, T, half, 2, device=theta.device, dtype=torch.float32)
+    check(lib().pgb_rot_table_build(ptr(theta), ptr(table), H, T, 2 * half, stream_of(theta)), "pgb_rot_table_build")
+    return table
+
+
+def layer_prefill(qp, kp, vp, gate_logits, decay_logits, decay_A, table, S0=None, theta=None, shift=0.0, rms_weight=None,
+                  rms_eps=0.0, want_sent: bool = False, out_dtype=None, S_out=None):
+    """The layer's prefill between its GEMMs in one kernel. qp,kp,vp: bf16 (B,T,H,D) views of the projection output
+    sharing strides, unit stride over (H,D); gate_logits (or None) / decay_logits: bf16 (B,T,H) views sharing strides;
+    table from rot_table(theta, >= T).  Returns (o (B,T,H*D), S fp32, sent or None)."""
+    need_cuda(qp, kp, vp, decay_logits, table)
+    B, T, H, D = qp.shape
+    for t in (qp, kp, vp):
+        if t.dtype != torch.bfloat16 or t.stride(3) != 1 or t.stride(2) != D or t.stride() != qp.stride():
+            raise ValueError("layer_prefill: q,k,v must be bf16 (B,T,H,D) views with unit strides over (H,D) and common strides")
+    if decay_logits.dtype != torch.bfloat16 or decay_logits.stride(2) != 1:
+        raise ValueError("layer_prefill: decay_logits must be a bf16 (B,T,H) view with unit stride over H")
+    if gate_logits is not None and (gate_logits.dtype != torch.bfloat16 or gate_logits.stride() != decay_logits.stride()):
+        raise ValueError("layer_prefill: gate_logits must share decay_logits' dtype and strides")
+    if table.shape[1] < T:
+        raise ValueError("layer_prefill: rotation table shorter than the window")
+    S0 = _f32c(S0)
+    shift_dev, shift_host = None, 0.0
+    if theta is not None and S0 is not None:
+        theta = _f32c(theta)
+        if torch.is_tensor(shift):
+            shift_dev = shift.to(torch.float32).reshape(())
+        else:
+            shift_host = float(shift)
+            if shift_host == 0.0:
+                theta = None
+    else:
+        theta = None
+    o = torch.empty(B, T, H * D, device=qp.device, dtype=out_dtype or qp.dtype)
+    S = _state_out(S_out, B, H, D, qp.device)
+    NC = (T + CHUNK - 1) // CHUNK
+    sent = torch.empty(B, H, NC, D, D, device=qp.device, dtype=torch.bfloat16) if want_sent else None
+    sbq = qp.stride(0) if B > 1 else T * qp.stride(1)
+    sba = decay_logits.stride(0) if B > 1 else T * decay_logits.stride(1)
+    check(lib().pgb_aspin_layer_prefill_fwd(
+        ptr(qp), ptr(kp), ptr(vp), sbq, qp.stride(1), ptr(gate_logits), ptr(decay_logits), sba, decay_logits.stride(1),
+        ptr(_f32c(decay_A)), ptr(table), table.shape[1], ptr(S0), ptr(theta), ptr(shift_dev), shift_host,
+        ptr(_f32c(rms_weight)), float(rms_eps), ptr(o), dtype_code(o), ptr(S), ptr(sent), B, H, T, D, stream_of(qp)),
+        "pgb_aspin_layer_prefill_fwd")
+    return o, S, sent
+
+
+# ----------------------------------------------------------------------------------------------------------
 def rotate(x, theta, pos):
     """Rotate channel pairs of x (B,H,T,D) by pos[t]*theta[h,i]."""
     need_cuda(x, theta, pos)

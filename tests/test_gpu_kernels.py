@@ -325,3 +325,39 @@ def test_add_norm(dt, d):
         y0, z0 = ops.add_norm(cu(x), None, norm)
         assert y0.data_ptr() == cu(x).data_ptr() or torch.equal(y0.cpu(), x)
         close(z0.float(), norm.cpu()(x).float(), 1e-2 if dt == torch.bfloat16 else 1e-5, "z without delta")
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("gate", [True, False])
+def test_layer_prefill_raw_projections(D, gate):
+    """The whole between-GEMMs kernel: raw (B,T,H,D) projection views in, normalised per-head read out, against
+    prep_ref + the CPU scan + an fp32 RMS norm on the same bf16 inputs."""
+    B, H, T = 2, 3, 333
+    g = torch.Generator().manual_seed(17 + D)
+    d = H * D
+    ld = 3 * d + 2 * H + 2                                                       # padded row, a multiple of 8
+    assert ld % 8 == 0
+    proj = (torch.randn(B, T, ld, generator=g) * 2).to(torch.bfloat16)
+    S0 = torch.randn(B, H, D, D, generator=g) * 0.1
+    A = torch.randn(H, generator=g) - 2
+    w = torch.rand(D, generator=g) + 0.5
+    th = synth.rope_theta(H, D) * (1 + 0.1 * torch.rand(H, D // 2, generator=g))
+    qp, kp, vp = (proj[..., i * d:(i + 1) * d].unflatten(-1, (H, D)) for i in range(3))
+    dl, gl = proj[..., 3 * d:3 * d + H], proj[..., 3 * d + H:3 * d + 2 * H]
+    q, k, v = prep_ref(qp, kp, vp, gl if gate else None, th, torch.arange(T))
+    q, k, v = (t.to(torch.bfloat16).float() for t in (q, k, v))                  # the operands are rounded to bf16
+    la = (-F.softplus(dl.float()) * A.exp()).transpose(1, 2)
+    ro, rS = oracle.assoc_scan(q, k, v, la, oracle.decode_rebase(S0, th, 50.0))
+    eps = 1e-6
+    rn = ro * torch.rsqrt(ro.pow(2).mean(-1, keepdim=True) + eps) * w
+    pd = cu(proj)
+    qd, kd, vd = (pd[..., i * d:(i + 1) * d].unflatten(-1, (H, D)) for i in range(3))
+    table = ops.rot_table(cu(th), 512)
+    o, S, _ = ops.layer_prefill(qd, kd, vd, pd[..., 3 * d + H:3 * d + 2 * H] if gate else None, pd[..., 3 * d:3 * d + H], cu(A),
+                                table, cu(S0), theta=cu(th), shift=50.0, rms_weight=cu(w), rms_eps=eps, out_dtype=torch.float32)
+    close(o.view(B, T, H, D).transpose(1, 2), rn, 3e-3, "layer o"); close(S, rS, 2e-3, "layer S")
+    # and bit-identical to the two-kernel route (prep kernel, then the fused prefill on its output)
+    q2, k2, v2 = ops.prep(qd, kd, vd, pd[..., 3 * d + H:3 * d + 2 * H] if gate else None, cu(th), cu(torch.arange(T)))
+    o2, S2, _ = ops.prefill_fused(q2, k2, v2, pd[..., 3 * d:3 * d + H], cu(A), cu(S0), theta=cu(th), shift=50.0,
+                                  rms_weight=cu(w), rms_eps=eps, out_dtype=torch.float32)
+    close(o, o2, 3e-3, "layer vs two-kernel o"); close(S, S2, 2e-3, "layer vs two-kernel S")
