@@ -41,6 +41,17 @@ constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
 
 __device__ int g_tc_error = 0;
 
+// Phase timing for tuning builds only (-DPGB_TC_TIMING): CTA 0 accumulates clock64() deltas per phase.
+#ifdef PGB_TC_TIMING
+__device__ unsigned long long g_tc_phase[16];
+#define TC_MARK(i) do { if (blockIdx.x == 0 && threadIdx.x == 0) { const long long now_ = clock64(); \
+        atomicAdd(&g_tc_phase[i], (unsigned long long)(now_ - tmark_)); tmark_ = now_; } } while (0)
+#define TC_MARK_INIT long long tmark_ = clock64()
+#else
+#define TC_MARK(i) do {} while (0)
+#define TC_MARK_INIT do {} while (0)
+#endif
+
 // ---------------------------------------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -295,6 +306,7 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
         }
     }
 
+    TC_MARK_INIT;
     for (int c = 0; c < NC && ok; ++c) {
         const int t0 = c * TC_C, st = c & 1;
         const uint32_t qs = base + SM::off_q + st * SM::TILE, ks = base + SM::off_k + st * SM::TILE, vs = base + SM::off_v + st * SM::TILE;
@@ -353,8 +365,11 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
                     }
                 }
         }
+        TC_MARK(0);                                                   // stats + state split
         if (!mbar_wait(st ? bar_full1 : bar_full0, (c >> 1) & 1, 1)) { ok = false; }
+        TC_MARK(1);                                                   // TMA wait
         __syncthreads();                                              // L, e^L, w are visible; the tiles have landed for everyone
+        TC_MARK(2);
         const float aC = expf(Ls[TC_C - 1]);
         if (ok) {
             if constexpr (RAW) {
@@ -439,9 +454,11 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
                 }
             }
         }
+        TC_MARK(3);                                                   // plumbing / K*w
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
+        TC_MARK(4);
         // ---- P, U, O2
         if (tid == 0 && ok) {
             tc_fence_after();
@@ -473,8 +490,10 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
             }
             mma_commit(bar_a);
         }
+        TC_MARK(5);                                                   // MMA issue
         if (ok && !mbar_wait(bar_a, c & 1, 2)) ok = false;
         tc_fence_after();
+        TC_MARK(6);                                                   // MMA wait
         if (ok) {
             // ---- A = P * decay, causal; hi and lo rows of the K-major A operand
             float pv[16];
@@ -506,9 +525,11 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
 #pragma unroll
                 for (int j = 0; j < 4 * NBO; ++j) S[g][j] = fmaf(aC, S[g][j], uv[g][j]);
         }
+        TC_MARK(7);                                                   // scores -> A, state update
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
+        TC_MARK(8);
         // ---- O1 = A V
         if (tid == 0 && ok) {
             tc_fence_after();
@@ -523,6 +544,7 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
         }
         if (ok && !mbar_wait(bar_b, c & 1, 3)) ok = false;
         tc_fence_after();
+        TC_MARK(9);                                                   // O1 issue + wait
         // ---- o = O1 + e^{L_t} O2 [* rsqrt(mean(o^2) + eps) * w]
         float ov[4 * NBO];
         {
@@ -572,8 +594,10 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
                 }
             }
         }
+        TC_MARK(10);                                                  // epilogue
         tc_fence_before();
         __syncthreads();                                              // every TMEM read of this chunk is done before the next MMAs
+        TC_MARK(11);
     }
     // ---- final state
     if (ok) {
@@ -677,6 +701,15 @@ int rot_table_launch(const float *theta, float *table, int H, int T, int D, cuda
     rot_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(theta, reinterpret_cast<float2 *>(table), H, T, D / 2);
     return check_launch("rot_table_kernel");
 }
+
+#ifdef PGB_TC_TIMING
+int tc_phase_dump(unsigned long long *out16) {
+    unsigned long long zero[16] = {};
+    cudaMemcpyFromSymbol(out16, g_tc_phase, sizeof(zero));
+    cudaMemcpyToSymbol(g_tc_phase, zero, sizeof(zero));
+    return 0;
+}
+#endif
 
 // Reads and clears the device-side flag a timed-out wait sets (0 = none). Synchronises the device.
 int tc_error_flag(int *out) {
