@@ -93,6 +93,21 @@ int pgb_aspin_prefill_fwd(const void *q, const void *k, const void *v, int io_dt
                           int D, int precision, void *stream);
 
 /* ---------------------------------------------------------------------------------------------------------
+ * Delta-rule chunked prefill on the tensor cores (bf16 operands): X = (I + beta strictly_lower(K K^T dec))^-1 for every
+ * chunk by a chunk-parallel kernel (exact fp32 substitution), then the walk over chunks with W = X rhs.
+ * Replaces src/assoc_kernel.py:512-546 delta_scan_kernel (ops delta_inv :658, delta_loop_fwd :363, assoc_out :128).
+ *   Arguments as pgb_aspin_prefill_fwd with io dtype bf16 and beta required, plus
+ *   x_scratch: device buffer of at least pgb_aspin_delta_scratch_bytes(B,H,T) bytes, 16-byte aligned, owned by the
+ *   caller; its contents after the call are the X matrices (bf16 head and tail per chunk) and may be discarded.
+ *   B*H and ceil(T/64) must each be at most 65535.
+ * ------------------------------------------------------------------------------------------------------- */
+int pgb_aspin_delta_prefill_fwd(const void *q, const void *k, const void *v, const float *la, const float *beta,
+                                const float *S0, const float *theta, const float *shift_dev, float shift_host, void *o,
+                                int o_dtype, float *S_out, void *sent, void *x_scratch, long long x_scratch_bytes, int B,
+                                int H, int T, int D, void *stream);
+long long pgb_aspin_delta_scratch_bytes(int B, int H, int T);
+
+/* ---------------------------------------------------------------------------------------------------------
  * The same chunked prefill (plain rule, bf16 operands, tensor cores) with the layer's neighbouring elementwise steps
  * fused in, so a layer's prefill is: projection GEMM -> prep -> THIS -> output GEMM.
  * Replaces, in src/assoc.py AssocCarrier.forward: the decay gate (:355-356, :467), the scan (:498-499), the per-head
@@ -117,7 +132,8 @@ int pgb_aspin_prefill_fused_fwd(const void *q, const void *k, const void *v, con
  *   qp, kp, vp: bf16 views (B,T,H*D) of the projection GEMM's output with element strides (in_stride_b, in_stride_t),
  *   unit stride inside a row; 16-byte aligned, strides multiples of 8.
  *   gate_logits (write gate, may be NULL) and decay_logits: bf16 views (B,T,H) with strides (aux_stride_b, aux_stride_t).
- *   rot_table: [H][rot_T][D/2] pairs (cos, sin) of position * theta from pgb_rot_table_build, rot_T >= T.
+ *   rot_table: [H][rot_T][D/2] pairs (cos, sin) of position * theta from pgb_rot_table_build; rot_T >= T rounded up to
+ *   a multiple of 64 (whole chunks of rows are bulk-copied).
  *   Everything else as in pgb_aspin_prefill_fused_fwd.  o is token-major [B][T][H][D].
  * ------------------------------------------------------------------------------------------------------- */
 int pgb_aspin_layer_prefill_fwd(const void *qp, const void *kp, const void *vp, long long in_stride_b,

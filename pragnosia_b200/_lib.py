@@ -24,6 +24,8 @@ SIGNATURES = {
     "pgb_lambda_scan_fwd_ex": [_vp, _vp, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "pgb_aspin_prep_fwd": [_vp, _vp, _vp, _i, _ll, _ll, _ll, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "pgb_aspin_prefill_fwd": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "pgb_aspin_delta_prefill_fwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _vp, _i, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _vp],
+    "pgb_aspin_delta_scratch_bytes": [_i, _i, _i],
     "pgb_aspin_prefill_fused_fwd": [_vp, _vp, _vp, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _f, _vp, _f, _vp, _i, _vp, _vp,
                                     _i, _i, _i, _i, _vp],
     "pgb_aspin_layer_prefill_fwd": [_vp, _vp, _vp, _ll, _ll, _vp, _vp, _ll, _ll, _vp, _vp, _i, _vp, _vp, _vp, _f, _vp, _f,
@@ -50,7 +52,7 @@ def lib() -> C.CDLL:
         for name, args in SIGNATURES.items():
             fn = getattr(L, name)
             fn.argtypes = args
-            fn.restype = _i
+            fn.restype = _ll if name.endswith("_bytes") else _i
         L.pgb_status_string.argtypes = [_i]; L.pgb_status_string.restype = C.c_char_p
         L.pgb_last_cuda_error.argtypes = []; L.pgb_last_cuda_error.restype = C.c_char_p
         _lib = L

@@ -148,8 +148,9 @@ class AssocCarrier(nn.Module):
     def _rot_table(self, T, c):
         """(cos, sin) of position * theta for this layer's window positions; rebuilt when theta changes or T grows."""
         key = c["theta"].data_ptr()
-        if self._rot is None or self._rot[0] != key or self._rot[1].shape[1] < T:
-            self._rot = (key, ops.rot_table(c["theta"], max(T, 64)))
+        need = (T + 63) // 64 * 64                                   # whole 64-token chunks
+        if self._rot is None or self._rot[0] != key or self._rot[1].shape[1] < need:
+            self._rot = (key, ops.rot_table(c["theta"], need))
         return self._rot[1]
 
     def _positions(self, T, device):

@@ -22,6 +22,9 @@ int prefill_tc_launch(const PrefillArgs &, int, int, cudaStream_t);
 bool prefill_tc_supported(int io_dtype, int D, bool delta);
 int decode_launch(const DecodeArgs &, int, int, int, int, cudaStream_t);
 int tc_error_flag(int *out);
+int tc_delta_error_flag(int *out);
+size_t prefill_tc_delta_scratch_bytes(int B, int H, int T);
+int prefill_tc_delta_launch(const PrefillArgs &, int, int, void *, cudaStream_t);
 int rot_table_launch(const float *, float *, int, int, int, cudaStream_t);
 int add_norm_launch(const void *, const void *, const void *, const void *, float, int, void *, void *, long long, int, int,
                     cudaStream_t);
@@ -141,7 +144,7 @@ int pgb_aspin_layer_prefill_fwd(const void *qp, const void *kp, const void *vp, 
     if (!qp || !kp || !vp || !decay_logits || !decay_A || !rot_table || !o || !S_out) return PGB_ERR_NULL_POINTER;
     if (!dtype_ok(o_dtype)) return PGB_ERR_BAD_DTYPE;
     if (B <= 0 || H <= 0 || T <= 0 || (long long)B * H > 0x7fffffffLL || aux_stride_b < 0 || aux_stride_t < H ||
-        in_stride_t < (long long)H * D || in_stride_b < 0 || rot_T < T)
+        in_stride_t < (long long)H * D || in_stride_b < 0 || rot_T < (T + 63) / 64 * 64)
         return PGB_ERR_BAD_SHAPE;
     if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
     if (!aligned(qp, 16) || !aligned(kp, 16) || !aligned(vp, 16) || in_stride_b % 8 || in_stride_t % 8 || !aligned(o, 16) ||
@@ -177,7 +180,33 @@ int pgb_add_norm(const void *x, const void *delta, const void *weight, const voi
 
 int pgb_tc_error_flag(int *out_host) {
     if (!out_host) return PGB_ERR_NULL_POINTER;
-    return tc_error_flag(out_host);
+    int a = 0, b = 0;
+    int rc = tc_error_flag(&a);
+    if (rc == PGB_OK) rc = tc_delta_error_flag(&b);
+    *out_host = a > b ? a : b;
+    return rc;
+}
+
+long long pgb_aspin_delta_scratch_bytes(int B, int H, int T) {
+    if (B <= 0 || H <= 0 || T <= 0) return 0;
+    return (long long)prefill_tc_delta_scratch_bytes(B, H, T);
+}
+
+int pgb_aspin_delta_prefill_fwd(const void *q, const void *k, const void *v, const float *la, const float *beta, const float *S0,
+                                const float *theta, const float *shift_dev, float shift_host, void *o, int o_dtype,
+                                float *S_out, void *sent, void *x_scratch, long long x_scratch_bytes, int B, int H, int T, int D,
+                                void *stream) {
+    if (!q || !k || !v || !la || !beta || !o || !S_out || !x_scratch) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(o_dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || H <= 0 || T <= 0) return PGB_ERR_BAD_SHAPE;
+    if ((long long)B * H > 65535 || (T + 63) / 64 > 65535) return PGB_ERR_TOO_LARGE;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    if (x_scratch_bytes < pgb_aspin_delta_scratch_bytes(B, H, T)) return PGB_ERR_BAD_SHAPE;
+    if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(o, 16) || !aligned(S_out, 16) ||
+        (S0 && !aligned(S0, 16)) || (sent && !aligned(sent, 16)) || !aligned(x_scratch, 16))
+        return PGB_ERR_MISALIGNED;
+    PrefillArgs a{q, k, v, la, beta, S0, o, S_out, (__nv_bfloat16 *)sent, theta, shift_dev, shift_host, B, H, T};
+    return prefill_tc_delta_launch(a, o_dtype, D, x_scratch, (cudaStream_t)stream);
 }
 
 int pgb_rotate_pairs(const void *x, int dtype, const float *theta, const float *pos, void *out, int B, int H, int T, int D,

@@ -30,16 +30,9 @@
 // per-layer table), so the separate prep pass and its HBM round trip disappear.
 //
 // Every mbarrier wait is bounded; a wait that runs out sets g_tc_error, and the CTA still frees its TMEM and returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace pgb {
-
-constexpr int TC_C = 64;
-constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
-
-__device__ int g_tc_error = 0;
 
 // Phase timing for tuning builds only (-DPGB_TC_TIMING): CTA 0 accumulates clock64() deltas per phase.
 #ifdef PGB_TC_TIMING
@@ -51,140 +44,6 @@ __device__ unsigned long long g_tc_phase[16];
 #define TC_MARK(i) do {} while (0)
 #define TC_MARK_INIT do {} while (0)
 #endif
-
-// ---------------------------------------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// bounded wait: false (and the error flag set) if the barrier never flips
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
-    for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i)
-        if (mbar_try(bar, parity)) return true;
-    atomicExch(&g_tc_error, code);
-    return false;
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2) {
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// 32 lanes x 32 columns of 32-bit: thread i of the warp gets lane (base lane + i), columns col .. col+31
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-    uint32_t *r = reinterpret_cast<uint32_t *>(v);
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// 16 lanes x 256 bits per repetition: thread l of the warp gets, for block j of 8 columns,
-//   v[4j+0], v[4j+1] = lane (base + l/4),     columns 8j + 2(l%4), +1
-//   v[4j+2], v[4j+3] = lane (base + l/4 + 8), same columns
-__device__ __forceinline__ void tmem_ld_frag4(uint32_t taddr, float (&v)[16]) {
-    uint32_t *r = reinterpret_cast<uint32_t *>(v);
-    asm volatile("tcgen05.ld.sync.aligned.16x256b.x4.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_frag8(uint32_t taddr, float (&v)[32]) {
-    uint32_t *r = reinterpret_cast<uint32_t *>(v);
-    asm volatile("tcgen05.ld.sync.aligned.16x256b.x8.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr) : "memory");
-}
-template <int NB>
-__device__ __forceinline__ void tmem_ld_frag(uint32_t taddr, float (&v)[4 * NB]) {
-    if constexpr (NB == 4) tmem_ld_frag4(taddr, v); else tmem_ld_frag8(taddr, v);
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// ---------------------------------------------------------------------------------------------- descriptors
-// Shared-memory matrix descriptor, 128-byte swizzle. lbo / sbo in bytes.
-//   K-major:  sbo = bytes between 8-row groups (1024); lbo unused (set 16).
-//   MN-major: sbo = bytes between 8-row (K) groups (1024); lbo = bytes between 64-element groups along M/N.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr >> 4) & 0x3fff);
-    d |= (uint64_t)((lbo >> 4) & 0x3fff) << 16;
-    d |= (uint64_t)((sbo >> 4) & 0x3fff) << 32;
-    d |= (uint64_t)1 << 46;                       // descriptor version (Blackwell)
-    d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
-    return d;
-}
-// Instruction descriptor for kind::f16 with bf16 operands and an fp32 accumulator.
-__host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, int a_mn_major, int b_mn_major) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
-           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
-}
-
-// byte offset of the 16-byte chunk (row r, chunk j) in a [rows][128 B] tile with the 128-byte swizzle
-__device__ __forceinline__ uint32_t swz(int r, int j) { return (uint32_t)(r * 128 + ((j ^ (r & 7)) << 4)); }
-
-__device__ __forceinline__ void split_bf16(float x, __nv_bfloat16 &hi, __nv_bfloat16 &lo) {
-    hi = __float2bfloat16_rn(x);
-    lo = __float2bfloat16_rn(x - __bfloat162float(hi));
-}
-// 8 fp32 -> one 16-byte chunk of bf16 heads and one of tails
-__device__ __forceinline__ void split8(const float (&x)[8], uint4 &hi, uint4 &lo) {
-    __nv_bfloat162 h[4], l[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        h[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);         // one packed convert for two heads
-        const float2 hf = __bfloat1622float2(h[i]);
-        l[i] = __floats2bfloat162_rn(x[2 * i] - hf.x, x[2 * i + 1] - hf.y);
-    }
-    hi = *reinterpret_cast<uint4 *>(h);
-    lo = *reinterpret_cast<uint4 *>(l);
-}
-
-// two fp32 -> packed bf16 heads and packed bf16 tails
-__device__ __forceinline__ void split2(float a, float b, uint32_t &hi, uint32_t &lo) {
-    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    const float2 hf = __bfloat1622float2(h);
-    const __nv_bfloat162 l = __floats2bfloat162_rn(a - hf.x, b - hf.y);
-    hi = *reinterpret_cast<const uint32_t *>(&h);
-    lo = *reinterpret_cast<const uint32_t *>(&l);
-}
 
 struct TcParams {
     const float *la, *S0, *theta, *shift_dev;
@@ -212,7 +71,7 @@ struct TcSmem {
     static constexpr int off_sh = off_al + TC_C * TC_C * 2;           // [D][D] bf16
     static constexpr int off_sl = off_sh + D * D * 2;
     static constexpr int off_misc = off_sl + D * D * 2;               // barriers, tmem base, L / eL / w, ...
-    static constexpr int bytes = off_misc + 2048 + 1024;              // + slack for the 1024-byte alignment
+    static constexpr int bytes = off_misc + 3072 + 1024;              // misc (2.2 KB used) + slack for the 1024-byte alignment
 };
 
 constexpr int TC_NT = 256;
@@ -237,7 +96,14 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + SM::off_misc + 64);
     float *Ls = reinterpret_cast<float *>(sm + SM::off_misc + 128);            // L[64]
     float *eLs = Ls + 64, *wts = eLs + 64, *red = wts + 64, *rmsw = red + 128; // red[2][64], rmsw[D]
-    const uint32_t bar_full0 = base + SM::off_misc, bar_full1 = bar_full0 + 8, bar_a = bar_full0 + 16, bar_b = bar_full0 + 24;
+    float *gts = rmsw + 128;                                                   // sigmoid(write gate) of the chunk's tokens
+    const uint32_t bar_full0 = base + SM::off_misc, bar_full1 = bar_full0 + 8, bar_a = bar_full0 + 16, bar_b = bar_full0 + 24,
+                   bar_rot = bar_full0 + 32;
+    // RAW, D = 64: the chunk's 64 x 32 (cos, sin) pairs are bulk-copied into the A-operand buffers, which are idle
+    // between one chunk's O1 product and the next chunk's score pass
+    constexpr bool ROT_SMEM = RAW && D == 64;
+    constexpr uint32_t ROT_BYTES = TC_C * (D / 2) * 8;
+    const float2 *rot_sm = reinterpret_cast<const float2 *>(sm + SM::off_ah);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, wg = warp >> 2, sub = warp & 3;
     const int bh = blockIdx.x, h = bh % p.H, b = bh / p.H;
@@ -246,7 +112,7 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
     const int tma_c0 = RAW ? h * D : 0, tma_c2 = RAW ? b : bh;
 
     if (tid == 0) {
-        mbar_init(bar_full0, 1); mbar_init(bar_full1, 1); mbar_init(bar_a, 1); mbar_init(bar_b, 1);
+        mbar_init(bar_full0, 1); mbar_init(bar_full1, 1); mbar_init(bar_a, 1); mbar_init(bar_b, 1); mbar_init(bar_rot, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) tmem_alloc(smem_u32(tmem_slot), TM_COLS);
@@ -304,7 +170,23 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
             tma_load_3d(base + SM::off_k + s * 8192, &mk, bar_full0, tma_c0 + 64 * s, 0, tma_c2);
             tma_load_3d(base + SM::off_v + s * 8192, &mv, bar_full0, tma_c0 + 64 * s, 0, tma_c2);
         }
+        if constexpr (ROT_SMEM) {
+            mbar_expect_tx(bar_rot, ROT_BYTES);
+            bulk_load_1d(base + SM::off_ah, p.rot + (size_t)h * p.rot_T * (D / 2), ROT_BYTES, bar_rot);
+        }
     }
+    // decay (and write-gate) inputs of the first chunk, fetched one chunk ahead from here on
+    auto fetch_decay = [&](int t) -> float {
+        if (t >= T) return 0.f;
+        if (p.la_raw != nullptr) return __bfloat162float(p.la_raw[(size_t)b * p.aux_sb + (size_t)t * p.aux_st + h]);
+        return la[t];
+    };
+    auto fetch_gate = [&](int t) -> float {
+        if (!RAW || p.gate_raw == nullptr || t >= T) return 0.f;
+        return __bfloat162float(p.gate_raw[(size_t)b * p.aux_sb + (size_t)t * p.aux_st + h]);
+    };
+    float nx_own = 0.f, nx_other = 0.f, nx_gate = 0.f;
+    if (warp < 2) { nx_own = fetch_decay(tid); nx_other = fetch_decay(tid ^ 32); nx_gate = fetch_gate(tid); }
 
     TC_MARK_INIT;
     for (int c = 0; c < NC && ok; ++c) {
@@ -321,18 +203,17 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
                 tma_load_3d(base + SM::off_v + o2 + s * 8192, &mv, nb, tma_c0 + 64 * s, t0 + TC_C, tma_c2);
             }
         }
+        TC_MARK(12);                                                  // next-chunk TMA issue
         // ---- decay statistics of the chunk: warps 0 and 1 each scan their 32 tokens and reduce the other half
         if (warp < 2) {
-            auto log_decay = [&](int r) -> float {
-                const int t = t0 + r;
-                if (t >= T) return 0.f;                               // padding tokens: alpha = 1
-                if (p.la_raw != nullptr) {                            // -softplus(gate logit) * exp(A_h)   (src/assoc.py:355-356)
-                    const float x = __bfloat162float(p.la_raw[(size_t)b * p.aux_sb + (size_t)t * p.aux_st + h]);
-                    return -softplusf_(x) * expf(p.decay_A[h]);
-                }
-                return la[t];
+            // -softplus(gate logit) * exp(A_h) when the decay comes as logits (src/assoc.py:355-356); padding tokens: alpha = 1
+            auto log_decay = [&](float raw, int r) -> float {
+                if (t0 + r >= T) return 0.f;
+                return p.la_raw != nullptr ? -softplusf_(raw) * expf(p.decay_A[h]) : raw;
             };
-            const float own = log_decay(tid), other = log_decay(tid ^ 32);
+            const float own = log_decay(nx_own, tid), other = log_decay(nx_other, tid ^ 32);
+            if (RAW) gts[tid] = p.gate_raw != nullptr ? sigmoidf_(nx_gate) : 1.f;
+            nx_own = fetch_decay(t0 + TC_C + tid); nx_other = fetch_decay(t0 + TC_C + (tid ^ 32)); nx_gate = fetch_gate(t0 + TC_C + tid);
             float sc = own;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -345,6 +226,7 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
             eLs[tid] = expf(L);
             wts[tid] = (t0 + tid < T) ? expf(fminf(Ltot - L, 0.f)) : 0.f;
         }
+        TC_MARK(13);                                                  // decay statistics
         // ---- the entering state as an MN-major B operand, hi and lo (and to HBM if asked for)
         {
             uint8_t *sh = sm + SM::off_sh + (D == 128 ? wg * (D * 128) : 0), *sl = sm + SM::off_sl + (D == 128 ? wg * (D * 128) : 0);
@@ -367,6 +249,7 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
         }
         TC_MARK(0);                                                   // stats + state split
         if (!mbar_wait(st ? bar_full1 : bar_full0, (c >> 1) & 1, 1)) { ok = false; }
+        if (ROT_SMEM && ok && !mbar_wait(bar_rot, c & 1, 4)) ok = false;
         TC_MARK(1);                                                   // TMA wait
         __syncthreads();                                              // L, e^L, w are visible; the tiles have landed for everyone
         TC_MARK(2);
@@ -399,16 +282,16 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
                         ss += __shfl_xor_sync(0xffffffffu, ss, 4);
                         float inv = 1.0f / fmaxf(sqrtf(ss), 1e-12f);
                         const int t = min(t0 + row, T - 1);
-                        if (which == 1 && p.gate_raw != nullptr)
-                            inv *= sigmoidf_(__bfloat162float(p.gate_raw[(size_t)b * p.aux_sb + (size_t)t * p.aux_st + h]));
+                        if (which == 1) inv *= gts[row];
                         const float w = wts[row];
 #pragma unroll
                         for (int s2 = 0; s2 < SUB; ++s2) {
                             float y[8];
                             if (which < 2) {
-                                const float4 *rt = reinterpret_cast<const float4 *>(
-                                    p.rot + ((size_t)h * p.rot_T + min(t, p.rot_T - 1)) * (D / 2) + s2 * 32 + cp * 4);
-                                const float4 r01 = __ldg(rt), r23 = __ldg(rt + 1);     // (c0,s0,c1,s1), (c2,s2,c3,s3)
+                                const float4 *rt = ROT_SMEM
+                                    ? reinterpret_cast<const float4 *>(rot_sm + row * (D / 2) + cp * 4)
+                                    : reinterpret_cast<const float4 *>(p.rot + ((size_t)h * p.rot_T + min(t, p.rot_T - 1)) * (D / 2) + s2 * 32 + cp * 4);
+                                const float4 r01 = rt[0], r23 = rt[1];                 // (c0,s0,c1,s1), (c2,s2,c3,s3)
                                 const float cs[4] = {r01.x, r01.z, r23.x, r23.z}, sn[4] = {r01.y, r01.w, r23.y, r23.w};
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
@@ -463,30 +346,29 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
         if (tid == 0 && ok) {
             tc_fence_after();
             constexpr uint32_t I_P = idesc_bf16(64, 64, 0, 0), I_U = idesc_bf16(D, D, 1, 1), I_O = idesc_bf16(64, D, 0, 1);
+            // a descriptor's start-address field counts 16-byte units: stepping is an add on the low word
+            const uint64_t dq = smem_desc(qs, 16, 1024), dk = smem_desc(ks, 16, 1024), dv = smem_desc(vs, 8192, 1024);
+            const uint64_t dkwh = smem_desc(base + SM::off_kwh, 8192, 1024), dkwl = smem_desc(base + SM::off_kwl, 8192, 1024);
+            const uint64_t dsh = smem_desc(base + SM::off_sh, D * 128, 1024), dsl = smem_desc(base + SM::off_sl, D * 128, 1024);
 #pragma unroll
             for (int k = 0; k < D / 16; ++k) {                        // P = Q K^T, K-major steps of 32 B inside a sub-tile
-                const uint32_t ko = (uint32_t)(k >> 2) * 8192u + (uint32_t)(k & 3) * 32u;
-                mma_bf16(tmem + TM_P, smem_desc(qs + ko, 16, 1024), smem_desc(ks + ko, 16, 1024), I_P, k > 0);
+                const uint32_t ko = ((uint32_t)(k >> 2) * 8192u + (uint32_t)(k & 3) * 32u) >> 4;
+                mma_bf16(tmem + TM_P, dq + ko, dk + ko, I_P, k > 0);
             }
 #pragma unroll
-            for (int k = 0; k < TC_C / 16; ++k) {                     // U = (K w)^T V over the 64 tokens, 16 rows (2048 B) a step
-                const uint32_t ko = (uint32_t)k * 2048u;
-                mma_bf16(tmem + TM_U, smem_desc(base + SM::off_kwh + ko, 8192, 1024), smem_desc(vs + ko, 8192, 1024), I_U, k > 0);
-            }
+            for (int k = 0; k < TC_C / 16; ++k)                       // U = (K w)^T V over the 64 tokens, 16 rows (2048 B) a step
+                mma_bf16(tmem + TM_U, dkwh + k * 128, dv + k * 128, I_U, k > 0);
 #pragma unroll
-            for (int k = 0; k < TC_C / 16; ++k) {
-                const uint32_t ko = (uint32_t)k * 2048u;
-                mma_bf16(tmem + TM_U, smem_desc(base + SM::off_kwl + ko, 8192, 1024), smem_desc(vs + ko, 8192, 1024), I_U, 1);
-            }
+            for (int k = 0; k < TC_C / 16; ++k) mma_bf16(tmem + TM_U, dkwl + k * 128, dv + k * 128, I_U, 1);
 #pragma unroll
             for (int k = 0; k < D / 16; ++k) {                        // O2 = Q S (hi then lo); S rows are the key index
-                const uint32_t qo = (uint32_t)(k >> 2) * 8192u + (uint32_t)(k & 3) * 32u, so = (uint32_t)k * 2048u;
-                mma_bf16(tmem + TM_O2, smem_desc(qs + qo, 16, 1024), smem_desc(base + SM::off_sh + so, D * 128, 1024), I_O, k > 0);
+                const uint32_t qo = ((uint32_t)(k >> 2) * 8192u + (uint32_t)(k & 3) * 32u) >> 4;
+                mma_bf16(tmem + TM_O2, dq + qo, dsh + k * 128, I_O, k > 0);
             }
 #pragma unroll
             for (int k = 0; k < D / 16; ++k) {
-                const uint32_t qo = (uint32_t)(k >> 2) * 8192u + (uint32_t)(k & 3) * 32u, so = (uint32_t)k * 2048u;
-                mma_bf16(tmem + TM_O2, smem_desc(qs + qo, 16, 1024), smem_desc(base + SM::off_sl + so, D * 128, 1024), I_O, 1);
+                const uint32_t qo = ((uint32_t)(k >> 2) * 8192u + (uint32_t)(k & 3) * 32u) >> 4;
+                mma_bf16(tmem + TM_O2, dq + qo, dsl + k * 128, I_O, 1);
             }
             mma_commit(bar_a);
         }
@@ -534,16 +416,20 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
         if (tid == 0 && ok) {
             tc_fence_after();
             constexpr uint32_t I_O = idesc_bf16(64, D, 0, 1);
+            const uint64_t dah = smem_desc(base + SM::off_ah, 16, 1024), dal = smem_desc(base + SM::off_al, 16, 1024);
+            const uint64_t dv = smem_desc(vs, 8192, 1024);
 #pragma unroll
-            for (int k = 0; k < TC_C / 16; ++k)
-                mma_bf16(tmem + TM_O1, smem_desc(base + SM::off_ah + k * 32, 16, 1024), smem_desc(vs + k * 2048, 8192, 1024), I_O, k > 0);
+            for (int k = 0; k < TC_C / 16; ++k) mma_bf16(tmem + TM_O1, dah + k * 2, dv + k * 128, I_O, k > 0);
 #pragma unroll
-            for (int k = 0; k < TC_C / 16; ++k)
-                mma_bf16(tmem + TM_O1, smem_desc(base + SM::off_al + k * 32, 16, 1024), smem_desc(vs + k * 2048, 8192, 1024), I_O, 1);
+            for (int k = 0; k < TC_C / 16; ++k) mma_bf16(tmem + TM_O1, dal + k * 2, dv + k * 128, I_O, 1);
             mma_commit(bar_b);
         }
         if (ok && !mbar_wait(bar_b, c & 1, 3)) ok = false;
         tc_fence_after();
+        if (ROT_SMEM && tid == 0 && ok && c + 1 < NC) {              // A buffers are idle again: next chunk's (cos, sin) rows
+            mbar_expect_tx(bar_rot, ROT_BYTES);
+            bulk_load_1d(base + SM::off_ah, p.rot + ((size_t)h * p.rot_T + t0 + TC_C) * (D / 2), ROT_BYTES, bar_rot);
+        }
         TC_MARK(9);                                                   // O1 issue + wait
         // ---- o = O1 + e^{L_t} O2 [* rsqrt(mean(o^2) + eps) * w]
         float ov[4 * NBO];
@@ -619,36 +505,6 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
 // ---------------------------------------------------------------------------------------------- host side
 namespace {
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void *sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(sym);
-    }
-    return fn;
-}
-
-// bf16 [n2][T][cols] with the given row / slab strides (elements); box = 64 columns x 64 tokens x 1, 128-byte swizzle,
-// zero fill past T
-bool make_map(CUtensorMap *m, const void *ptr, long long n2, int T, long long cols, long long stride_t, long long stride_2) {
-    EncodeTiledFn fn = encode_fn();
-    if (fn == nullptr) return false;
-    cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)T, (cuuint64_t)n2};
-    cuuint64_t strides[2] = {(cuuint64_t)stride_t * 2, (cuuint64_t)stride_2 * 2};
-    cuuint32_t box[3] = {64, 64, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int D, bool RAW>
 int tc_go(const PrefillArgs &a, int o_dtype, cudaStream_t stream) {
     using SM = TcSmem<D>;
@@ -656,12 +512,12 @@ int tc_go(const PrefillArgs &a, int o_dtype, cudaStream_t stream) {
     const int BH = a.B * a.H;
     bool made;
     if (RAW)       // (B,T,H*D) views into the projection GEMM's output
-        made = make_map(&mq, a.q, a.B, a.T, (long long)a.H * D, a.raw_st, a.raw_sb) &&
-               make_map(&mk, a.k, a.B, a.T, (long long)a.H * D, a.raw_st, a.raw_sb) &&
-               make_map(&mv, a.v, a.B, a.T, (long long)a.H * D, a.raw_st, a.raw_sb);
+        made = tc_make_map(&mq, a.q, a.B, a.T, (long long)a.H * D, a.raw_st, a.raw_sb) &&
+               tc_make_map(&mk, a.k, a.B, a.T, (long long)a.H * D, a.raw_st, a.raw_sb) &&
+               tc_make_map(&mv, a.v, a.B, a.T, (long long)a.H * D, a.raw_st, a.raw_sb);
     else           // contiguous (B*H, T, D)
-        made = make_map(&mq, a.q, BH, a.T, D, D, (long long)a.T * D) && make_map(&mk, a.k, BH, a.T, D, D, (long long)a.T * D) &&
-               make_map(&mv, a.v, BH, a.T, D, D, (long long)a.T * D);
+        made = tc_make_map(&mq, a.q, BH, a.T, D, D, (long long)a.T * D) && tc_make_map(&mk, a.k, BH, a.T, D, D, (long long)a.T * D) &&
+               tc_make_map(&mv, a.v, BH, a.T, D, D, (long long)a.T * D);
     if (!made) {
         set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
         return PGB_ERR_CUDA;
@@ -711,13 +567,6 @@ int tc_phase_dump(unsigned long long *out16) {
 }
 #endif
 
-// Reads and clears the device-side flag a timed-out wait sets (0 = none). Synchronises the device.
-int tc_error_flag(int *out) {
-    int zero = 0;
-    cudaError_t e = cudaMemcpyFromSymbol(out, g_tc_error, sizeof(int));
-    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
-    if (e != cudaSuccess) { set_cuda_error(e, "tc_error_flag"); return PGB_ERR_CUDA; }
-    return PGB_OK;
-}
+int tc_error_flag(int *out) { return tc_read_error_flag(out); }
 
 }  // namespace pgb

@@ -121,6 +121,14 @@ def prefill(q, k, v, la, beta=None, S0=None, theta=None, shift=0.0, want_sent: b
     S = _state_out(S_out, B, H, D, q.device)
     NC = (T + CHUNK - 1) // CHUNK
     sent = torch.empty(B, H, NC, D, D, device=q.device, dtype=torch.bfloat16) if want_sent else None
+    if beta is not None and q.dtype == torch.bfloat16 and precision != _lib.PREFILL_FP32 and B * H <= 65535:
+        # delta rule on the tensor cores: the chunk inverses go through a scratch buffer (allocated here, by torch)
+        nbytes = lib().pgb_aspin_delta_scratch_bytes(B, H, T)
+        scratch = torch.empty(nbytes, device=q.device, dtype=torch.uint8)
+        check(lib().pgb_aspin_delta_prefill_fwd(ptr(q), ptr(k), ptr(v), ptr(la), ptr(beta), ptr(S0), ptr(theta), ptr(shift_dev),
+                                                shift_host, ptr(o), dtype_code(o), ptr(S), ptr(sent), ptr(scratch), nbytes,
+                                                B, H, T, D, stream_of(q)), "pgb_aspin_delta_prefill_fwd")
+        return o, S, sent
     check(lib().pgb_aspin_prefill_fwd(ptr(q), ptr(k), ptr(v), dtype_code(q), ptr(la), ptr(beta), ptr(S0), ptr(theta),
                                       ptr(shift_dev), shift_host, ptr(o), dtype_code(o), ptr(S), ptr(sent), B, H, T, D, precision,
                                       stream_of(q)), "pgb_aspin_prefill_fwd")
@@ -188,8 +196,8 @@ def layer_prefill(qp, kp, vp, gate_logits, decay_logits, decay_A, table, S0=None
         raise ValueError("layer_prefill: decay_logits must be a bf16 (B,T,H) view with unit stride over H")
     if gate_logits is not None and (gate_logits.dtype != torch.bfloat16 or gate_logits.stride() != decay_logits.stride()):
         raise ValueError("layer_prefill: gate_logits must share decay_logits' dtype and strides")
-    if table.shape[1] < T:
-        raise ValueError("layer_prefill: rotation table shorter than the window")
+    if table.shape[1] < (T + CHUNK - 1) // CHUNK * CHUNK:
+        raise ValueError("layer_prefill: the rotation table must cover the window rounded up to whole 64-token chunks")
     S0 = _f32c(S0)
     shift_dev, shift_host = None, 0.0
     if theta is not None and S0 is not None:

@@ -19,7 +19,7 @@ def L():
 
 def declared_symbols():
     text = (ROOT / "include" / "pragnosia_b200.h").read_text()
-    return sorted(set(re.findall(r"^(?:int|const char \*)\s*(pgb_[a-z0-9_]+)\(", text, flags=re.M)))
+    return sorted(set(re.findall(r"^(?:int|long long|const char \*)\s*(pgb_[a-z0-9_]+)\(", text, flags=re.M)))
 
 
 def test_every_declared_symbol_is_exported(L):

@@ -352,7 +352,7 @@ def test_layer_prefill_raw_projections(D, gate):
     rn = ro * torch.rsqrt(ro.pow(2).mean(-1, keepdim=True) + eps) * w
     pd = cu(proj)
     qd, kd, vd = (pd[..., i * d:(i + 1) * d].unflatten(-1, (H, D)) for i in range(3))
-    table = ops.rot_table(cu(th), 512)
+    table = ops.rot_table(cu(th), 512)                                         # covers T rounded up to whole chunks
     o, S, _ = ops.layer_prefill(qd, kd, vd, pd[..., 3 * d + H:3 * d + 2 * H] if gate else None, pd[..., 3 * d:3 * d + H], cu(A),
                                 table, cu(S0), theta=cu(th), shift=50.0, rms_weight=cu(w), rms_eps=eps, out_dtype=torch.float32)
     close(o.view(B, T, H, D).transpose(1, 2), rn, 3e-3, "layer o"); close(S, rS, 2e-3, "layer S")

@@ -97,3 +97,65 @@ def test_extreme_decay_and_many_chains():
     ro, rS = oracle.assoc_scan(q.float(), k.float(), v.float(), la, None)
     check(o, S, ro, rS, "extreme decay")
     assert flag() == 0
+
+
+# ------------------------------------------------------------------------------------------------ delta rule
+def delta_inputs(B, H, T, D, seed):
+    x = synth.assoc_op_inputs(B, H, T, D, seed=seed, delta=True, with_state=True)
+    q = oracle.rotate(x["q"], x["theta"], x["pos"]).to(torch.bfloat16)
+    k = oracle.rotate(x["k"], x["theta"], x["pos"]).to(torch.bfloat16)
+    return q, k, x["v"].to(torch.bfloat16), x["la"], x["beta"], x["S0"]
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("T", [1, 63, 64, 65, 200, 333, 512])
+def test_delta_tensor_cores(D, T):
+    """The delta rule on the tensor cores (X by exact fp32 substitution, then W = X rhs) against the chunked CPU form and
+    the literal per-token recurrence, on the same bf16-rounded inputs: output 2e-3, state 1e-4."""
+    q, k, v, la, be, S0 = delta_inputs(2, 3, T, D, seed=200 + T + D)
+    d = lambda t: t.to(DEV)
+    ro, rS = oracle.assoc_scan(q.float(), k.float(), v.float(), la, S0, beta=be)
+    o, S, sent = ops.prefill(d(q), d(k), d(v), d(la), d(be), d(S0), out_dtype=torch.float32, want_sent=True)
+    check(o, S, ro, rS, f"delta D{D} T{T}")
+    lo, lS = oracle.delta_literal(q[:1, :1].double(), k[:1, :1].double(), v[:1, :1].double(), la[:1, :1].double(),
+                                  be[:1, :1].double(), S0[:1, :1].double())
+    check(o[:1, :1], S[:1, :1], lo.float(), lS.float(), f"delta literal D{D} T{T}")
+    assert torch.equal(sent[:, :, 0].cpu(), S0.to(torch.bfloat16))
+    of, Sf, _ = ops.prefill(d(q), d(k), d(v), d(la), d(be), d(S0), precision=_lib.PREFILL_FP32, out_dtype=torch.float32)
+    assert rel_err(o.cpu(), of.cpu()) < 5e-4 and rel_err(S.cpu(), Sf.cpu()) < 1e-4
+    o2, S2, _ = ops.prefill(d(q), d(k), d(v), d(la), d(be), d(S0), out_dtype=torch.float32)
+    assert torch.equal(o, o2) and torch.equal(S, S2)
+    assert flag() == 0
+
+
+def test_delta_known_answers_tensor_cores(golden):
+    """Repeated key with beta -> 1 (the case that broke reduced-precision inverses, src/assoc_kernel.py:577-582), 256
+    correlated writes with beta = 1, and the rebase + two-window split."""
+    import torch.nn.functional as F
+    R = golden("delta_kat")["repeated"]
+    k = R["k"].expand(1, 1, 128, 64).contiguous().to(torch.bfloat16)
+    qq, vv = R["q"].to(torch.bfloat16), R["v"].to(torch.bfloat16)
+    be = torch.full((1, 1, 128), 0.99999); la = torch.full((1, 1, 128), -1e-4)
+    ro, rS = oracle.assoc_scan(qq.double(), k.double(), vv.double(), la.double(), None, beta=be.double())
+    o, S, _ = ops.prefill(qq.to(DEV), k.to(DEV), vv.to(DEV), la.to(DEV), be.to(DEV), None, out_dtype=torch.float32)
+    assert S.abs().max().item() < 3.0
+    check(o, S, ro.float(), rS.float(), "repeated key")
+    g = torch.Generator().manual_seed(1)
+    Kr = F.normalize(torch.randn(2, 4, 256, 64, generator=g), dim=-1).to(torch.bfloat16)
+    Vr = F.normalize(torch.randn(2, 4, 256, 64, generator=g), dim=-1).to(torch.bfloat16)
+    z, one = torch.zeros(2, 4, 256), torch.ones(2, 4, 256)
+    ro, rS = oracle.assoc_scan(Kr.float(), Kr.float(), Vr.float(), z, None, beta=one)
+    o, S, _ = ops.prefill(Kr.to(DEV), Kr.to(DEV), Vr.to(DEV), z.to(DEV), one.to(DEV), None, out_dtype=torch.float32)
+    assert S.abs().max().item() < 2.0
+    check(o, S, ro, rS, "correlated writes")
+    q, k, v, la, be, S0 = delta_inputs(2, 3, 300, 128, seed=9)
+    th = torch.rand(3, 64) * 0.5
+    d = lambda t: t.to(DEV)
+    o, S, _ = ops.prefill(d(q), d(k), d(v), d(la), d(be), d(S0), theta=d(th), shift=41.0, out_dtype=torch.float32)
+    ro, rS = oracle.assoc_scan(q.float(), k.float(), v.float(), la, oracle.decode_rebase(S0, th, 41.0), beta=be)
+    check(o, S, ro, rS, "delta rebase")
+    a = ops.prefill(d(q[:, :, :130]), d(k[:, :, :130]), d(v[:, :, :130]), d(la[:, :, :130]), d(be[:, :, :130]), d(S0), out_dtype=torch.float32)
+    b = ops.prefill(d(q[:, :, 130:]), d(k[:, :, 130:]), d(v[:, :, 130:]), d(la[:, :, 130:]), d(be[:, :, 130:]), a[1], out_dtype=torch.float32)
+    r2, rS2 = oracle.assoc_scan(q.float(), k.float(), v.float(), la, S0, beta=be)
+    check(torch.cat([a[0], b[0]], 2), b[1], r2, rS2, "delta two windows")
+    assert flag() == 0
