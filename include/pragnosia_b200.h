@@ -108,6 +108,28 @@ int pgb_aspin_delta_prefill_fwd(const void *q, const void *k, const void *v, con
 long long pgb_aspin_delta_scratch_bytes(int B, int H, int T);
 
 /* ---------------------------------------------------------------------------------------------------------
+ * pgb_aspin_delta_prefill_fwd without the x_scratch argument. It has no counterpart in the reference.
+ * It exists for callers that cannot get device memory at the moment they call: an operator hook inside a serving
+ * runtime that owns every byte of device memory and hands the hook only tensor pointers and a stream (allocating there
+ * would synchronise the device, can fail in the middle of a request, and is usually forbidden outright), or code that
+ * is being recorded into a CUDA graph, where the ordinary allocation calls are not allowed. For them the chunk inverses
+ * go to a fixed 32 MiB array that is part of the library's device image, so this call never allocates or frees.
+ *   Limit: B * H * ceil(T/64) <= 2048 (16 KiB per (sequence-head, chunk)); larger problems return PGB_ERR_TOO_LARGE and
+ *   must use pgb_aspin_delta_prefill_fwd. Every GPU that loads the library keeps those 32 MiB reserved until the process
+ *   exits, whether or not this entry point is ever used.
+ *   The first call on each device looks up the array's device address (a host-side query, cached afterwards). Make that
+ *   first call outside any stream capture.
+ *   All calls on a device share the one array and it keeps whatever the previous call left there (nothing in it has to
+ *   start at zero: each call overwrites the part it reads). Two calls whose kernels can run at the same time on one
+ *   device -- different streams, or different host threads -- would overwrite each other's inverses: serialise them.
+ *   Inputs, outputs, dtype and dimension rules are exactly those of pgb_aspin_delta_prefill_fwd.
+ * ------------------------------------------------------------------------------------------------------- */
+int pgb_aspin_delta_prefill_noscratch_fwd(const void *q, const void *k, const void *v, const float *la, const float *beta,
+                                          const float *S0, const float *theta, const float *shift_dev, float shift_host,
+                                          void *o, int o_dtype, float *S_out, void *sent, int B, int H, int T, int D,
+                                          void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
  * The same chunked prefill (plain rule, bf16 operands, tensor cores) with the layer's neighbouring elementwise steps
  * fused in, so a layer's prefill is: projection GEMM -> prep -> THIS -> output GEMM.
  * Replaces, in src/assoc.py AssocCarrier.forward: the decay gate (:355-356, :467), the scan (:498-499), the per-head

@@ -26,6 +26,7 @@ SIGNATURES = {
     "pgb_aspin_prefill_fwd": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "pgb_aspin_delta_prefill_fwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _vp, _i, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _vp],
     "pgb_aspin_delta_scratch_bytes": [_i, _i, _i],
+    "pgb_aspin_delta_prefill_noscratch_fwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp],
     "pgb_aspin_prefill_fused_fwd": [_vp, _vp, _vp, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _f, _vp, _f, _vp, _i, _vp, _vp,
                                     _i, _i, _i, _i, _vp],
     "pgb_aspin_layer_prefill_fwd": [_vp, _vp, _vp, _ll, _ll, _vp, _vp, _ll, _ll, _vp, _vp, _i, _vp, _vp, _vp, _f, _vp, _f,

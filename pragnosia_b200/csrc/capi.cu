@@ -25,6 +25,8 @@ int tc_error_flag(int *out);
 int tc_delta_error_flag(int *out);
 size_t prefill_tc_delta_scratch_bytes(int B, int H, int T);
 int prefill_tc_delta_launch(const PrefillArgs &, int, int, void *, cudaStream_t);
+int prefill_tc_delta_static_launch(const PrefillArgs &, int, int, cudaStream_t);
+long long prefill_tc_delta_static_capacity();
 int rot_table_launch(const float *, float *, int, int, int, cudaStream_t);
 int add_norm_launch(const void *, const void *, const void *, const void *, float, int, void *, void *, long long, int, int,
                     cudaStream_t);
@@ -51,7 +53,9 @@ const char *pgb_status_string(int s) {
         case PGB_ERR_MISALIGNED: return "pointer or stride breaks the alignment rule";
         case PGB_ERR_BAD_DTYPE: return "unknown dtype code";
         case PGB_ERR_CUDA: return "CUDA launch failed";
-        case PGB_ERR_TOO_LARGE: return "size exceeds the documented maximum";
+        case PGB_ERR_TOO_LARGE:
+            return "size exceeds the documented maximum (for pgb_aspin_delta_prefill_noscratch_fwd: B*H*ceil(T/64) > 2048, the "
+                   "built-in 32 MiB scratch; use pgb_aspin_delta_prefill_fwd with your own buffer)";
         default: return "unknown status";
     }
 }
@@ -162,6 +166,23 @@ int pgb_rot_table_build(const float *theta, float *table, int H, int T, int D, v
     if (H <= 0 || T <= 0 || D <= 0 || (D & 1)) return PGB_ERR_BAD_SHAPE;
     if (!aligned(table, 16)) return PGB_ERR_MISALIGNED;
     return rot_table_launch(theta, table, H, T, D, (cudaStream_t)stream);
+}
+
+int pgb_aspin_delta_prefill_noscratch_fwd(const void *q, const void *k, const void *v, const float *la, const float *beta,
+                                          const float *S0, const float *theta, const float *shift_dev, float shift_host,
+                                          void *o, int o_dtype, float *S_out, void *sent, int B, int H, int T, int D,
+                                          void *stream) {
+    if (!q || !k || !v || !la || !beta || !o || !S_out) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(o_dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || H <= 0 || T <= 0) return PGB_ERR_BAD_SHAPE;
+    if ((long long)B * H > 65535 || (T + 63) / 64 > 65535) return PGB_ERR_TOO_LARGE;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    if (pgb_aspin_delta_scratch_bytes(B, H, T) > prefill_tc_delta_static_capacity()) return PGB_ERR_TOO_LARGE;
+    if (!aligned(q, 16) || !aligned(k, 16) || !aligned(v, 16) || !aligned(o, 16) || !aligned(S_out, 16) ||
+        (S0 && !aligned(S0, 16)) || (sent && !aligned(sent, 16)))
+        return PGB_ERR_MISALIGNED;
+    PrefillArgs a{q, k, v, la, beta, S0, o, S_out, (__nv_bfloat16 *)sent, theta, shift_dev, shift_host, B, H, T};
+    return prefill_tc_delta_static_launch(a, o_dtype, D, (cudaStream_t)stream);
 }
 
 int pgb_add_norm(const void *x, const void *delta, const void *weight, const void *bias, float eps, int kind, void *y, void *z,

@@ -509,4 +509,35 @@ int prefill_tc_delta_launch(const PrefillArgs &a, int o_dtype, int D, void *x_sc
 
 int tc_delta_error_flag(int *out) { return tc_read_error_flag(out); }
 
+// ------------------------------------------------------------------------------------------------ built-in scratch
+// The same delta prefill for callers that have no way to hand over a scratch buffer. The chunk inverses then live in
+// this file-scope device array: PGB_STATIC_SCRATCH_BYTES of device memory that every GPU which loads the library keeps
+// reserved until the process exits. In host code the array's name is only a stand-in for the device object, so its
+// device address is asked for once per device (cudaGetSymbolAddress, with that device current) and cached.
+constexpr size_t PGB_STATIC_SCRATCH_BYTES = 32u << 20;                 // 2048 (sequence-head, chunk) pairs of 16 KiB
+static __device__ __align__(256) unsigned char g_static_scratch[PGB_STATIC_SCRATCH_BYTES];
+
+static void *static_scratch_ptr() {
+    constexpr int MAX_DEV = 64;
+    static void *cache[MAX_DEV] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return nullptr;
+    void *ptr = __atomic_load_n(&cache[dev], __ATOMIC_ACQUIRE);
+    if (ptr == nullptr) {
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || ptr == nullptr) { set_cuda_error(e, "cudaGetSymbolAddress(static scratch)"); return nullptr; }
+        __atomic_store_n(&cache[dev], ptr, __ATOMIC_RELEASE);         // the same value whoever gets here first
+    }
+    return ptr;
+}
+
+long long prefill_tc_delta_static_capacity() { return (long long)PGB_STATIC_SCRATCH_BYTES; }
+
+int prefill_tc_delta_static_launch(const PrefillArgs &a, int o_dtype, int D, cudaStream_t stream) {
+    if (prefill_tc_delta_scratch_bytes(a.B, a.H, a.T) > PGB_STATIC_SCRATCH_BYTES) return PGB_ERR_TOO_LARGE;
+    void *scratch = static_scratch_ptr();
+    if (scratch == nullptr) return PGB_ERR_CUDA;
+    return prefill_tc_delta_launch(a, o_dtype, D, scratch, stream);
+}
+
 }  // namespace pgb
