@@ -37,10 +37,6 @@ B_PER_GPU, T_TOTAL, WINDOW = 16, 2048, 512
 CPU_SAMPLE_B, CPU_SAMPLE_T = 2, 2048
 WORKLOAD = "cfg1: aspin LM prefill d768 L12 H12x64 V8192, B=16 x T=2048 per GPU as four carried 512-token windows"
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the prefill kernel at the bench shape (B16 H12 T512 D64),
-# from the ncu capture summarised under profiles/; None until captured.
-NCU_TRAFFIC_BYTES = {"aspin_prefill": None}
-
 
 def peaks():
     p = ROOT / "MEASURED_PEAKS.json"
@@ -209,13 +205,14 @@ def product_arm(args):
                    "parallelism": f"batch-sharded x{world}, no data-path collective"},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": ids_host.numel() * 8,
                 "d2h_bytes_per_step": out_host.numel() * 2},
-        "gpu_launches": args.steps * CFG["layers"] * (T_TOTAL // WINDOW) * 2,     # prep + prefill per layer-window
+        # this library's kernels per step: per window and layer one fused prefill and two add+norm, plus the final norm
+        "gpu_launches": args.steps * ((T_TOTAL // WINDOW) * CFG["layers"] * 3 + 1),
         "clocks": clocks,
     }
     if rank == 0:
         pk = peaks()
         with torch.no_grad():
-            result["roofline"], result["kernels"] = kernel_rooflines(dev, pk, flush)
+            result["roofline"], result["kernels"] = kernel_rooflines(pk)
             result["decode"] = decode_numbers(model, dev, pk, args)
         if world == 1:
             toks, sec, threads = cpu_reference_time(3, 1)
@@ -228,57 +225,27 @@ def product_arm(args):
         dist.destroy_process_group()
 
 
-def kernel_rooflines(dev, pk, flush):
-    """Each hand-written kernel alone at the workload's shape: algorithmic bytes / CUDA-event time against the measured
-    HBM copy bandwidth."""
-    from pragnosia_b200 import ops, synth
+# ncu DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch of each kernel_bench case, from the captures
+# summarised under profiles/ (None = not captured). The roofline entry scales the layer_prefill figure, captured on the
+# larger-than-L2 case, to the bench window by head-tokens.
+NCU_TRAFFIC_BYTES = {"layer_prefill": None}
+
+
+def kernel_rooflines(pk):
+    """Each hand-written kernel alone on its kernel_bench case: algorithmic bytes / CUDA-event time against the measured
+    HBM copy bandwidth. The first entry is the kernel the timed step spends its carrier time in."""
+    from pragnosia_b200 import kernel_bench as kb
     out = []
-    # chunked prefill at the configuration-1 window: B16 H12 T512 D64, bf16 I/O
-    B, H, T, D = B_PER_GPU, 12, WINDOW, 64
-    x = synth.assoc_op_inputs(B, H, T, D, seed=3, with_state=True)
-    q, k, v = (x[n].to(dev).to(torch.bfloat16) for n in "qkv")
-    la, S0 = x["la"].to(dev), x["S0"].to(dev)
-    fn = lambda: ops.prefill(q, k, v, la, None, S0)
-    for _ in range(3): fn()
-    ms = event_time_ms(fn, 20, flush)
-    alg = B * H * T * (4 * D * 2 + 4) + 2 * B * H * D * D * 4            # q,k,v,o bf16 + la, state in and out
-    roof = dict(bound="hbm", achieved=alg / ms / 1e6, peak=pk["hbm_gbs"], unit="GB/s", frac=alg / ms / 1e6 / pk["hbm_gbs"],
-                traffic=NCU_TRAFFIC_BYTES["aspin_prefill"], kernel="aspin_prefill (plain rule, B16 H12 T512 D64, bf16 I/O)",
-                us_per_launch=ms * 1e3, algorithmic_bytes=alg, peak_source=pk["src"])
-    out.append(dict(roof))
-    # fused prep at the same shape
-    proj = torch.randn(B, T, 3 * H * D + 2 * H, device=dev, dtype=torch.bfloat16)
-    d = H * D
-    views = [proj[..., i * d:(i + 1) * d].unflatten(-1, (H, D)) for i in range(3)]
-    th, pos = x["theta"].to(dev), x["pos"].to(dev)
-    fn = lambda: ops.prep(*views, proj[..., 3 * d + H:3 * d + 2 * H], th, pos)
-    for _ in range(3): fn()
-    ms = event_time_ms(fn, 20, flush)
-    alg = B * H * T * D * 2 * 6
-    out.append(dict(kernel="aspin_prep (B16 T512 H12 D64, bf16)", bound="hbm", achieved=alg / ms / 1e6, peak=pk["hbm_gbs"],
-                    unit="GB/s", frac=alg / ms / 1e6 / pk["hbm_gbs"], us_per_launch=ms * 1e3, algorithmic_bytes=alg))
-    # decode step at batch 64: state read + write
-    Bd = 64
-    S = torch.randn(Bd, H, D, D, device=dev) * 0.1
-    row = torch.randn(Bd, 3 * d + 2 * H, device=dev, dtype=torch.bfloat16)
-    vs = [row[:, i * d:(i + 1) * d].unflatten(1, (H, D)) for i in range(3)]
-    A = torch.zeros(H, device=dev) - 5
-    fn = lambda: ops.decode_step(*vs, row[:, 3 * d:3 * d + H], S, th, gate=row[:, 3 * d + H:], decay_A=A, shift=1.0, S_out=S)
-    for _ in range(3): fn()
-    ms = event_time_ms(fn, 50, flush)
-    alg = 2 * Bd * H * D * D * 4 + Bd * H * D * 2 * 4
-    out.append(dict(kernel="aspin_decode_step (B64 H12 D64, in place)", bound="hbm", achieved=alg / ms / 1e6, peak=pk["hbm_gbs"],
-                    unit="GB/s", frac=alg / ms / 1e6 / pk["hbm_gbs"], us_per_launch=ms * 1e3, algorithmic_bytes=alg))
-    # per-token lambda scan on a configuration-4 slice: B8 T4096 D768 fp32 (4 x 100 MB)
-    xs = synth.lambda_scan_inputs(8, 4096, 768, seed=4)
-    u, lm, an = (xs[n].to(dev) for n in ("u", "logmag", "ang"))
-    fn = lambda: ops.lambda_scan(u, lm, an)
-    for _ in range(3): fn()
-    ms = event_time_ms(fn, 10, flush)
-    alg = u.numel() * 16
-    out.append(dict(kernel="lambda_scan (B8 T4096 D768, per-token angle)", bound="hbm", achieved=alg / ms / 1e6,
-                    peak=pk["hbm_gbs"], unit="GB/s", frac=alg / ms / 1e6 / pk["hbm_gbs"], us_per_launch=ms * 1e3,
-                    algorithmic_bytes=alg))
+    for name in ("layer_prefill_cfg1", "layer_prefill", "prefill", "prefill_d128", "prefill_delta", "prefill_delta_d64", "decode",
+                 "decode_delta", "lambda", "lambda_bcast", "prep", "add_norm"):
+        us, alg = kb.time_case(name)
+        out.append(dict(kernel=name, what=kb.CASES[name][1], bound="hbm", achieved=alg / us / 1e3, peak=pk["hbm_gbs"], unit="GB/s",
+                        frac=alg / us / 1e3 / pk["hbm_gbs"], us_per_launch=us, algorithmic_bytes=alg))
+    roof = dict(out[0])
+    big = NCU_TRAFFIC_BYTES.get("layer_prefill")
+    roof["traffic"] = None if big is None else big * (16 * 12 * 512) / (64 * 12 * 1024)
+    roof["peak_source"] = pk["src"]
+    roof["kernel"] = "prefill_tc_kernel<64, RAW> (fused layer prefill, B16 H12 T512 D64, bf16 I/O)"
     return roof, out
 
 

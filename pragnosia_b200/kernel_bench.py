@@ -25,6 +25,23 @@ def _prefill(B, H, T, D, fused=False):
     return (lambda: ops.prefill(q, k, v, la, None, S0, precision=_lib.PREFILL_TENSOR)), alg
 
 
+def _layer_prefill(B, H, T, D):
+    """The fused between-GEMMs kernel on raw projection views (what LM.forward_carried launches per layer-window)."""
+    dev = "cuda"
+    d = H * D
+    ld = (3 * d + 2 * H + 7) // 8 * 8
+    proj = torch.randn(B, T, ld, device=dev, dtype=torch.bfloat16)
+    qp, kp, vp = (proj[..., i * d:(i + 1) * d].unflatten(-1, (H, D)) for i in range(3))
+    th = synth.rope_theta(H, D).to(dev)
+    table = ops.rot_table(th, (T + 63) // 64 * 64)
+    A, w = torch.zeros(H, device=dev) - 3, torch.ones(D, device=dev)
+    S = torch.randn(B, H, D, D, device=dev) * 0.1
+    alg = B * H * T * (4 * D * 2 + 4) + 2 * B * H * D * D * 4          # q,k,v,o bf16 + two bf16 gate logits; state in and out
+    fn = lambda: ops.layer_prefill(qp, kp, vp, proj[..., 3 * d + H:3 * d + 2 * H], proj[..., 3 * d:3 * d + H], A, table, S,
+                                   theta=th, shift=float(T), rms_weight=w, rms_eps=1e-6, S_out=S)
+    return fn, alg
+
+
 def _prefill_delta(B, H, T, D):
     dev = "cuda"
     x = synth.assoc_op_inputs(B, H, T, D, seed=1, delta=True, with_state=True)
@@ -76,7 +93,10 @@ CASES = {
     "prefill": (lambda: _prefill(64, 12, 1024, 64), "aspin chunked prefill, plain rule, tensor cores: B64 H12 T1024 D64 bf16"),
     "prefill_cfg1": (lambda: _prefill(16, 12, 512, 64), "the same at one configuration-1 window: B16 H12 T512 D64"),
     "prefill_d128": (lambda: _prefill(8, 16, 2048, 128), "the same at head dim 128: B8 H16 T2048 D128"),
-    "prefill_delta": (lambda: _prefill_delta(8, 16, 1024, 128), "delta-rule chunked prefill: B8 H16 T1024 D128 bf16 I/O"),
+    "layer_prefill": (lambda: _layer_prefill(64, 12, 1024, 64), "fused layer prefill on raw projections (plumbing + scan + norm): B64 H12 T1024 D64"),
+    "layer_prefill_cfg1": (lambda: _layer_prefill(16, 12, 512, 64), "the same at one configuration-1 window: B16 H12 T512 D64"),
+    "prefill_delta": (lambda: _prefill_delta(8, 16, 1024, 128), "delta-rule chunked prefill, tensor cores: B8 H16 T1024 D128 bf16 I/O"),
+    "prefill_delta_d64": (lambda: _prefill_delta(16, 12, 1024, 64), "the same at head dim 64: B16 H12 T1024 D64"),
     "prep": (lambda: _prep(16, 512, 12, 64), "normalise / gate / rotate / transpose: B16 T512 H12 D64 bf16"),
     "decode": (lambda: _decode(64, 12, 64), "fused recurrent decode step, plain rule, in place: B64 H12 D64"),
     "decode_delta": (lambda: _decode(64, 12, 64, True), "fused recurrent decode step, delta rule, in place: B64 H12 D64"),
