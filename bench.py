@@ -148,6 +148,7 @@ def product_arm(args):
         dist.init_process_group("nccl", device_id=dev)
     torch.manual_seed(0)
     model = LM(**CFG).to(dev).to(torch.bfloat16).eval()
+    model.use_graphs = not args.eager
     ids_host = synth.token_ids(B_PER_GPU, T_TOTAL, CFG["vocab"], seed=1 + rank).pin_memory()
     ids = ids_host.to(dev)
     flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -156,11 +157,17 @@ def product_arm(args):
     def step():
         return model.forward_carried(ids, WINDOW)
 
+    copy_stream = torch.cuda.Stream(device=dev)
+
     def step_e2e(out_host):
+        """ids from pinned host memory in, logits back to pinned host memory: the upload and the pass on the compute stream,
+        the 134 MB read-back on a copy stream so that it overlaps the next step's compute (two host buffers alternate)."""
         x = ids_host.to(dev, non_blocking=True)
         lg = model.forward_carried(x, WINDOW)
-        out_host.copy_(lg, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        copy_stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(copy_stream):
+            out_host.copy_(lg, non_blocking=True)
+        lg.record_stream(copy_stream)
 
     def barrier():
         if world > 1:
@@ -181,14 +188,17 @@ def product_arm(args):
         barrier()
         clocks = sampler.stop()
         ms_step = sum(ms) / len(ms)
-        # end to end: host ids in, logits out, wall clock around the whole call (copies included)
-        out_host = torch.empty(B_PER_GPU, WINDOW, CFG["vocab"], dtype=torch.bfloat16).pin_memory()
-        for _ in range(2):
-            step_e2e(out_host)
+        # end to end: host ids in, logits out; wall clock from the first upload to the last byte of the last read-back
+        outs = [torch.empty(B_PER_GPU, WINDOW, CFG["vocab"], dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        out_host = outs[0]
+        for i in range(2):
+            step_e2e(outs[i % 2])
+        copy_stream.synchronize()
         barrier()
         t0 = time.perf_counter()
-        for _ in range(args.steps):
-            step_e2e(out_host)
+        for i in range(args.steps):
+            step_e2e(outs[i % 2])
+        copy_stream.synchronize()
         barrier()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
     t = torch.tensor([ms_step, e2e_ms], device=dev, dtype=torch.float64)
@@ -209,7 +219,9 @@ def product_arm(args):
         "gpu_launches": args.steps * ((T_TOTAL // WINDOW) * CFG["layers"] * 3 + 1),
         "clocks": clocks,
     }
-    if rank == 0:
+    if rank == 0 and args.step_only:
+        print(json.dumps(result))
+    elif rank == 0:
         pk = peaks()
         with torch.no_grad():
             result["roofline"], result["kernels"] = kernel_rooflines(pk)
@@ -228,7 +240,7 @@ def product_arm(args):
 # ncu DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch of each kernel_bench case, from the captures
 # summarised under profiles/ (None = not captured). The roofline entry scales the layer_prefill figure, captured on the
 # larger-than-L2 case, to the bench window by head-tokens.
-NCU_TRAFFIC_BYTES = {"layer_prefill": None}
+NCU_TRAFFIC_BYTES = {"layer_prefill": 328330240 + 92654336}
 
 
 def kernel_rooflines(pk):
@@ -279,6 +291,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="product", choices=["product", "reference"])
     ap.add_argument("--decode-steps", type=int, default=4096)
+    ap.add_argument("--eager", action="store_true", help="no CUDA graphs in the timed step (for a per-kernel launch list)")
+    ap.add_argument("--step-only", action="store_true", help="only the timed step: no kernel roofline, decode or CPU legs")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)

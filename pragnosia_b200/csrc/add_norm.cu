@@ -47,7 +47,7 @@ template <typename T_> __device__ __forceinline__ float round_io(float x) {
     if constexpr (sizeof(T_) == 2) return __bfloat162float(__float2bfloat16_rn(x)); else return x;
 }
 
-template <typename T_, int KIND>
+template <typename T_, int KIND, int NCH>
 __global__ void __launch_bounds__(AN_WARPS * 32)
 add_norm_kernel(const T_ *__restrict__ x, const T_ *__restrict__ delta, const T_ *__restrict__ w, const T_ *__restrict__ b,
                 float eps, T_ *__restrict__ y, T_ *__restrict__ z, long long rows, int d) {
@@ -57,10 +57,10 @@ add_norm_kernel(const T_ *__restrict__ x, const T_ *__restrict__ delta, const T_
     if (row >= rows) return;
     const int npieces = d / N;
     const size_t base = (size_t)row * d;
-    float v[AN_MAXCH][N];
+    float v[NCH][N];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int c = 0; c < AN_MAXCH; ++c) {
+    for (int c = 0; c < NCH; ++c) {
         const int pc = lane + 32 * c;
         if (pc < npieces) {
             ld_piece<T_>(v[c], x + base + (size_t)pc * N);
@@ -82,7 +82,7 @@ add_norm_kernel(const T_ *__restrict__ x, const T_ *__restrict__ delta, const T_
         mean = warp_sum(s1) / (float)d;
         float sv = 0.f;
 #pragma unroll
-        for (int c = 0; c < AN_MAXCH; ++c) {
+        for (int c = 0; c < NCH; ++c) {
             if (lane + 32 * c < npieces) {
 #pragma unroll
                 for (int i = 0; i < N; ++i) { const float t = v[c][i] - mean; sv = fmaf(t, t, sv); }
@@ -91,7 +91,7 @@ add_norm_kernel(const T_ *__restrict__ x, const T_ *__restrict__ delta, const T_
         rstd = rsqrtf(warp_sum(sv) / (float)d + eps);
     }
 #pragma unroll
-    for (int c = 0; c < AN_MAXCH; ++c) {
+    for (int c = 0; c < NCH; ++c) {
         const int pc = lane + 32 * c;
         if (pc < npieces) {
             float ww[N], bb[N], out[N];
@@ -108,11 +108,16 @@ int add_norm_launch(const void *x, const void *delta, const void *w, const void 
                     long long rows, int d, int dtype, cudaStream_t stream) {
     const long long ctas = (rows + AN_WARPS - 1) / AN_WARPS;
     if (ctas > 0x7fffffffLL) return PGB_ERR_TOO_LARGE;
-#define PGB_AN(T_, K_) add_norm_kernel<T_, K_><<<(unsigned)ctas, AN_WARPS * 32, 0, stream>>>( \
+    // 16-byte pieces per lane: 1, 2, 3, 4 or 8 (the row stays in registers, so the buffer is sized to the row)
+    const int n = dtype == PGB_BF16 ? 8 : 4, need = (d / n + 31) / 32;
+#define PGB_AN2(T_, K_, C_) add_norm_kernel<T_, K_, C_><<<(unsigned)ctas, AN_WARPS * 32, 0, stream>>>( \
         (const T_ *)x, (const T_ *)delta, (const T_ *)w, (const T_ *)b, eps, (T_ *)y, (T_ *)z, rows, d)
+#define PGB_AN(T_, K_) do { if (need <= 1) PGB_AN2(T_, K_, 1); else if (need <= 2) PGB_AN2(T_, K_, 2); else if (need <= 3) PGB_AN2(T_, K_, 3); \
+        else if (need <= 4) PGB_AN2(T_, K_, 4); else PGB_AN2(T_, K_, 8); } while (0)
     if (dtype == PGB_BF16) { if (kind == 0) PGB_AN(__nv_bfloat16, 0); else PGB_AN(__nv_bfloat16, 1); }
     else { if (kind == 0) PGB_AN(float, 0); else PGB_AN(float, 1); }
 #undef PGB_AN
+#undef PGB_AN2
     return check_launch("add_norm_kernel");
 }
 

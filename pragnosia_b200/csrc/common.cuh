@@ -38,6 +38,10 @@ __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf
 // softplus with torch's threshold (x > 20 -> x)
 __device__ __forceinline__ float softplusf_(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 
+// cheap forms for gate logits that arrive in bf16 (8 bits of mantissa): ex2/lg2-based, ~1e-6 relative
+__device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+__device__ __forceinline__ float fast_softplus(float x) { return x > 20.0f ? x : __logf(1.0f + __expf(x)); }
+
 // launch arguments shared between the C ABI layer and the kernels' translation units
 struct PrefillArgs {
     const void *q, *k, *v; const float *la, *beta, *S0; void *o; float *S_out; __nv_bfloat16 *sent;

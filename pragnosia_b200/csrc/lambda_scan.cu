@@ -40,7 +40,7 @@ __device__ __forceinline__ void st_vec(float *p, const float (&d)[VEC]) {
 }
 
 template <int VEC, int TS, bool ANG_BCAST>
-__global__ void __launch_bounds__(LS_WARPS * 32)
+__global__ void __launch_bounds__(LS_WARPS * 32, 4)
 lambda_scan_kernel(const float *__restrict__ u, const float *__restrict__ lm, const float *__restrict__ an,
                    long long an_sb, long long an_st, const float *__restrict__ h0r, const float *__restrict__ h0i,
                    float *__restrict__ y, float *__restrict__ hr_out, float *__restrict__ hi_out, int B, int T, int D) {

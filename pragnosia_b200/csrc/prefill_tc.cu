@@ -185,6 +185,7 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
         if (!RAW || p.gate_raw == nullptr || t >= T) return 0.f;
         return __bfloat162float(p.gate_raw[(size_t)b * p.aux_sb + (size_t)t * p.aux_st + h]);
     };
+    const float expA = p.decay_A != nullptr ? expf(p.decay_A[h]) : 1.f;
     float nx_own = 0.f, nx_other = 0.f, nx_gate = 0.f;
     if (warp < 2) { nx_own = fetch_decay(tid); nx_other = fetch_decay(tid ^ 32); nx_gate = fetch_gate(tid); }
 
@@ -209,10 +210,10 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
             // -softplus(gate logit) * exp(A_h) when the decay comes as logits (src/assoc.py:355-356); padding tokens: alpha = 1
             auto log_decay = [&](float raw, int r) -> float {
                 if (t0 + r >= T) return 0.f;
-                return p.la_raw != nullptr ? -softplusf_(raw) * expf(p.decay_A[h]) : raw;
+                return p.la_raw != nullptr ? -fast_softplus(raw) * expA : raw;
             };
             const float own = log_decay(nx_own, tid), other = log_decay(nx_other, tid ^ 32);
-            if (RAW) gts[tid] = p.gate_raw != nullptr ? sigmoidf_(nx_gate) : 1.f;
+            if (RAW) gts[tid] = p.gate_raw != nullptr ? fast_sigmoid(nx_gate) : 1.f;
             nx_own = fetch_decay(t0 + TC_C + tid); nx_other = fetch_decay(t0 + TC_C + (tid ^ 32)); nx_gate = fetch_gate(t0 + TC_C + tid);
             float sc = own;
 #pragma unroll
