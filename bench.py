@@ -257,7 +257,7 @@ def kernel_rooflines(pk):
     big = NCU_TRAFFIC_BYTES.get("layer_prefill")
     roof["traffic"] = None if big is None else big * (16 * 12 * 512) / (64 * 12 * 1024)
     roof["peak_source"] = pk["src"]
-    roof["kernel"] = "prefill_tc_kernel<64, RAW> (fused layer prefill, B16 H12 T512 D64, bf16 I/O)"
+    roof["kernel"] = "prefill_tc_ws_kernel<RAW> (fused layer prefill, B16 H12 T512 D64, bf16 I/O)"
     return roof, out
 
 

@@ -188,6 +188,10 @@ int pgb_add_norm(const void *x, const void *delta, const void *weight, const voi
  * Unlike every other entry point it SYNCHRONISES the device. No counterpart in the reference. */
 int pgb_tc_error_flag(int *out_host);
 
+/* Which plain-rule tensor-core kernel head dim 64 uses: 0 (default) = the warp-specialised pipeline, 1 = the single-role
+ * kernel that head dim 128 always uses. Process-wide; for A/B timing and tests. No counterpart in the reference. */
+int pgb_tc_set_variant(int variant);
+
 /* ---------------------------------------------------------------------------------------------------------
  * Rotation of channel pairs (2i, 2i+1) of x (B,H,T,D) by pos[t] * theta[h][i]; any even D.
  * Replaces src/assoc.py:34-39 rotate.   x, out: dtype, contiguous.  theta [H][D/2] fp32.  pos [T] fp32.

@@ -34,6 +34,7 @@ SIGNATURES = {
     "pgb_rot_table_build": [_vp, _vp, _i, _i, _i, _vp],
     "pgb_add_norm": [_vp, _vp, _vp, _vp, _f, _i, _vp, _vp, _ll, _i, _i, _vp],
     "pgb_tc_error_flag": [_vp],
+    "pgb_tc_set_variant": [_i],
     "pgb_rotate_pairs": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "pgb_aspin_decode_step": [_vp, _vp, _vp, _i, _ll, _i, _vp, _ll, _i, _i, _vp, _ll, _vp, _vp, _vp, _f, _vp, _vp, _vp,
                               _f, _vp, _i, _ll, _i, _i, _i, _vp],

@@ -23,6 +23,8 @@ bool prefill_tc_supported(int io_dtype, int D, bool delta);
 int decode_launch(const DecodeArgs &, int, int, int, int, cudaStream_t);
 int tc_error_flag(int *out);
 int tc_delta_error_flag(int *out);
+int tc_ws_error_flag(int *out);
+int prefill_tc_ws_launch(const PrefillArgs &, int, cudaStream_t);
 size_t prefill_tc_delta_scratch_bytes(int B, int H, int T);
 int prefill_tc_delta_launch(const PrefillArgs &, int, int, void *, cudaStream_t);
 int prefill_tc_delta_static_launch(const PrefillArgs &, int, int, cudaStream_t);
@@ -34,6 +36,14 @@ int rotate_launch(const void *, int, const float *, const float *, void *, int, 
 
 // PGB_PREFILL_AUTO sends bf16 plain-rule work to the tensor-core kernel only once this is on
 static const bool kAutoUsesTensor = true;
+
+// Plain-rule tensor-core prefill: head dim 64 runs the warp-specialised pipeline, head dim 128 the single-role kernel.
+// variant: 0 = that choice, 1 = force the single-role kernel (kept reachable for A/B timing and tests).
+static int g_tc_variant = 0;
+static int tc_dispatch(const PrefillArgs &a, int o_dtype, int D, cudaStream_t stream) {
+    if (D == 64 && g_tc_variant == 0) return prefill_tc_ws_launch(a, o_dtype, stream);
+    return prefill_tc_launch(a, o_dtype, D, stream);
+}
 
 static inline size_t esize(int dt) { return dt == PGB_BF16 ? 2 : 4; }
 static inline bool dtype_ok(int dt) { return dt == PGB_F32 || dt == PGB_BF16; }
@@ -116,7 +126,7 @@ int pgb_aspin_prefill_fwd(const void *q, const void *k, const void *v, int io_dt
     const bool tc_ok = prefill_tc_supported(io_dtype, D, beta != nullptr);
     if (precision == PGB_PREFILL_TENSOR && !tc_ok) return PGB_ERR_UNSUPPORTED_DIM;
     if (precision == PGB_PREFILL_TENSOR || (precision == PGB_PREFILL_AUTO && tc_ok && kAutoUsesTensor))
-        return prefill_tc_launch(a, o_dtype, D, (cudaStream_t)stream);
+        return tc_dispatch(a, o_dtype, D, (cudaStream_t)stream);
     return prefill_fp32_launch(a, io_dtype, o_dtype, D, (cudaStream_t)stream);
 }
 
@@ -136,7 +146,7 @@ int pgb_aspin_prefill_fused_fwd(const void *q, const void *k, const void *v, con
     PrefillArgs a{q, k, v, nullptr, nullptr, S0, o, S_out, (__nv_bfloat16 *)sent, theta, shift_dev, shift_host, B, H, T};
     a.la_raw = decay_logits; a.la_sb = decay_stride_b; a.la_st = decay_stride_t; a.decay_A = decay_A;
     a.rms_w = rms_weight; a.rms_eps = rms_eps; a.o_token_major = 1;
-    return prefill_tc_launch(a, o_dtype, D, (cudaStream_t)stream);
+    return tc_dispatch(a, o_dtype, D, (cudaStream_t)stream);
 }
 
 int pgb_aspin_layer_prefill_fwd(const void *qp, const void *kp, const void *vp, long long in_stride_b, long long in_stride_t,
@@ -158,7 +168,7 @@ int pgb_aspin_layer_prefill_fwd(const void *qp, const void *kp, const void *vp, 
     a.la_raw = decay_logits; a.la_sb = aux_stride_b; a.la_st = aux_stride_t; a.decay_A = decay_A;
     a.rms_w = rms_weight; a.rms_eps = rms_eps; a.o_token_major = 1;
     a.raw = 1; a.raw_sb = in_stride_b; a.raw_st = in_stride_t; a.gate_raw = gate_logits; a.rot = rot_table; a.rot_T = rot_T;
-    return prefill_tc_launch(a, o_dtype, D, (cudaStream_t)stream);
+    return tc_dispatch(a, o_dtype, D, (cudaStream_t)stream);
 }
 
 int pgb_rot_table_build(const float *theta, float *table, int H, int T, int D, void *stream) {
@@ -199,11 +209,20 @@ int pgb_add_norm(const void *x, const void *delta, const void *weight, const voi
     return add_norm_launch(x, delta, weight, bias, eps, kind, y, z, rows, d, dtype, (cudaStream_t)stream);
 }
 
+int pgb_tc_set_variant(int variant) {
+    if (variant != 0 && variant != 1) return PGB_ERR_BAD_SHAPE;
+    g_tc_variant = variant;
+    return PGB_OK;
+}
+
 int pgb_tc_error_flag(int *out_host) {
     if (!out_host) return PGB_ERR_NULL_POINTER;
     int a = 0, b = 0;
     int rc = tc_error_flag(&a);
     if (rc == PGB_OK) rc = tc_delta_error_flag(&b);
+    int c = 0;
+    if (rc == PGB_OK) rc = tc_ws_error_flag(&c);
+    b = b > c ? b : c;
     *out_host = a > b ? a : b;
     return rc;
 }

@@ -45,19 +45,6 @@ __device__ unsigned long long g_tc_phase[16];
 #define TC_MARK_INIT do {} while (0)
 #endif
 
-struct TcParams {
-    const float *la, *S0, *theta, *shift_dev;
-    float shift_host;
-    void *o; float *S_out; __nv_bfloat16 *sent;
-    int H, T, o_is_f32;
-    // fused layer pieces (all optional): decay gate logits instead of log-decays, per-head RMS norm of the read,
-    // token-major output
-    const __nv_bfloat16 *la_raw; long long aux_sb, aux_st; const float *decay_A;
-    const float *rms_w; float rms_eps; int o_token_major;
-    // RAW mode: write-gate logits (same strides as la_raw) and the rotation table [H][rot_T][D/2] of (cos, sin)
-    const __nv_bfloat16 *gate_raw; const float2 *rot; int rot_T;
-};
-
 template <int D>
 struct TcSmem {
     static constexpr int TILE = TC_C * D * 2;                         // one Q / K / V tile, bytes

@@ -195,4 +195,19 @@ __device__ __forceinline__ void split2(float a, float b, uint32_t &hi, uint32_t 
 }
 
 
+// kernel parameters of the plain-rule tensor-core prefill kernels
+struct TcParams {
+    const float *la, *S0, *theta, *shift_dev;
+    float shift_host;
+    void *o; float *S_out; __nv_bfloat16 *sent;
+    int H, T, o_is_f32;
+    // fused layer pieces (all optional): decay gate logits instead of log-decays, per-head RMS norm of the read,
+    // token-major output
+    const __nv_bfloat16 *la_raw; long long aux_sb, aux_st; const float *decay_A;
+    const float *rms_w; float rms_eps; int o_token_major;
+    // RAW mode: write-gate logits (same strides as la_raw) and the rotation table [H][rot_T][D/2] of (cos, sin)
+    const __nv_bfloat16 *gate_raw; const float2 *rot; int rot_T;
+};
+
+
 }  // namespace pgb

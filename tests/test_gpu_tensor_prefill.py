@@ -15,6 +15,15 @@ DEV = "cuda"
 TC = _lib.PREFILL_TENSOR
 
 
+@pytest.fixture(autouse=True, params=[0, 1], ids=["pipelined", "single-role"])
+def tc_variant(request):
+    """Every case runs on both plain-rule tensor-core kernels: the warp-specialised pipeline (head dim 64 default) and the
+    single-role kernel (always used at head dim 128)."""
+    _lib.check(_lib.lib().pgb_tc_set_variant(request.param), "pgb_tc_set_variant")
+    yield request.param
+    _lib.lib().pgb_tc_set_variant(0)
+
+
 def flag():
     out = ctypes.c_int(-1)
     _lib.check(_lib.lib().pgb_tc_error_flag(ctypes.byref(out)), "pgb_tc_error_flag")
