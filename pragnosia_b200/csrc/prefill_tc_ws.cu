@@ -516,7 +516,7 @@ __global__ void __launch_bounds__(WS_NT, 1) prefill_tc_ws_kernel(const __grid_co
             }
             if (progress) idle = 0;
             else {
-                if (++idle > TC_WAIT_LIMIT) { atomicExch(&g_tc_error, 51); break; }
+                if (++idle > (TC_WAIT_LIMIT >> 2)) { atomicExch(&g_tc_error, 51); break; }
                 __nanosleep(20);                                      // leave the issue slots to the working warps
             }
         }
@@ -561,7 +561,7 @@ __global__ void __launch_bounds__(WS_NT, 1) prefill_tc_ws_kernel(const __grid_co
             }
             if (progress) idle = 0;
             else {
-                if (++idle > TC_WAIT_LIMIT) { atomicExch(&g_tc_error, 52); break; }
+                if (++idle > (TC_WAIT_LIMIT >> 2)) { atomicExch(&g_tc_error, 52); break; }
                 __nanosleep(20);
             }
         }

@@ -8,7 +8,8 @@
 namespace pgb {
 
 constexpr int TC_C = 64;
-constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;                        // polls of a sleeping poll loop
+constexpr long long TC_WAIT_CYCLES = 1ll << 27;                      // SM cycles a blocking mbarrier wait may take
 
 // Set (to the code of the wait) when a bounded mbarrier wait inside a tensor-core kernel runs out. One copy per
 // translation unit (no relocatable device code in this build); each unit exports a reader, the C ABI takes the maximum.
@@ -70,10 +71,14 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// bounded wait: false (and the error flag set) if the barrier never flips
+// bounded wait: false (and the error flag set) if the barrier has not flipped after TC_WAIT_CYCLES of the SM clock
+// (about 70 ms; a healthy kernel waits microseconds), so a broken pipeline winds down in a fraction of a second
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
-    for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i)
-        if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    do {
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try(bar, parity)) return true;
+    } while (clock64() - t0 < TC_WAIT_CYCLES);
     atomicExch(&g_tc_error, code);
     return false;
 }

@@ -100,6 +100,7 @@ CASES = {
     "prep": (lambda: _prep(16, 512, 12, 64), "normalise / gate / rotate / transpose: B16 T512 H12 D64 bf16"),
     "decode": (lambda: _decode(64, 12, 64), "fused recurrent decode step, plain rule, in place: B64 H12 D64"),
     "decode_delta": (lambda: _decode(64, 12, 64, True), "fused recurrent decode step, delta rule, in place: B64 H12 D64"),
+    "decode_b1024": (lambda: _decode(1024, 12, 64), "the plain-rule step at a batch whose state (403 MB) exceeds L2: B1024 H12 D64"),
     "lambda": (lambda: _lambda(64, 1024, 768), "per-token lambda scan, per-token angle: B64 T1024 D768 fp32"),
     "lambda_bcast": (lambda: _lambda(64, 1024, 768, True), "per-token lambda scan, one angle per channel: B64 T1024 D768 fp32"),
     "add_norm": (lambda: _add_norm(8192, 768), "residual add + RMS norm: 8192 rows of 768 bf16"),

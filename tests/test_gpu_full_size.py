@@ -1,0 +1,131 @@
+"""The benchmark configurations at their FULL sizes on one GPU. The CPU oracle cannot run these whole, so each case checks
+(a) size-independent properties of the op -- a long call equals carried windows, exact linearity -- and (b) the literal
+per-token recurrence in fp64 on a few sampled chains of the full-length problem (sequences, heads and channels are
+independent, so a chain of the big launch is checked exactly like a small launch). Inputs are generated on the device
+from a seed. Tolerances as everywhere: output 2e-3, carried state 1e-4 (max|d| / max|ref|)."""
+import ctypes
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+import oracle
+from oracle import rel_err
+from pragnosia_b200 import ops, synth, _lib
+from pragnosia_b200.model import LM
+
+pytestmark = pytest.mark.gpu
+torch.set_grad_enabled(False)
+DEV = "cuda"
+
+
+def flag():
+    out = ctypes.c_int(-1)
+    _lib.check(_lib.lib().pgb_tc_error_flag(ctypes.byref(out)), "pgb_tc_error_flag")
+    return out.value
+
+
+def op_inputs(B, H, T, D, seed, delta):
+    """Configuration-0 distributions on the device: q, v ~ N(0,1), k L2-normalised, forget gate sigmoid(N(2,1)),
+    beta sigmoid(N(0,1)), rotation theta_i = 10000^(-2i/D) applied at positions 0..T-1; bf16 q, k, v."""
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    rn = lambda *s: torch.randn(*s, device=DEV, generator=g)
+    theta = synth.rope_theta(H, D).to(DEV)
+    pos = torch.arange(T, device=DEV, dtype=torch.float32)
+    q = ops.rotate(rn(B, H, T, D), theta, pos).to(torch.bfloat16)
+    k = ops.rotate(F.normalize(rn(B, H, T, D), dim=-1), theta, pos).to(torch.bfloat16)
+    v = rn(B, H, T, D).to(torch.bfloat16)
+    la = F.logsigmoid(2.0 + rn(B, H, T))
+    beta = torch.sigmoid(rn(B, H, T)) if delta else None
+    return q, k, v, la, beta
+
+
+def chain(t, b, h):
+    return t[b:b + 1, h:h + 1].double().cpu()
+
+
+def test_config3_delta_rule_full_size():
+    """B=8, T=8192, H=16, d=128, chunk 64, bf16 inputs, fp32 state: one call equals two carried halves, and three
+    sampled chains match the exact sequential delta-rule recurrence (fp64, CPU)."""
+    B, H, T, D = 8, 16, 8192, 128
+    q, k, v, la, be = op_inputs(B, H, T, D, seed=3, delta=True)
+    o, S, _ = ops.prefill(q, k, v, la, be, None, out_dtype=torch.float32)
+    assert torch.isfinite(o).all() and torch.isfinite(S).all() and flag() == 0
+    h = T // 2
+    o1, S1, _ = ops.prefill(q[:, :, :h], k[:, :, :h], v[:, :, :h], la[:, :, :h], be[:, :, :h], None, out_dtype=torch.float32)
+    o2, S2, _ = ops.prefill(q[:, :, h:], k[:, :, h:], v[:, :, h:], la[:, :, h:], be[:, :, h:], S1, out_dtype=torch.float32)
+    assert rel_err(torch.cat([o1, o2], 2), o) <= 1e-5 and rel_err(S2, S) <= 1e-5
+    for b, hh in ((0, 0), (3, 7), (7, 15)):
+        ro, rS = oracle.delta_literal(chain(q, b, hh), chain(k, b, hh), chain(v, b, hh), chain(la, b, hh), chain(be, b, hh))
+        eo, es = rel_err(o[b:b + 1, hh:hh + 1].double().cpu(), ro), rel_err(S[b:b + 1, hh:hh + 1].double().cpu(), rS)
+        assert eo <= 2e-3 and es <= 1e-4, f"chain ({b},{hh}): o {eo:.2e} S {es:.2e}"
+
+
+def test_config4_aspin_prefill_shard_full_length():
+    """The long-context aspin prefill (B=64, T=32768, H=12, d=64, bf16) at the batch shard one of eight GPUs gets (B=8):
+    one 32768-token call equals four carried 8192-token windows, and two sampled chains match the literal recurrence."""
+    B, H, T, D = 8, 12, 32768, 64
+    q, k, v, la, _ = op_inputs(B, H, T, D, seed=4, delta=False)
+    o, S, _ = ops.prefill(q, k, v, la, None, None, precision=_lib.PREFILL_TENSOR)
+    assert o.dtype == torch.bfloat16 and torch.isfinite(o.float()).all() and flag() == 0
+    St, outs, W = None, [], T // 4
+    for w in range(4):
+        sl = slice(w * W, (w + 1) * W)
+        ow, St, _ = ops.prefill(q[:, :, sl], k[:, :, sl], v[:, :, sl], la[:, :, sl], None, St, precision=_lib.PREFILL_TENSOR)
+        outs.append(ow)
+    assert rel_err(torch.cat(outs, 2).float(), o.float()) <= 1e-5 and rel_err(St, S) <= 1e-5
+    for b, hh in ((0, 0), (7, 11)):
+        ro, rS = oracle.plain_literal(chain(q, b, hh), chain(k, b, hh), chain(v, b, hh), chain(la, b, hh))
+        eo = rel_err(o[b:b + 1, hh:hh + 1].double().cpu(), ro)                 # bf16 output: half an ulp of 2^-8
+        es = rel_err(S[b:b + 1, hh:hh + 1].double().cpu(), rS)
+        assert eo <= 4e-3 and es <= 1e-4, f"chain ({b},{hh}): o {eo:.2e} S {es:.2e}"
+
+
+def test_config4_lambda_scan_shard_full_length():
+    """The fspin per-token lambda scan (B=64, T=32768, D=768 complex channels, fp32) at the B=8 shard of one of eight
+    GPUs: exact homogeneity (scan(2u) = 2 scan(u) bit for bit), two carried halves equal one call, and sampled
+    (sequence, channel) chains match the literal sequential recurrence in fp64."""
+    B, T, D = 8, 32768, 768
+    g = torch.Generator(device=DEV).manual_seed(5)
+    logmag = (0.9 + 0.099 * torch.rand(B, T, D, device=DEV, generator=g)).log()
+    ang = math.pi * torch.rand(B, T, D, device=DEV, generator=g)
+    u = torch.randn(B, T, D, device=DEV, generator=g) * (0.1 * torch.randn(D, device=DEV, generator=g))
+    y, (hr, hi) = ops.lambda_scan(u, logmag, ang)
+    assert torch.isfinite(y).all()
+    y2, (hr2, hi2) = ops.lambda_scan(2.0 * u, logmag, ang)
+    assert torch.equal(y2, 2.0 * y) and torch.equal(hr2, 2.0 * hr) and torch.equal(hi2, 2.0 * hi)
+    del y2
+    h = T // 2
+    ya, ha = ops.lambda_scan(u[:, :h], logmag[:, :h], ang[:, :h])
+    yb, hb = ops.lambda_scan(u[:, h:], logmag[:, h:], ang[:, h:], h0=ha)
+    assert rel_err(torch.cat([ya, yb], 1), y) <= 1e-5 and rel_err(hb[0], hr) <= 1e-5 and rel_err(hb[1], hi) <= 1e-5
+    del ya, yb
+    for b, c0 in ((0, 0), (5, 381), (7, 760)):
+        cs = slice(c0, c0 + 8)
+        ry, (rr, ri) = oracle.lambda_literal(u[b:b + 1, :, cs].double().cpu(), logmag[b:b + 1, :, cs].double().cpu(),
+                                             ang[b:b + 1, :, cs].double().cpu())
+        assert rel_err(y[b:b + 1, :, cs].double().cpu(), ry) <= 1e-5
+        assert rel_err(hr[b:b + 1, cs].double().cpu(), rr) <= 1e-4 and rel_err(hi[b:b + 1, cs].double().cpu(), ri) <= 1e-4
+
+
+def test_config1_lm_prefill_full_size_rows():
+    """The timed configuration itself: d=768, 12 layers, 12 heads x 64, vocabulary 8192, bf16 weights, fp32 state,
+    B=16 x T=2048 as four carried 512-token windows. Rows of the batch are independent, so two rows are checked against
+    the fp32 oracle run on the same bf16-rounded weights (bf16 activations bound the agreement, as in the small case),
+    and the rows' results do not depend on what else is in the batch."""
+    cfg = oracle.lm_config(vocab=8192, d=768, layers=12, mlp_mult=4, ctx=512, mixer="aspin", norm="rms")
+    P = oracle.init_lm_params(cfg, seed=1)
+    m = LM(vocab=8192, d=768, layers=12, mlp_mult=4, ctx=512, mixer="aspin", norm="rms")
+    m.load_state_dict(P, strict=True)
+    m = m.to(DEV).to(torch.bfloat16).eval()
+    ids = synth.token_ids(16, 2048, 8192, seed=21)
+    lg, states = m.forward_carried(ids.to(DEV), return_states=True)
+    assert tuple(lg.shape) == (16, 512, 8192) and states[0][0].dtype == torch.float32 and flag() == 0
+    rows = [0, 11]
+    Pb = {k: v.to(torch.bfloat16).float() for k, v in P.items()}
+    ref, rstates = oracle.lm_prefill(Pb, cfg, ids[rows])
+    assert rel_err(lg[rows].float().cpu(), ref) <= 3e-2
+    assert rel_err(states[0][0][rows].cpu(), rstates[0][0]) <= 3e-2
+    lg2 = m.forward_carried(ids[rows].to(DEV))
+    assert rel_err(lg2.float(), lg[rows].float()) <= 2e-2                      # GEMM tiling may differ with the batch size
