@@ -1,7 +1,8 @@
 // Per-token complex recurrence h_t = lambda_t h_{t-1} + u_t as a chunked parallel scan.
 //
-// Layout in HBM: u, logmag, y are [B][T][D] fp32 with D contiguous. The kernel is HBM-bound: 12 B read (8 B when
-// the angle is one value per channel) and 4 B written per (b,t,d) element.
+// Layout in HBM: u, logmag, y are [B][T][D] fp32 with D contiguous: 12 B read (8 B when the angle is one value per
+// channel) and 4 B written per (b,t,d) element. Measured, the kernel is bound by instruction issue before HBM (accurate
+// expf and sincosf per element), so the tile is kept small (SEG = 4 steps a lane) for 24 resident warps per SM.
 //
 // Work split. A lane owns VEC adjacent channels (VEC = 4: one 128-bit access). A warp is TS time-segments x CQ
 // channel groups (TS * CQ = 32): lanes of one segment read 16*CQ contiguous bytes of one time row, so every 128-byte
@@ -18,8 +19,10 @@
 
 namespace pgb {
 
-constexpr int LS_SEG = 8;
+constexpr int LS_SEG_VEC4 = 4;      // steps a lane owns per tile, 128-bit path: 12 values x 4 channels x 4 steps in registers
+constexpr int LS_SEG_VEC1 = 8;      // scalar path (D not a multiple of 4, or unaligned)
 constexpr int LS_WARPS = 4;
+constexpr int LS_CTAS_PER_SM = 6;   // 24 warps an SM = 6 a scheduler, whose 16 K registers then allow 80 a thread
 
 template <int VEC>
 __device__ __forceinline__ void ld_vec(float (&d)[VEC], const float *p) {
@@ -39,8 +42,8 @@ __device__ __forceinline__ void st_vec(float *p, const float (&d)[VEC]) {
     }
 }
 
-template <int VEC, int TS, bool ANG_BCAST>
-__global__ void __launch_bounds__(LS_WARPS * 32, 4)
+template <int VEC, int TS, bool ANG_BCAST, int SEG>
+__global__ void __launch_bounds__(LS_WARPS * 32, TS == 32 ? LS_CTAS_PER_SM - 1 : LS_CTAS_PER_SM)   // 32 segments are chosen when warps are scarce: registers over occupancy
 lambda_scan_kernel(const float *__restrict__ u, const float *__restrict__ lm, const float *__restrict__ an,
                    long long an_sb, long long an_st, const float *__restrict__ h0r, const float *__restrict__ h0i,
                    float *__restrict__ y, float *__restrict__ hr_out, float *__restrict__ hi_out, int B, int T, int D) {
@@ -76,12 +79,12 @@ lambda_scan_kernel(const float *__restrict__ u, const float *__restrict__ lm, co
     }
 
     const size_t row0 = (size_t)b * T;
-    for (int t0 = 0; t0 < T; t0 += TS * LS_SEG) {
-        const int tb = t0 + seg * LS_SEG;
-        float c[LS_SEG][VEC], s[LS_SEG][VEC], x[LS_SEG][VEC];
+    for (int t0 = 0; t0 < T; t0 += TS * SEG) {
+        const int tb = t0 + seg * SEG;
+        float c[SEG][VEC], s[SEG][VEC], x[SEG][VEC];
         // 1. loads first, all of them
 #pragma unroll
-        for (int i = 0; i < LS_SEG; ++i) {
+        for (int i = 0; i < SEG; ++i) {
             const int t = tb + i;
             if (live && t < T) {
                 const size_t off = (row0 + t) * D + d0;
@@ -95,7 +98,7 @@ lambda_scan_kernel(const float *__restrict__ u, const float *__restrict__ lm, co
         }
         // c, s of every step; steps past the end are the identity map
 #pragma unroll
-        for (int i = 0; i < LS_SEG; ++i) {
+        for (int i = 0; i < SEG; ++i) {
             const bool ok = live && (tb + i) < T;
 #pragma unroll
             for (int v = 0; v < VEC; ++v) {
@@ -114,7 +117,7 @@ lambda_scan_kernel(const float *__restrict__ u, const float *__restrict__ lm, co
 #pragma unroll
             for (int v = 0; v < VEC; ++v) { Ar[v] = 1.f; Ai[v] = 0.f; Br[v] = 0.f; Bi[v] = 0.f; }
 #pragma unroll
-            for (int i = 0; i < LS_SEG; ++i) {
+            for (int i = 0; i < SEG; ++i) {
 #pragma unroll
                 for (int v = 0; v < VEC; ++v) {
                     const float nbr = c[i][v] * Br[v] - s[i][v] * Bi[v] + x[i][v];
@@ -158,7 +161,7 @@ lambda_scan_kernel(const float *__restrict__ u, const float *__restrict__ lm, co
         }
         // 4. replay in the reference's order and store Re h
 #pragma unroll
-        for (int i = 0; i < LS_SEG; ++i) {
+        for (int i = 0; i < SEG; ++i) {
             const int t = tb + i;
             float out[VEC];
 #pragma unroll
@@ -197,7 +200,7 @@ DevInfo dev_info() {
     d.ok = true; return d;
 }
 
-template <int VEC, int TS>
+template <int VEC, int TS, int SEG>
 int launch_ts(const float *u, const float *lm, const float *an, long long sb, long long st, const float *h0r,
               const float *h0i, float *y, float *hro, float *hio, int B, int T, int D, cudaStream_t stream) {
     constexpr int CQ = 32 / TS;
@@ -206,36 +209,50 @@ int launch_ts(const float *u, const float *lm, const float *an, long long sb, lo
     const long long ctas = (warps + LS_WARPS - 1) / LS_WARPS;
     if (ctas > 0x7fffffffLL) return PGB_ERR_TOO_LARGE;
     if (sb == 0 && st == 0)
-        lambda_scan_kernel<VEC, TS, true><<<(unsigned)ctas, LS_WARPS * 32, 0, stream>>>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D);
+        lambda_scan_kernel<VEC, TS, true, SEG><<<(unsigned)ctas, LS_WARPS * 32, 0, stream>>>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D);
     else
-        lambda_scan_kernel<VEC, TS, false><<<(unsigned)ctas, LS_WARPS * 32, 0, stream>>>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D);
+        lambda_scan_kernel<VEC, TS, false, SEG><<<(unsigned)ctas, LS_WARPS * 32, 0, stream>>>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D);
     return check_launch("lambda_scan_kernel");
 }
 
-template <int VEC>
+template <int VEC, int SEG>
 int launch_vec(int ts, const float *u, const float *lm, const float *an, long long sb, long long st, const float *h0r,
                const float *h0i, float *y, float *hro, float *hio, int B, int T, int D, cudaStream_t stream) {
     switch (ts) {
-        case 1:  return launch_ts<VEC, 1>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
-        case 2:  return launch_ts<VEC, 2>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
-        case 4:  return launch_ts<VEC, 4>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
-        case 8:  return launch_ts<VEC, 8>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
-        case 16: return launch_ts<VEC, 16>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
-        default: return launch_ts<VEC, 32>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
+        case 1:  return launch_ts<VEC, 1, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
+        case 2:  return launch_ts<VEC, 2, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
+        case 4:  return launch_ts<VEC, 4, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
+        case 8:  return launch_ts<VEC, 8, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
+        case 16: return launch_ts<VEC, 16, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
+        default: return launch_ts<VEC, 32, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
     }
 }
 
 }  // namespace
 
-// Number of time segments per warp: the smallest power of two that gives every SM about two resident CTAs' worth of
-// warps, never more segments than the sequence has SEG-step pieces. `force_ts` > 0 overrides (tests).
+// Number of time segments per warp. The kernel is bound by instruction issue (about 80 instructions per element with a
+// per-token angle), every warp walks its whole time axis, and all warps of a launch take the same time, so the launch
+// lasts rounds x tiles-per-warp x tile cost with rounds = ceil(warps / resident warps). More segments shorten a warp's
+// walk but cost shuffle-scan rounds and, past the resident capacity, a whole extra round. Take the power of two with the
+// smallest estimate. `force_ts` > 0 overrides (tests).
 int lambda_scan_pick_ts(int B, int T, int D, int vec, int sms, int force_ts) {
     if (force_ts > 0) return force_ts;
+    const int seg = vec == 4 ? LS_SEG_VEC4 : LS_SEG_VEC1;
     const int ngroups = (D + vec - 1) / vec;
-    const long long want_lanes = (long long)sms * 3 * LS_WARPS * 32 * 2;     // ~3 CTAs per SM resident, two rounds
-    int ts = 1;
-    while (ts < 32 && (long long)B * ngroups * ts < want_lanes && ts * LS_SEG < T) ts <<= 1;
-    return ts;
+    const long long cap = (long long)sms * LS_CTAS_PER_SM * LS_WARPS;           // resident warps
+    int best = 1;
+    double best_cost = 0.0;
+    for (int ts = 1, lg = 0; ts <= 32; ts <<= 1, ++lg) {
+        if (ts > 1 && (ts / 2) * seg >= T) break;                               // the sequence has no more pieces to hand out
+        const int cq = 32 / ts;
+        const long long warps = (long long)B * ((ngroups + cq - 1) / cq);
+        const long long rounds = (warps + cap - 1) / cap;
+        const long long tiles = (T + ts * seg - 1) / (ts * seg);
+        const double tile = seg * 60.0 + lg * 14.0 + 12.0;                      // per lane and channel: steps, scan rounds, hand-over
+        const double cost = (double)rounds * (double)tiles * tile;
+        if (ts == 1 || cost < best_cost) { best = ts; best_cost = cost; }
+    }
+    return best;
 }
 
 int lambda_scan_launch(const float *u, const float *lm, const float *an, long long sb, long long st, const float *h0r,
@@ -247,8 +264,8 @@ int lambda_scan_launch(const float *u, const float *lm, const float *an, long lo
                     aligned(hro, 16) && aligned(hio, 16) && (h0r == nullptr || (aligned(h0r, 16) && aligned(h0i, 16))) &&
                     (sb % 4 == 0) && (st % 4 == 0);
     const int ts = lambda_scan_pick_ts(B, T, D, v4 ? 4 : 1, sms, force_ts);
-    return v4 ? launch_vec<4>(ts, u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream)
-              : launch_vec<1>(ts, u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
+    return v4 ? launch_vec<4, LS_SEG_VEC4>(ts, u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream)
+              : launch_vec<1, LS_SEG_VEC1>(ts, u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
 }
 
 }  // namespace pgb
