@@ -153,6 +153,23 @@ __global__ void __launch_bounds__(128) delta_inv_kernel(const __grid_constant__ 
 }
 
 // ------------------------------------------------------------------------------------------------ the chunk walk
+// Phase timing for tuning builds only (-DPGB_TC_TIMING): CTA (0,0) accumulates clock64() deltas per phase.
+#ifdef PGB_TC_TIMING
+__device__ unsigned long long g_td_phase[16];
+#define TD_MARK(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) { const long long now_ = clock64(); \
+        atomicAdd(&g_td_phase[i], (unsigned long long)(now_ - tmark_)); tmark_ = now_; } } while (0)
+#define TD_MARK_INIT long long tmark_ = clock64()
+int td_phase_dump(unsigned long long *out16) {
+    unsigned long long zero[16] = {};
+    cudaMemcpyFromSymbol(out16, g_td_phase, sizeof(zero));
+    cudaMemcpyToSymbol(g_td_phase, zero, sizeof(zero));
+    return 0;
+}
+#else
+#define TD_MARK(i) do {} while (0)
+#define TD_MARK_INIT do {} while (0)
+#endif
+
 struct TdParams {
     const float *la, *beta, *S0, *theta, *shift_dev;
     float shift_host;
@@ -175,7 +192,7 @@ struct TdSmem {
     static constexpr int off_sh = off_wl + SQ;                        // S slice [D key rows][64 value columns]
     static constexpr int off_sl = off_sh + D * 128;
     static constexpr int off_misc = off_sl + D * 128;
-    static constexpr int bytes = off_misc + 2048 + 1024;
+    static constexpr int bytes = off_misc + 3072 + 1024;             // barriers, tensor-memory slot, two statistics slots
 };
 
 template <int D>
@@ -192,8 +209,7 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *sm = smem_raw + (base - smem_u32(smem_raw));
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + SM::off_misc + 64);
-    float *Ls = reinterpret_cast<float *>(sm + SM::off_misc + 128);
-    float *eLs = Ls + 64, *wts = eLs + 64, *bes = wts + 64;
+    float *stats = reinterpret_cast<float *>(sm + SM::off_misc + 128);    // [2 chunks][L, e^L, w, beta][64]
     const uint32_t bar_full0 = base + SM::off_misc, bar_full1 = bar_full0 + 8, bar_a = bar_full0 + 16, bar_b = bar_full0 + 24,
                    bar_c = bar_full0 + 32;
 
@@ -204,7 +220,7 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
     const float *la = p.la + (size_t)bh * T, *beta = p.beta + (size_t)bh * T;
 
     if (tid == 0) {
-        mbar_init(bar_full0, 1); mbar_init(bar_full1, 1); mbar_init(bar_a, 1); mbar_init(bar_b, 1); mbar_init(bar_c, 1);
+        mbar_init(bar_full0, 1); mbar_init(bar_full1, 1); mbar_init(bar_a, 3); mbar_init(bar_b, 1); mbar_init(bar_c, 2);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) tmem_alloc(smem_u32(tmem_slot), TM_COLS);
@@ -263,14 +279,23 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
     };
     bool ok = true;
     if (tid == 0) load_stage(0, 0);
+    // The decay statistics do not depend on the state: warps 6 and 7, idle while a tensor-core round is in flight, prepare
+    // the next chunk's one iteration ahead (a global load plus a dependent shuffle scan, ~2.5k cycles otherwise exposed).
+    auto stats_of = [&](int c) {
+        float *L = stats + (c & 1) * 256;
+        chunk_stats(la, beta, c * TC_C, T, tid - 192, lane, warp - 6, L, L + 64, L + 128, L + 192);
+    };
+    if (warp >= 6) stats_of(0);
+    TD_MARK_INIT;
 
     for (int c = 0; c < NC && ok; ++c) {
         const int t0 = c * TC_C, st = c & 1;
+        TD_MARK(0);
         const uint32_t sb = base + SM::off_stage + st * SM::STAGE;
         const uint32_t qs = sb, ks = sb + SM::QK, vs = sb + 2 * SM::QK, xh = vs + SM::SQ, xl = xh + SM::SQ;
         uint8_t *ks_ptr = sm + SM::off_stage + st * SM::STAGE + SM::QK, *vs_ptr = ks_ptr + SM::QK;
         if (tid == 0 && c + 1 < NC) load_stage(c + 1, st ^ 1);
-        if (warp < 2) chunk_stats(la, beta, t0, T, tid, lane, warp, Ls, eLs, wts, bes);
+        const float *Ls = stats + (c & 1) * 256, *eLs = Ls + 64, *wts = eLs + 64, *bes = wts + 64;
         // ---- entering state slice as an MN-major B operand (rows = key index), head and tail
         {
 #pragma unroll
@@ -290,8 +315,10 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
                     }
                 }
         }
+        TD_MARK(1);
         if (!mbar_wait(st ? bar_full1 : bar_full0, (c >> 1) & 1, 21)) ok = false;
         __syncthreads();
+        TD_MARK(2);
         const float aC = expf(Ls[TC_C - 1]);
         // ---- K * w, head and tail, in K's own layout (an MN-major A operand)
         if (ok) {
@@ -313,30 +340,40 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
+        TD_MARK(3);
         // ---- round 1: P = Q K^T, KS = K S, O2 = Q S
         const uint64_t dsh = smem_desc(base + SM::off_sh, 16, 1024), dsl = smem_desc(base + SM::off_sl, 16, 1024);
-        if (tid == 0 && ok) {
+        // Everyone waits for the round, so issue time counts: the three products go out from three warps (one accumulator
+        // each, so no ordering between them is needed), each through one elected lane of the converged warp, which keeps the
+        // descriptors in the uniform datapath (measured: about 33 cycles per tcgen05.mma against 65-100 from a lone thread).
+        if (warp < 3 && __all_sync(0xffffffffu, ok)) {                // whole warps, converged: one elected lane each issues
             tc_fence_after();
             constexpr uint32_t I_P = idesc_bf16(64, 64, 0, 0), I_S = idesc_bf16(64, 64, 0, 1);
             const uint64_t dq = smem_desc(qs, 16, 1024), dk = smem_desc(ks, 16, 1024);
+            if (warp == 0) {
 #pragma unroll
-            for (int k = 0; k < D / 16; ++k) {
-                const uint32_t ko = ((uint32_t)(k >> 2) * 8192u + (uint32_t)(k & 3) * 32u) >> 4;
-                mma_bf16(tmem + TM_P, dq + ko, dk + ko, I_P, k > 0);
-            }
-#pragma unroll
-            for (int half = 0; half < 2; ++half)
-#pragma unroll
-                for (int k = 0; k < D / 16; ++k) {                    // S rows (key index) advance 16 rows = 2048 B per step
+                for (int k = 0; k < D / 16; ++k) {
                     const uint32_t ko = ((uint32_t)(k >> 2) * 8192u + (uint32_t)(k & 3) * 32u) >> 4;
-                    const uint64_t ds = (half ? dsl : dsh) + k * 128;
-                    mma_bf16(tmem + TM_KS, dk + ko, ds, I_S, half | (k > 0));
-                    mma_bf16(tmem + TM_O2, dq + ko, ds, I_S, half | (k > 0));
+                    mma_bf16_elect(tmem + TM_P, dq + ko, dk + ko, I_P, k > 0);
                 }
-            mma_commit(bar_a);
+            } else {
+                const uint64_t da = warp == 1 ? dk : dq;
+                const uint32_t acc = warp == 1 ? TM_KS : TM_O2;
+#pragma unroll
+                for (int half = 0; half < 2; ++half)
+#pragma unroll
+                    for (int k = 0; k < D / 16; ++k) {                // S rows (key index) advance 16 rows = 2048 B per step
+                        const uint32_t ko = ((uint32_t)(k >> 2) * 8192u + (uint32_t)(k & 3) * 32u) >> 4;
+                        mma_bf16_elect(tmem + acc, da + ko, (half ? dsl : dsh) + k * 128, I_S, half | (k > 0));
+                    }
+            }
+            mma_commit_elect(bar_a);
         }
+        TD_MARK(4);
+        if (warp >= 6 && c + 1 < NC) stats_of(c + 1);
         if (ok && !mbar_wait(bar_a, c & 1, 22)) ok = false;
         tc_fence_after();
+        TD_MARK(5);
         if (ok) {
             // ---- A = P * decay (causal), head and tail; rhs = beta (V - e^{L_t} K S), head and tail
             float pv[16], kv[16];
@@ -371,22 +408,25 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
+        TD_MARK(6);
         // ---- round 2: W = X rhs  (head*head + head*tail + tail*head)
         const uint64_t dwh = smem_desc(base + SM::off_wh, 16, 1024), dwl = smem_desc(base + SM::off_wl, 16, 1024);
-        if (tid == 0 && ok) {
+        if (warp == 0 && __all_sync(0xffffffffu, ok)) {               // the whole warp, converged: one elected lane issues
             tc_fence_after();
             constexpr uint32_t I_W = idesc_bf16(64, 64, 0, 1);
             const uint64_t dxh = smem_desc(xh, 16, 1024), dxl = smem_desc(xl, 16, 1024);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) mma_bf16(tmem + TM_KS, dxh + k * 2, dwh + k * 128, I_W, k > 0);
+            for (int k = 0; k < 4; ++k) mma_bf16_elect(tmem + TM_KS, dxh + k * 2, dwh + k * 128, I_W, k > 0);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) mma_bf16(tmem + TM_KS, dxh + k * 2, dwl + k * 128, I_W, 1);
+            for (int k = 0; k < 4; ++k) mma_bf16_elect(tmem + TM_KS, dxh + k * 2, dwl + k * 128, I_W, 1);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) mma_bf16(tmem + TM_KS, dxl + k * 2, dwh + k * 128, I_W, 1);
-            mma_commit(bar_b);
+            for (int k = 0; k < 4; ++k) mma_bf16_elect(tmem + TM_KS, dxl + k * 2, dwh + k * 128, I_W, 1);
+            mma_commit_elect(bar_b);
         }
+        TD_MARK(7);
         if (ok && !mbar_wait(bar_b, c & 1, 23)) ok = false;
         tc_fence_after();
+        TD_MARK(8);
         if (ok) {
             // ---- W back to shared memory (over rhs), head and tail
             float wv[16];
@@ -405,28 +445,34 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
+        TD_MARK(9);
         // ---- round 3: O1 = A W, U = (K w)^T W
-        if (tid == 0 && ok) {
+        if (warp < 2 && __all_sync(0xffffffffu, ok)) {                // O1 from one warp's elected lane, U from another's
             tc_fence_after();
             constexpr uint32_t I_O = idesc_bf16(64, 64, 0, 1), I_U = idesc_bf16(D, 64, 1, 1);
-            const uint64_t dah = smem_desc(base + SM::off_ah, 16, 1024), dal = smem_desc(base + SM::off_al, 16, 1024);
-            const uint64_t dkwh = smem_desc(base + SM::off_kwh, 8192, 1024), dkwl = smem_desc(base + SM::off_kwl, 8192, 1024);
+            if (warp == 0) {
+                const uint64_t dah = smem_desc(base + SM::off_ah, 16, 1024), dal = smem_desc(base + SM::off_al, 16, 1024);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) mma_bf16(tmem + TM_O1, dah + k * 2, dwh + k * 128, I_O, k > 0);
+                for (int k = 0; k < 4; ++k) mma_bf16_elect(tmem + TM_O1, dah + k * 2, dwh + k * 128, I_O, k > 0);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) mma_bf16(tmem + TM_O1, dah + k * 2, dwl + k * 128, I_O, 1);
+                for (int k = 0; k < 4; ++k) mma_bf16_elect(tmem + TM_O1, dah + k * 2, dwl + k * 128, I_O, 1);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) mma_bf16(tmem + TM_O1, dal + k * 2, dwh + k * 128, I_O, 1);
+                for (int k = 0; k < 4; ++k) mma_bf16_elect(tmem + TM_O1, dal + k * 2, dwh + k * 128, I_O, 1);
+            } else {
+                const uint64_t dkwh = smem_desc(base + SM::off_kwh, 8192, 1024), dkwl = smem_desc(base + SM::off_kwl, 8192, 1024);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) mma_bf16(tmem + TM_KS, dkwh + k * 128, dwh + k * 128, I_U, k > 0);
+                for (int k = 0; k < 4; ++k) mma_bf16_elect(tmem + TM_KS, dkwh + k * 128, dwh + k * 128, I_U, k > 0);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) mma_bf16(tmem + TM_KS, dkwh + k * 128, dwl + k * 128, I_U, 1);
+                for (int k = 0; k < 4; ++k) mma_bf16_elect(tmem + TM_KS, dkwh + k * 128, dwl + k * 128, I_U, 1);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) mma_bf16(tmem + TM_KS, dkwl + k * 128, dwh + k * 128, I_U, 1);
-            mma_commit(bar_c);
+                for (int k = 0; k < 4; ++k) mma_bf16_elect(tmem + TM_KS, dkwl + k * 128, dwh + k * 128, I_U, 1);
+            }
+            mma_commit_elect(bar_c);
         }
+        TD_MARK(10);
         if (ok && !mbar_wait(bar_c, c & 1, 24)) ok = false;
         tc_fence_after();
+        TD_MARK(11);
         if (ok) {
             float ov[16], o2v[16], uv[NSG][16];
             tmem_ld_frag4(tmem + lane_base + TM_O1 + col0, ov);
@@ -457,6 +503,7 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
         }
         tc_fence_before();
         __syncthreads();
+        TD_MARK(12);
     }
     if (ok) {
 #pragma unroll
