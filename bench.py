@@ -240,7 +240,7 @@ def product_arm(args):
 # ncu DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch of each kernel_bench case, from the captures
 # summarised under profiles/ (None = not captured). The roofline entry scales the layer_prefill figure, captured on the
 # larger-than-L2 case, to the bench window by head-tokens.
-NCU_TRAFFIC_BYTES = {"layer_prefill": 328330240 + 92654336}
+NCU_TRAFFIC_BYTES = {"layer_prefill": 324200448 + 91691520}
 
 
 def kernel_rooflines(pk):

@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(WS_NT, 1) prefill_tc_ws_kernel(const __grid_co
             if constexpr (RAW) {
                 const float2 *rot_sm = reinterpret_cast<const float2 *>(sm + SM::off_rot + s2 * ROT_BYTES);
                 const int cp = lane & 7;
-#pragma unroll
+#pragma unroll 1                                                      // rolled: five roles share the instruction cache
                 for (int pass = 0; pass < 2; ++pass) {
                     // every load of the pass first: the stores below may alias anything as far as the compiler can tell,
                     // and would otherwise chain the three tiles one behind the other
