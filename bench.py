@@ -284,6 +284,120 @@ def decode_numbers(model, dev, pk, args):
     return res
 
 
+CFG4 = dict(B=64, T=32768, H=12, D=64, DS=768, window=4096)
+
+
+def long_context_arm(args):
+    """Configuration 4 (a second workload, not the headline): the fspin per-token lambda scan (B=64, T=32768, D=768 complex
+    channels, fp32) and the aspin prefill (B=64, T=32768, H=12, d=64, bf16), partitioned by batch over the ranks (STRONG
+    scaling: the whole job is fixed), walked in 4096-token windows with the state carried. Timed twice: compute only, and
+    with every window's output all-gathered over NVLink behind a side stream while the next window computes."""
+    import math
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from pragnosia_b200 import ops, sharded, synth, _lib
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product arm has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    c = CFG4
+    b0, b1 = sharded.shard_range(c["B"], rank, world)
+    Bl = b1 - b0
+    g = torch.Generator(device=dev).manual_seed(4 + rank)
+    rn = lambda *sh: torch.randn(*sh, device=dev, generator=g)
+    with torch.no_grad():
+        theta = synth.rope_theta(c["H"], c["D"]).to(dev)
+        pos = torch.arange(c["T"], device=dev, dtype=torch.float32) % c["window"]
+        q = ops.rotate(rn(Bl, c["H"], c["T"], c["D"]), theta, pos).to(torch.bfloat16)
+        k = ops.rotate(F.normalize(rn(Bl, c["H"], c["T"], c["D"]), dim=-1), theta, pos).to(torch.bfloat16)
+        v = rn(Bl, c["H"], c["T"], c["D"]).to(torch.bfloat16)
+        la = F.logsigmoid(2.0 + rn(Bl, c["H"], c["T"]))
+        logmag = (0.9 + 0.099 * torch.rand(Bl, c["T"], c["DS"], device=dev, generator=g)).log()
+        ang = math.pi * torch.rand(Bl, c["T"], c["DS"], device=dev, generator=g)
+        u = rn(Bl, c["T"], c["DS"]) * (0.1 * rn(c["DS"]))
+
+        # a window of a (B, T, ...) tensor is not contiguous; the windows are laid out once, outside the timed region,
+        # as a streaming caller would hand them over
+        W = c["window"]
+        nw = c["T"] // W
+        split = lambda t, dim: [t.narrow(dim, w * W, W).contiguous() for w in range(nw)]
+        qw, kw, vw, law = split(q, 2), split(k, 2), split(v, 2), split(la, 2)
+        uw, lmw, anw = split(u, 1), split(logmag, 1), split(ang, 1)
+        del q, k, v, la, u, logmag, ang
+
+        def step(with_gather):
+            ga, gb = sharded.WindowGather(enabled=with_gather), sharded.WindowGather(enabled=with_gather)
+            a, b, e = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            st = {"h": None, "S": None}
+
+            def scan_window(w):
+                y, st["h"] = ops.lambda_scan(uw[w], lmw[w], anw[w], h0=st["h"])
+                return y
+
+            def prefill_window(w):
+                o, st["S"], _ = ops.prefill(qw[w], kw[w], vw[w], law[w], None, st["S"], precision=_lib.PREFILL_TENSOR)
+                return o
+
+            a.record()
+            ys = sharded.run_windows(scan_window, nw, ga)
+            b.record()
+            os_ = sharded.run_windows(prefill_window, nw, gb)
+            e.record(); e.synchronize()
+            del ys, os_
+            return a.elapsed_time(b), b.elapsed_time(e), ga.bytes_received + gb.bytes_received
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        res = {}
+        sampler = ClockSampler(local)
+        for with_gather in (False, True):
+            for _ in range(max(args.warmup, 3)):
+                step(with_gather)
+            if not with_gather:
+                sampler.start()
+            barrier()
+            tl = tp = 0.0; nbytes = 0
+            for _ in range(args.steps):
+                x, y, nbytes = step(with_gather)
+                tl += x; tp += y
+            barrier()
+            if not with_gather:
+                clocks = sampler.stop()
+            res[with_gather] = (tl / args.steps, tp / args.steps, nbytes)
+    t = torch.tensor([res[False][0], res[False][1], res[True][0], res[True][1]], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    l0, p0, l1, p1 = t.tolist()
+    tokens = c["B"] * c["T"]
+    pk = peaks()
+    lam_bytes, asp_bytes = Bl * c["T"] * c["DS"] * 16, Bl * c["H"] * c["T"] * (4 * c["D"] * 2 + 4)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "long_context_tokens_per_s", "value": tokens / ((l0 + p0) * 1e-3), "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": l0 + p0, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp32 scan / bf16 prefill, fp32 state", "data": "synthetic",
+            "config": {"workload": "cfg4: lambda scan B64 T32768 D768 fp32 + aspin prefill B64 T32768 H12 D64 bf16, "
+                                   f"{c['window']}-token windows with carried state, batch split over {world} GPU(s)",
+                       "l2": "inputs of 3-6 GB per tensor per GPU: far larger than L2",
+                       "parallelism": f"batch-sharded x{world}; outputs gathered per window on a side stream in the with_gather arm"},
+            "parts": {"lambda_scan_ms": l0, "aspin_prefill_ms": p0,
+                      "lambda_scan_gbs_per_gpu": lam_bytes / (l0 * 1e-3) / 1e9, "aspin_prefill_gbs_per_gpu": asp_bytes / (p0 * 1e-3) / 1e9,
+                      "hbm_peak_gbs": pk["hbm_gbs"], "peak_source": pk["src"]},
+            "with_gather": {"value": tokens / ((l1 + p1) * 1e-3), "unit": "tok/s", "ms_per_step": l1 + p1, "lambda_scan_ms": l1,
+                            "aspin_prefill_ms": p1, "bytes_received_per_rank": res[True][2]},
+            "gpu_launches": args.steps * 2 * (c["T"] // c["window"]), "clocks": clocks}))
+    if world > 1:
+        dist.barrier()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -293,9 +407,13 @@ def main():
     ap.add_argument("--decode-steps", type=int, default=4096)
     ap.add_argument("--eager", action="store_true", help="no CUDA graphs in the timed step (for a per-kernel launch list)")
     ap.add_argument("--step-only", action="store_true", help="only the timed step: no kernel roofline, decode or CPU legs")
+    ap.add_argument("--workload", default="cfg1", choices=["cfg1", "cfg4"],
+                    help="cfg1 (default): the headline LM prefill; cfg4: the long-context scan + prefill, batch split over the ranks")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
+    elif args.workload == "cfg4":
+        long_context_arm(args)
     else:
         product_arm(args)
 

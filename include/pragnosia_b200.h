@@ -183,6 +183,20 @@ int pgb_rot_table_build(const float *theta, float *table, int H, int T, int D, v
 int pgb_add_norm(const void *x, const void *delta, const void *weight, const void *bias, float eps, int kind, void *y,
                  void *z, long long rows, int d, int dtype, void *stream);
 
+/* ---------------------------------------------------------------------------------------------------------
+ * Linear layer for a few rows (decode at batch <= 8) with the residual add and norm before it and the activation
+ * after it in the same launch:   s = x + delta ;  z = norm(s) ;  y = act(z W^T + bias).
+ * Replaces, for T = 1 and small batch, the F.linear / LayerNorm / GELU calls of src/assoc.py:384-512 (projections,
+ * output projection) and src/model.py:552-560 (MLP), and the tied head at src/model.py:863. bf16 only, fp32 accumulate;
+ * s, z and the pre-activation are rounded to bf16 where the separate ops round them.
+ *   x, delta [B][K]; delta may be NULL.  x_out [B][K] or NULL: receives s (must not alias x or delta).
+ *   norm_kind 0: none, 1: RMS norm (norm_weight [K]), 2: layer norm (norm_weight, norm_bias [K]).
+ *   W [N][K] (torch.nn.Linear layout), bias [N] or NULL;  act 0: none, 1: GELU (erf);  y [B][N].
+ *   B <= 8, K a multiple of 8 and at most 6144; x, delta, x_out, W, norm vectors 16-byte aligned.
+ * ------------------------------------------------------------------------------------------------------- */
+int pgb_skinny_linear(const void *x, const void *delta, const void *norm_weight, const void *norm_bias, int norm_kind, float eps,
+                      const void *W, const void *bias, int act, void *y, void *x_out, int B, int K, int N, void *stream);
+
 /* Health check of the tensor-core prefill kernel: every wait inside it is bounded, and a wait that runs out sets a
  * device-side flag instead of hanging. This reads the flag into *out_host (0 = no wait ever ran out) and clears it.
  * Unlike every other entry point it SYNCHRONISES the device. No counterpart in the reference. */

@@ -107,16 +107,8 @@ class AssocCarrier(nn.Module):
         d = self.d
         zero_shift = (not torch.is_tensor(p0)) and p0 == 0
         if T == 1:
-            y2 = y.view(B, -1)
-            if S0 is None:
-                S0 = torch.zeros(B, H, dk, dk, device=z.device, dtype=torch.float32)
-            o = torch.empty(B, 1, d, device=z.device, dtype=z.dtype)
-            _, S = ops.decode_step(
-                y2[:, 0:d].unflatten(1, (H, dk)), y2[:, d:2 * d].unflatten(1, (H, dk)), y2[:, 2 * d:3 * d].unflatten(1, (H, dk)),
-                y2[:, 3 * d:3 * d + H], S0, c["theta"], gate=y2[:, 3 * d + H:3 * d + 2 * H], delta=self.delta,
-                gate_is_logit=True, decay_A=c["A"], normalize=True, shift=0.0 if zero_shift else p0,
-                rms_weight=c["onw"], rms_eps=self._rms_eps(z.dtype), out=o.view(B, H, dk),
-                S_out=S0 if self.inplace_state else None)
+            o, S = self.step_from_projection(y.view(B, -1), S0, 0.0 if zero_shift else p0)
+            o = o.view(B, 1, d)
             self.sent = None
         else:
             qp, kp, vp = (y[..., i * d:(i + 1) * d].unflatten(-1, (H, dk)) for i in range(3))
@@ -144,6 +136,23 @@ class AssocCarrier(nn.Module):
             # a device-side position (graphed decode): with inplace_state the caller owns and updates it
             return delta, (S, p0 if self.inplace_state else p0 * 0 + T)
         return delta, (S, T)
+
+    def step_from_projection(self, y2, S0, shift):
+        """The recurrent step of one token per sequence from the fused projection's output y2 (B, 3d+2h[+pad]) =
+        [q | k | v | decay logits | gate logits]: one kernel (normalise, gates, rotate the state, write, read, per-head RMS
+        norm). Returns (o (B,d), S); with inplace_state the state is updated where it lies."""
+        c = self._consts()
+        B, H, dk, d = y2.shape[0], self.h, self.dk, self.d
+        if S0 is None:
+            S0 = torch.zeros(B, H, dk, dk, device=y2.device, dtype=torch.float32)
+        o = torch.empty(B, d, device=y2.device, dtype=y2.dtype)
+        _, S = ops.decode_step(
+            y2[:, 0:d].unflatten(1, (H, dk)), y2[:, d:2 * d].unflatten(1, (H, dk)), y2[:, 2 * d:3 * d].unflatten(1, (H, dk)),
+            y2[:, 3 * d:3 * d + H], S0, c["theta"], gate=y2[:, 3 * d + H:3 * d + 2 * H], delta=self.delta,
+            gate_is_logit=True, decay_A=c["A"], normalize=True, shift=shift,
+            rms_weight=c["onw"], rms_eps=self._rms_eps(y2.dtype), out=o.view(B, H, dk),
+            S_out=S0 if self.inplace_state else None)
+        return o, S
 
     def _rot_table(self, T, c):
         """(cos, sin) of position * theta for this layer's window positions; rebuilt when theta changes or T grows."""

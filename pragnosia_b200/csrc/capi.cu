@@ -30,6 +30,8 @@ int prefill_tc_delta_launch(const PrefillArgs &, int, int, void *, cudaStream_t)
 int prefill_tc_delta_static_launch(const PrefillArgs &, int, int, cudaStream_t);
 long long prefill_tc_delta_static_capacity();
 int rot_table_launch(const float *, float *, int, int, int, cudaStream_t);
+int skinny_linear_launch(const void *, const void *, const void *, const void *, int, float, const void *, const void *, int, void *,
+                         void *, int, int, int, cudaStream_t);
 int add_norm_launch(const void *, const void *, const void *, const void *, float, int, void *, void *, long long, int, int,
                     cudaStream_t);
 int rotate_launch(const void *, int, const float *, const float *, void *, int, int, int, int, cudaStream_t);
@@ -193,6 +195,19 @@ int pgb_aspin_delta_prefill_noscratch_fwd(const void *q, const void *k, const vo
         return PGB_ERR_MISALIGNED;
     PrefillArgs a{q, k, v, la, beta, S0, o, S_out, (__nv_bfloat16 *)sent, theta, shift_dev, shift_host, B, H, T};
     return prefill_tc_delta_static_launch(a, o_dtype, D, (cudaStream_t)stream);
+}
+
+int pgb_skinny_linear(const void *x, const void *delta, const void *norm_weight, const void *norm_bias, int norm_kind, float eps,
+                      const void *W, const void *bias, int act, void *y, void *x_out, int B, int K, int N, void *stream) {
+    if (!x || !W || !y) return PGB_ERR_NULL_POINTER;
+    if (norm_kind < 0 || norm_kind > 2 || act < 0 || act > 1) return PGB_ERR_BAD_SHAPE;
+    if ((norm_kind != 0 && !norm_weight) || (norm_kind == 2 && !norm_bias)) return PGB_ERR_NULL_POINTER;
+    if (B < 1 || K < 8 || N < 1 || (K % 8) != 0) return PGB_ERR_BAD_SHAPE;
+    if (B > 8 || K > 6144) return PGB_ERR_TOO_LARGE;                 // eight rows of K bf16 in shared memory: 96 KiB
+    if (!aligned(x, 16) || !aligned(W, 16) || (delta && !aligned(delta, 16)) || (x_out && !aligned(x_out, 16)) ||
+        (norm_weight && !aligned(norm_weight, 16)) || (norm_bias && !aligned(norm_bias, 16)))
+        return PGB_ERR_MISALIGNED;
+    return skinny_linear_launch(x, delta, norm_weight, norm_bias, norm_kind, eps, W, bias, act, y, x_out, B, K, N, (cudaStream_t)stream);
 }
 
 int pgb_add_norm(const void *x, const void *delta, const void *weight, const void *bias, float eps, int kind, void *y, void *z,

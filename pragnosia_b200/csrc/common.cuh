@@ -39,6 +39,23 @@ __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf
 __device__ __forceinline__ float softplusf_(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 
 // cheap forms for gate logits that arrive in bf16 (8 bits of mantissa): ex2/lg2-based, ~1e-6 relative
+// Programmatic dependent launch. A kernel launched with pdl_launch() may start while the kernel before it in the stream
+// is still running; pdl_wait() blocks until that kernel has completed and its writes are visible (a no-op when the launch
+// carried no such dependency), so everything that reads activations or writes anything comes after it, and only
+// constants (weights) are touched before. pdl_launch_dependents() lets the next kernel in the stream start likewise.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+template <typename... KArgs, typename... Args>
+inline cudaError_t pdl_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 // 2^x by the hardware approximation (relative error about 2^-22; results below 2^-126 flush to zero)
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;

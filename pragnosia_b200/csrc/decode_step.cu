@@ -32,6 +32,10 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_step_kernel(DecodeArgs a) 
     const TIN *kp = (const TIN *)a.kp + (size_t)b * a.in_sb + (size_t)h * D;
     const TIN *vp = (const TIN *)a.vp + (size_t)b * a.in_sb + (size_t)h * D;
 
+    // Launched as a programmatic dependent: nothing is read before the kernel ahead (the projection) has completed, and the
+    // kernel behind (the output projection) may start requesting its weights now.
+    pdl_wait();
+    pdl_launch_dependents();
     // ---- the state slice first: its loads are the long latency, everything below overlaps with them
     const int cg = tid % NCG, rg = tid / NCG;
     const int col = cg * 4;
@@ -165,13 +169,15 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_step_kernel(DecodeArgs a) 
 template <typename TIN, typename TOUT>
 static int decode_dispatch(const DecodeArgs &a, int D, int delta, cudaStream_t stream) {
     const unsigned grid = (unsigned)(a.B * a.H);
+    cudaError_t e;
     if (D == 64) {
-        if (delta) decode_step_kernel<TIN, TOUT, 64, true><<<grid, DEC_THREADS, 0, stream>>>(a);
-        else decode_step_kernel<TIN, TOUT, 64, false><<<grid, DEC_THREADS, 0, stream>>>(a);
+        if (delta) e = pdl_launch(decode_step_kernel<TIN, TOUT, 64, true>, dim3(grid), dim3(DEC_THREADS), 0, stream, a);
+        else e = pdl_launch(decode_step_kernel<TIN, TOUT, 64, false>, dim3(grid), dim3(DEC_THREADS), 0, stream, a);
     } else {
-        if (delta) decode_step_kernel<TIN, TOUT, 128, true><<<grid, DEC_THREADS, 0, stream>>>(a);
-        else decode_step_kernel<TIN, TOUT, 128, false><<<grid, DEC_THREADS, 0, stream>>>(a);
+        if (delta) e = pdl_launch(decode_step_kernel<TIN, TOUT, 128, true>, dim3(grid), dim3(DEC_THREADS), 0, stream, a);
+        else e = pdl_launch(decode_step_kernel<TIN, TOUT, 128, false>, dim3(grid), dim3(DEC_THREADS), 0, stream, a);
     }
+    if (e != cudaSuccess) { set_cuda_error(e, "decode_step launch"); return PGB_ERR_CUDA; }
     return check_launch("decode_step_kernel");
 }
 

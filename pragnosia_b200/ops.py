@@ -289,3 +289,34 @@ def add_norm(x, delta, norm: torch.nn.Module):
     check(lib().pgb_add_norm(ptr(x), ptr(delta), ptr(w), ptr(b), float(eps), 0 if rms else 1, ptr(y), ptr(z),
                              x.numel() // d, d, dtype_code(x), stream_of(x)), "pgb_add_norm")
     return (x if delta is None else y), z
+
+
+def skinny_linear(x, W, bias=None, delta=None, norm: Optional[torch.nn.Module] = None, act: Optional[str] = None,
+                  want_sum: bool = False):
+    """y = act(norm(x + delta) W^T + bias) for a few rows in ONE launch (decode at batch <= 8; bf16).
+    x, delta (B,K); W (N,K); norm an nn.RMSNorm / nn.LayerNorm or None; act None or "gelu" (erf).
+    Returns y (B,N), or (y, x + delta) with want_sum (the new residual stream, rounded to bf16 like a separate add)."""
+    need_cuda(x, W)
+    B, K = x.shape
+    N = W.shape[0]
+    if x.dtype != torch.bfloat16 or W.dtype != torch.bfloat16:
+        raise ValueError("skinny_linear: bf16 only")
+    x, W = x.contiguous(), W.contiguous()
+    if delta is not None:
+        delta = delta.to(x.dtype).contiguous()
+    kind, nw, nb, eps = 0, None, None, 0.0
+    if norm is not None:
+        rms = isinstance(norm, torch.nn.RMSNorm)
+        kind = 1 if rms else 2
+        nw = norm.weight.to(x.dtype).contiguous()
+        nb = None if rms else norm.bias.to(x.dtype).contiguous()
+        eps = (norm.eps if norm.eps is not None else torch.finfo(torch.float32).eps) if rms else norm.eps
+    if bias is not None:
+        bias = bias.to(x.dtype).contiguous()
+    y = torch.empty(B, N, device=x.device, dtype=x.dtype)
+    s = torch.empty_like(x) if (want_sum and delta is not None) else None
+    check(lib().pgb_skinny_linear(ptr(x), ptr(delta), ptr(nw), ptr(nb), kind, float(eps), ptr(W), ptr(bias),
+                                  1 if act == "gelu" else 0, ptr(y), ptr(s), B, K, N, stream_of(x)), "pgb_skinny_linear")
+    if want_sum:
+        return y, (x if delta is None else s)
+    return y

@@ -66,6 +66,12 @@ def test_bad_calls_are_rejected_on_the_host(L):
     assert L.pgb_aspin_decode_step(*dec(delta=1)) == 1
     assert L.pgb_aspin_decode_step(*dec(sb=8)) == 2
     assert L.pgb_rotate_pairs(one, 0, one, one, one, 1, 1, 1, 7, None) == 2
+    # fused small-batch linear: norm without its weight, more than eight rows, K not a multiple of 8, unaligned W
+    sk = lambda nw=None, kind=0, B=1, K=768, W=one: (one, None, nw, None, kind, 1e-5, W, None, 0, one, None, B, K, 16, None)
+    assert L.pgb_skinny_linear(*sk(kind=1)) == 1
+    assert L.pgb_skinny_linear(*sk(B=9)) == 7
+    assert L.pgb_skinny_linear(*sk(K=100)) == 2
+    assert L.pgb_skinny_linear(*sk(W=odd)) == 4
 
 
 def test_ops_refuse_cpu_tensors():

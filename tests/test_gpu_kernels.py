@@ -361,3 +361,40 @@ def test_layer_prefill_raw_projections(D, gate):
     o2, S2, _ = ops.prefill_fused(q2, k2, v2, pd[..., 3 * d:3 * d + H], cu(A), cu(S0), theta=cu(th), shift=50.0,
                                   rms_weight=cu(w), rms_eps=eps, out_dtype=torch.float32)
     close(o, o2, 3e-3, "layer vs two-kernel o"); close(S, S2, 2e-3, "layer vs two-kernel S")
+
+
+@pytest.mark.parametrize("B", [1, 3, 8])
+@pytest.mark.parametrize("K,N", [(768, 2328), (3072, 768), (768, 8192)])
+@pytest.mark.parametrize("norm,act", [(None, None), ("rms", "gelu"), ("ln", None)])
+def test_skinny_linear(B, K, N, norm, act):
+    """The fused small-batch linear layer (residual add + norm + linear + bias + GELU in one launch) against the same
+    chain of separate torch ops in bf16 (src/model.py:552-560, src/assoc.py:388-451 at T = 1)."""
+    import torch.nn.functional as F
+    g = torch.Generator().manual_seed(B * 1000 + K + N)
+    bf = lambda t: t.to(DEV).to(torch.bfloat16)
+    x, delta = bf(torch.randn(B, K, generator=g)), bf(0.5 * torch.randn(B, K, generator=g))
+    W, bias = bf(torch.randn(N, K, generator=g) * K ** -0.5), bf(0.1 * torch.randn(N, generator=g))
+    mod = None
+    if norm is not None:
+        mod = (torch.nn.RMSNorm(K) if norm == "rms" else torch.nn.LayerNorm(K)).to(DEV).to(torch.bfloat16)
+        with torch.no_grad():
+            mod.weight.copy_(bf(1.0 + 0.2 * torch.randn(K, generator=g)))
+            if norm == "ln":
+                mod.bias.copy_(bf(0.1 * torch.randn(K, generator=g)))
+    for dl in (delta, None):
+        s = x if dl is None else x + dl
+        z = s if mod is None else mod(s)
+        ref = F.linear(z, W, bias)
+        if act == "gelu":
+            ref = F.gelu(ref)
+        y, s2 = ops.skinny_linear(x, W, bias, delta=dl, norm=mod, act=act, want_sum=True)
+        assert y.dtype == torch.bfloat16 and tuple(y.shape) == (B, N)
+        assert torch.equal(s2, s)                                             # the residual stream, bit for bit
+        exact = F.linear(z.float(), W.float(), bias.float())                  # same rounded operands, fp32 accumulate
+        exact = exact.to(torch.bfloat16).float()
+        if act == "gelu":
+            exact = F.gelu(exact)
+        assert rel_err(y.float().cpu(), exact.cpu()) <= 4e-3                  # one bf16 ulp of the largest value
+        assert rel_err(y.float().cpu(), ref.float().cpu()) <= 8e-3
+    y0 = ops.skinny_linear(x, W)                                              # no bias, nothing fused
+    assert rel_err(y0.float().cpu(), F.linear(x.float(), W.float()).cpu()) <= 4e-3

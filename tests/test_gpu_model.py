@@ -144,3 +144,25 @@ def test_generate_runs_and_is_seeded():
     g1 = Decoder(m, batch=3, use_graph=False).generate(prompt, 12, temp=0.0)
     g2 = Decoder(m, batch=3, use_graph=True).generate(prompt, 12, temp=0.0)
     assert torch.equal(g1, g2)
+
+
+@pytest.mark.parametrize("mixer,norm", [("aspin", "rms"), ("dspin", "ln")])
+def test_fused_small_batch_decode_matches_the_separate_ops(mixer, norm):
+    """The bf16 decode step at batch <= 8 runs every linear layer through the fused kernel (five launches a layer); it
+    must give the logits and states of the step built from separate ops, eagerly and under the captured graph."""
+    m, _, _ = small_lm(mixer, norm, torch.bfloat16)
+    ids = synth.token_ids(3, 50, 256, seed=17).to(DEV)
+    outs = {}
+    for fused in (False, True):
+        for use_graph in (False, True):
+            dec = Decoder(m, batch=3, use_graph=use_graph, fused=fused)
+            assert dec._fused_ok() == fused
+            lg = [dec.prefill(ids[:, :40])]
+            for t in range(40, 50):
+                lg.append(dec.step(ids[:, t]).clone())
+            outs[(fused, use_graph)] = (torch.stack(lg, 1), dec.states[1][0].clone())
+    ref_lg, ref_S = outs[(False, False)]
+    for key, (lg, S) in outs.items():
+        close(lg, ref_lg, 3e-2, f"logits fused={key[0]} graph={key[1]}")
+        close(S, ref_S, 3e-2, f"state fused={key[0]} graph={key[1]}")
+    close(outs[(True, True)][0], outs[(True, False)][0], 1e-6, "fused: graph replay equals eager")
