@@ -270,7 +270,7 @@ def decode_numbers(model, dev, pk, args):
     for B in (1, 64):
         dec = Decoder(model, batch=B)
         prompt = synth.token_ids(B, 512, CFG["vocab"], seed=7).to(dev)
-        dec.generate(prompt, 16, temp=1.0, seed=0)                      # captures the graph
+        dec.generate(prompt, n, temp=1.0, seed=0)                       # captures the per-token graph for this length
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(); dec.generate(prompt, n, temp=1.0, seed=0); b.record(); b.synchronize()

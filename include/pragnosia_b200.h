@@ -197,6 +197,26 @@ int pgb_add_norm(const void *x, const void *delta, const void *weight, const voi
 int pgb_skinny_linear(const void *x, const void *delta, const void *norm_weight, const void *norm_bias, int norm_kind, float eps,
                       const void *W, const void *bias, int act, void *y, void *x_out, int B, int K, int N, void *stream);
 
+/* ---------------------------------------------------------------------------------------------------------
+ * The two ends of a decode step as single launches, so that a token is a fixed kernel sequence with no work on the host
+ * (the reference samples on the host and syncs per token: src/bench.py:79-86, 193-239; embedding: src/model.py:859).
+ *
+ * pgb_decode_embed:  x[b][:] = E[tok[b]][:] + P[pos[0]][:]   (bf16; E [vocab][d], P [ctx][d], x [B][d]; tok [B] and pos [1]
+ *   are int64 on the device; ids outside the tables are clamped).
+ *
+ * pgb_decode_sample: tok[b] ~ softmax(logits[b] / temp) (temp = 0: argmax) by Gumbel-max with a counter-based uniform
+ *   mixed from (seed, count[0], b, v); logits [B][V] fp32 or bf16. Writes hist[b][count[0]] when hist != NULL and
+ *   count[0] < hist_cols. The window position and the rebase shift belong to the token being fed to the model, so when
+ *   count[0] > 0 the kernel first advances them for the previous token: pos[0] = (pos[0] + 1) mod ctx, shift[0] = 1
+ *   (either may be NULL). Once every row has drawn, count[0] += 1. ticket is one zero-initialised uint32 the kernel uses
+ *   and leaves at zero.
+ * ------------------------------------------------------------------------------------------------------- */
+int pgb_decode_embed(const long long *tok, const long long *pos, const void *E, const void *P, void *x, int B, int d, int vocab,
+                     int ctx, void *stream);
+int pgb_decode_sample(const void *logits, int dtype, float temp, unsigned long long seed, long long *tok, long long *hist,
+                      int hist_cols, long long *count, long long *pos, float *shift, unsigned int *ticket, int B, int V, int ctx,
+                      void *stream);
+
 /* Health check of the tensor-core prefill kernel: every wait inside it is bounded, and a wait that runs out sets a
  * device-side flag instead of hanging. This reads the flag into *out_host (0 = no wait ever ran out) and clears it.
  * Unlike every other entry point it SYNCHRONISES the device. No counterpart in the reference. */

@@ -30,6 +30,9 @@ int prefill_tc_delta_launch(const PrefillArgs &, int, int, void *, cudaStream_t)
 int prefill_tc_delta_static_launch(const PrefillArgs &, int, int, cudaStream_t);
 long long prefill_tc_delta_static_capacity();
 int rot_table_launch(const float *, float *, int, int, int, cudaStream_t);
+int decode_embed_launch(const long long *, const long long *, const void *, const void *, void *, int, int, int, int, cudaStream_t);
+int decode_sample_launch(const void *, int, float, unsigned long long, long long *, long long *, int, long long *, long long *, float *,
+                         unsigned int *, int, int, int, cudaStream_t);
 int skinny_linear_launch(const void *, const void *, const void *, const void *, int, float, const void *, const void *, int, void *,
                          void *, int, int, int, cudaStream_t);
 int add_norm_launch(const void *, const void *, const void *, const void *, float, int, void *, void *, long long, int, int,
@@ -195,6 +198,26 @@ int pgb_aspin_delta_prefill_noscratch_fwd(const void *q, const void *k, const vo
         return PGB_ERR_MISALIGNED;
     PrefillArgs a{q, k, v, la, beta, S0, o, S_out, (__nv_bfloat16 *)sent, theta, shift_dev, shift_host, B, H, T};
     return prefill_tc_delta_static_launch(a, o_dtype, D, (cudaStream_t)stream);
+}
+
+int pgb_decode_embed(const long long *tok, const long long *pos, const void *E, const void *P, void *x, int B, int d, int vocab,
+                     int ctx, void *stream) {
+    if (!tok || !pos || !E || !P || !x) return PGB_ERR_NULL_POINTER;
+    if (B < 1 || d < 8 || (d % 8) != 0 || vocab < 1 || ctx < 1) return PGB_ERR_BAD_SHAPE;
+    if (!aligned(E, 16) || !aligned(P, 16) || !aligned(x, 16) || !aligned(tok, 8) || !aligned(pos, 8)) return PGB_ERR_MISALIGNED;
+    return decode_embed_launch(tok, pos, E, P, x, B, d, vocab, ctx, (cudaStream_t)stream);
+}
+
+int pgb_decode_sample(const void *logits, int dtype, float temp, unsigned long long seed, long long *tok, long long *hist,
+                      int hist_cols, long long *count, long long *pos, float *shift, unsigned int *ticket, int B, int V, int ctx,
+                      void *stream) {
+    if (!logits || !tok || !count || !ticket) return PGB_ERR_NULL_POINTER;
+    if (dtype != PGB_F32 && dtype != PGB_BF16) return PGB_ERR_BAD_DTYPE;
+    if (B < 1 || V < 1 || ctx < 1 || hist_cols < 0 || !(temp >= 0.f)) return PGB_ERR_BAD_SHAPE;
+    if (!aligned(tok, 8) || !aligned(count, 8) || (hist && !aligned(hist, 8)) || (pos && !aligned(pos, 8)) || !aligned(ticket, 4))
+        return PGB_ERR_MISALIGNED;
+    return decode_sample_launch(logits, dtype, temp, seed, tok, hist, hist_cols, count, pos, shift, ticket, B, V, ctx,
+                                (cudaStream_t)stream);
 }
 
 int pgb_skinny_linear(const void *x, const void *delta, const void *norm_weight, const void *norm_bias, int norm_kind, float eps,

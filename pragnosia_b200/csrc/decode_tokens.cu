@@ -1,0 +1,128 @@
+// The two ends of a decode step, each as one launch, so that a whole token (draw, bookkeeping, embedding, layers, head)
+// is a fixed sequence of kernels with nothing left to the host (reference: the host-side loop and sampler of
+// src/bench.py:79-86, 193-239, which syncs with the host for every token).
+//
+//   embed:   x[b][:] = E[tok[b]][:] + P[pos][:]                               (src/model.py:859: token + wrapped position)
+//   sample:  tok[b] ~ softmax(logits[b] / temp)   (temp = 0: argmax), recorded in hist[b][count]. The position and the
+//            rebase shift belong to the token being fed to the model, so from the second draw on (count > 0) the kernel
+//            first advances them for the previous token: pos = (pos + 1) mod ctx, shift = 1; the CTA that finishes last
+//            then does count += 1.
+//
+// The draw is the Gumbel-max form of categorical sampling, tok = argmax_v (logit_v / temp - log(-log u_v)), with u_v a
+// counter-based uniform (a 64-bit mix of seed, step count, sequence and vocabulary index): reproducible from the seed,
+// independent of launch geometry, and it needs no state.
+#include "common.cuh"
+
+namespace pgb {
+
+__global__ void __launch_bounds__(128) decode_embed_kernel(const long long *__restrict__ tok, const long long *__restrict__ pos,
+                                                           const __nv_bfloat16 *__restrict__ E, const __nv_bfloat16 *__restrict__ P,
+                                                           __nv_bfloat16 *__restrict__ x, int d, int vocab, int ctx) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int b = blockIdx.x;
+    long long t = tok[b], p = pos[0];
+    t = t < 0 ? 0 : (t >= vocab ? vocab - 1 : t);                     // ids outside the table are clamped, never dereferenced
+    p = p < 0 ? 0 : (p >= ctx ? ctx - 1 : p);
+    const uint4 *er = reinterpret_cast<const uint4 *>(E + (size_t)t * d), *pr = reinterpret_cast<const uint4 *>(P + (size_t)p * d);
+    uint4 *xr = reinterpret_cast<uint4 *>(x + (size_t)b * d);
+    for (int i = threadIdx.x; i < d / 8; i += blockDim.x) {
+        const uint4 a = er[i], c = pr[i];
+        const __nv_bfloat162 *a2 = reinterpret_cast<const __nv_bfloat162 *>(&a), *c2 = reinterpret_cast<const __nv_bfloat162 *>(&c);
+        uint4 o;
+        __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 fa = __bfloat1622float2(a2[j]), fc = __bfloat1622float2(c2[j]);
+            o2[j] = __floats2bfloat162_rn(fa.x + fc.x, fa.y + fc.y);
+        }
+        xr[i] = o;
+    }
+}
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {     // splitmix64 finaliser
+    z += 0x9e3779b97f4a7c15ull;
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+    z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+    return z ^ (z >> 31);
+}
+
+constexpr int SAMPLE_NT = 256;
+
+template <typename T_>
+__global__ void __launch_bounds__(SAMPLE_NT) decode_sample_kernel(const T_ *__restrict__ logits, float temp, unsigned long long seed,
+                                                                  long long *__restrict__ tok, long long *__restrict__ hist, int hist_cols,
+                                                                  long long *__restrict__ count, long long *__restrict__ pos,
+                                                                  float *__restrict__ shift, unsigned int *__restrict__ ticket,
+                                                                  int V, int ctx) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float sval[SAMPLE_NT / 32];
+    __shared__ int sidx[SAMPLE_NT / 32];
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long step = count[0];
+    if (b == 0 && tid == 0 && step > 0) {                             // nobody in this kernel reads these two
+        if (pos != nullptr) pos[0] = (pos[0] + 1) % ctx;
+        if (shift != nullptr) shift[0] = 1.0f;
+    }
+    const T_ *row = logits + (size_t)b * V;
+    const float inv_t = temp > 0.f ? 1.0f / temp : 1.0f;
+    const unsigned long long key = mix64(seed ^ mix64((unsigned long long)step * 0x100000001b3ull + (unsigned long long)b));
+    float best = -INFINITY;
+    int arg = V;                                                      // ties go to the smallest index
+    for (int v = tid; v < V; v += SAMPLE_NT) {
+        float s;
+        if constexpr (sizeof(T_) == 2) s = __bfloat162float(row[v]); else s = row[v];
+        s *= inv_t;
+        if (temp > 0.f) {
+            const unsigned long long r = mix64(key + (unsigned long long)v);
+            const float u = ((float)(r >> 40) + 0.5f) * (1.0f / 16777216.0f);          // (0, 1), 24 bits
+            s -= logf(-logf(u));
+        }
+        if (s > best || (s == best && v < arg)) { best = s; arg = v; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    if (lane == 0) { sval[warp] = best; sidx[warp] = arg; }
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < SAMPLE_NT / 32; ++w)
+            if (sval[w] > best || (sval[w] == best && sidx[w] < arg)) { best = sval[w]; arg = sidx[w]; }
+        if (arg >= V) arg = 0;                                        // a row of NaNs: still a valid id
+        tok[b] = arg;
+        if (hist != nullptr && step >= 0 && step < hist_cols) hist[(size_t)b * hist_cols + step] = arg;
+        __threadfence();
+        if (atomicAdd(ticket, 1u) == gridDim.x - 1) {                 // every row has read the count: advance it
+            count[0] = step + 1;
+            *ticket = 0u;
+        }
+    }
+}
+
+int decode_embed_launch(const long long *tok, const long long *pos, const void *E, const void *P, void *x, int B, int d, int vocab,
+                        int ctx, cudaStream_t stream) {
+    cudaError_t e = pdl_launch(decode_embed_kernel, dim3((unsigned)B), dim3(128), 0, stream, tok, pos, (const __nv_bfloat16 *)E,
+                               (const __nv_bfloat16 *)P, (__nv_bfloat16 *)x, d, vocab, ctx);
+    if (e != cudaSuccess) { set_cuda_error(e, "decode_embed launch"); return PGB_ERR_CUDA; }
+    return check_launch("decode_embed_kernel");
+}
+
+int decode_sample_launch(const void *logits, int dtype, float temp, unsigned long long seed, long long *tok, long long *hist,
+                         int hist_cols, long long *count, long long *pos, float *shift, unsigned int *ticket, int B, int V, int ctx,
+                         cudaStream_t stream) {
+    cudaError_t e;
+    if (dtype == PGB_BF16)
+        e = pdl_launch(decode_sample_kernel<__nv_bfloat16>, dim3((unsigned)B), dim3(SAMPLE_NT), 0, stream, (const __nv_bfloat16 *)logits,
+                       temp, seed, tok, hist, hist_cols, count, pos, shift, ticket, V, ctx);
+    else
+        e = pdl_launch(decode_sample_kernel<float>, dim3((unsigned)B), dim3(SAMPLE_NT), 0, stream, (const float *)logits, temp, seed,
+                       tok, hist, hist_cols, count, pos, shift, ticket, V, ctx);
+    if (e != cudaSuccess) { set_cuda_error(e, "decode_sample launch"); return PGB_ERR_CUDA; }
+    return check_launch("decode_sample_kernel");
+}
+
+}  // namespace pgb

@@ -64,11 +64,11 @@ class Decoder:
         return (self.fused and self.B <= 4 and m.e.weight.dtype == torch.bfloat16 and m.d % 8 == 0 and
                 all(isinstance(mx, AssocCarrier) for mx in m.mix))
 
-    def _step_fused(self):
+    def _step_fused(self, advance: bool = True):
         """Every linear layer of the step as one launch that also does the residual add and norm before it and the
         activation after it (ops.skinny_linear): per layer projection, state step, output projection, MLP up, MLP down."""
         m, B = self.m, self.B
-        x, delta = (m.e(self.tok) + m.p(self.pos)).view(B, m.d), None
+        x, delta = ops.decode_embed(self.tok, self.pos, m.e.weight, m.p.weight), None
         for i, (mx, mp) in enumerate(zip(m.mix, m.mlp)):
             c = mx._consts()
             y, x = ops.skinny_linear(x, c["W"], c["b"], delta=delta, norm=mx.ln, want_sum=True)
@@ -78,13 +78,14 @@ class Decoder:
             d1 = ops.skinny_linear(o, c["ow"])
             hmid, x = ops.skinny_linear(x, mp.a.weight, mp.a.bias, delta=d1, norm=mp.n, act="gelu", want_sum=True)
             delta = ops.skinny_linear(hmid, mp.b.weight, mp.b.bias)
-        self.shift.fill_(1.0)
-        self.pos.copy_((self.pos + 1) % self.w)
+        if advance:
+            self.shift.fill_(1.0)
+            self.pos.copy_((self.pos + 1) % self.w)
         return ops.skinny_linear(x, m.e.weight, delta=delta, norm=m.n).float()
 
-    def _step(self):
+    def _step(self, advance: bool = True):
         if self._fused_ok():
-            return self._step_fused()
+            return self._step_fused(advance)
         m = self.m
         x, delta = m.e(self.tok) + m.p(self.pos), None
         for i, (mx, mp) in enumerate(zip(m.mix, m.mlp)):
@@ -99,8 +100,9 @@ class Decoder:
                 for a, b in zip(st, new): a.copy_(b)
             x, z = m._add_norm(x, delta, mp.n)
             delta = mp.ff(z)
-        self.shift.fill_(1.0)
-        self.pos.copy_((self.pos + 1) % self.w)
+        if advance:
+            self.shift.fill_(1.0)
+            self.pos.copy_((self.pos + 1) % self.w)
         return F.linear(m._add_norm(x, delta, m.n)[1], m.e.weight)[:, -1].float()
 
     @torch.no_grad()
@@ -135,12 +137,56 @@ class Decoder:
 
     @torch.no_grad()
     def generate(self, prompt_ids: torch.Tensor, n: int, temp: float = 0.0, seed: int = 0):
-        """prompt_ids (B,Tp) -> sampled ids (B,n)."""
-        g = torch.Generator(device=self.dev).manual_seed(seed)
+        """prompt_ids (B,Tp) -> sampled ids (B,n). With use_graph the draw, the bookkeeping and the model step of one token
+        are a single CUDA-graph replay (no per-token work on the host besides the replay itself)."""
         lg = self.prefill(prompt_ids)
-        out = torch.empty(self.B, n, dtype=torch.long, device=self.dev)
-        for i in range(n):
-            nxt = self.sample(lg, temp, g)
-            out[:, i] = nxt
+        if self.use_graph:
+            return self._generate_graphed(lg, n, temp, seed)
+        out = torch.zeros(self.B, max(n, 1), dtype=torch.long, device=self.dev)
+        cnt = torch.zeros(1, dtype=torch.long, device=self.dev)
+        ticket = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        nxt = torch.empty(self.B, dtype=torch.long, device=self.dev)
+        for _ in range(n):                                   # the same draws as the graphed loop, launched one by one
+            ops.decode_sample(lg, temp, seed, nxt, cnt, ticket, hist=out)
             lg = self.step(nxt)
-        return out
+        return out[:, :n]
+
+    def _token_body(self, temp: float, seed: int):
+        """Draw from the waiting logits, record the token at the running index, run the model on the token, leave the next
+        logits waiting: a fixed kernel sequence, nothing on the host. The position and the rebase shift belong to the token
+        being fed, so the draw kernel advances them for the PREVIOUS token (from the second token on) before the step."""
+        ops.decode_sample(self._lg_in, temp, seed, self.tok, self._cnt, self._ticket, hist=self._hist, pos=self.pos,
+                          shift=self.shift, ctx=self.w)
+        self._lg_in.copy_(self._step(advance=False))
+
+    def _generate_graphed(self, lg, n: int, temp: float, seed: int):
+        key = (n, float(temp), int(seed))
+        if getattr(self, "_gen_key", None) != key:
+            V = lg.shape[-1]
+            self._lg_in = torch.empty(self.B, V, dtype=torch.float32, device=self.dev)
+            self._hist = torch.zeros(self.B, max(n, 4), dtype=torch.long, device=self.dev)   # the warm-up passes write three columns
+            self._cnt = torch.zeros(1, dtype=torch.long, device=self.dev)
+            self._ticket = torch.zeros(1, dtype=torch.int32, device=self.dev)
+            self._lg_in.copy_(lg)
+            saved = [tuple(t.clone() if torch.is_tensor(t) else t for t in st) for st in self.states]
+            pos, shift = self.pos.clone(), self.shift.clone()
+            s = torch.cuda.Stream(); s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                for _ in range(2): self._token_body(temp, seed)
+            torch.cuda.current_stream().wait_stream(s)
+            self._gen_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self._gen_graph):
+                self._token_body(temp, seed)
+            for st, sv in zip(self.states, saved):           # warm-up and capture advanced the state: restore it
+                for a, b in zip(st, sv):
+                    if torch.is_tensor(a): a.copy_(b)
+            self.pos.copy_(pos); self.shift.copy_(shift)
+            self._gen_key = key
+        self._lg_in.copy_(lg)
+        self._cnt.zero_()
+        for _ in range(n):
+            self._gen_graph.replay()
+        if n > 0:                                            # the last token's step has not been followed by a draw
+            self.shift.fill_(1.0)
+            self.pos.copy_((self.pos + 1) % self.w)
+        return self._hist[:, :n].clone()

@@ -320,3 +320,30 @@ def skinny_linear(x, W, bias=None, delta=None, norm: Optional[torch.nn.Module] =
     if want_sum:
         return y, (x if delta is None else s)
     return y
+
+
+def decode_embed(tok, pos, E, P):
+    """x (B,d) = E[tok] + P[pos] in one launch; tok (B,) / (B,1) int64 and pos (1,) int64 on the device, bf16 tables."""
+    need_cuda(tok, pos, E, P)
+    if E.dtype != torch.bfloat16 or P.dtype != torch.bfloat16 or tok.dtype != torch.long or pos.dtype != torch.long:
+        raise ValueError("decode_embed: bf16 tables, int64 ids")
+    B, d = tok.numel(), E.shape[1]
+    x = torch.empty(B, d, device=E.device, dtype=E.dtype)
+    check(lib().pgb_decode_embed(ptr(tok.contiguous()), ptr(pos), ptr(E.contiguous()), ptr(P.contiguous()), ptr(x), B, d,
+                                 E.shape[0], P.shape[0], stream_of(E)), "pgb_decode_embed")
+    return x
+
+
+def decode_sample(logits, temp, seed, tok, count, ticket, hist=None, pos=None, shift=None, ctx: int = 1):
+    """Draw one id per row of logits (B,V) into tok (B,) / (B,1) int64, record it in hist[:, count] and advance the step
+    counters (count, pos modulo ctx, shift) -- all on the device, one launch. ticket: a zeroed uint32/int32 scalar."""
+    need_cuda(logits, tok, count, ticket)
+    B, V = logits.shape
+    if logits.dtype not in (torch.float32, torch.bfloat16):
+        logits = logits.float()
+    logits = logits.contiguous()
+    cols = 0 if hist is None else hist.shape[1]
+    check(lib().pgb_decode_sample(ptr(logits), dtype_code(logits), float(temp), int(seed) & 0xFFFFFFFFFFFFFFFF, ptr(tok), ptr(hist),
+                                  cols, ptr(count), ptr(pos), ptr(shift), ptr(ticket), B, V, int(ctx), stream_of(logits)),
+          "pgb_decode_sample")
+    return tok

@@ -72,6 +72,10 @@ def test_bad_calls_are_rejected_on_the_host(L):
     assert L.pgb_skinny_linear(*sk(B=9)) == 7
     assert L.pgb_skinny_linear(*sk(K=100)) == 2
     assert L.pgb_skinny_linear(*sk(W=odd)) == 4
+    # decode-step ends: d not a multiple of 8; a negative temperature; a missing ticket
+    assert L.pgb_decode_embed(one, one, one, one, one, 1, 60, 10, 10, None) == 2
+    assert L.pgb_decode_sample(one, 0, -1.0, 0, one, None, 0, one, None, None, one, 1, 8, 1, None) == 2
+    assert L.pgb_decode_sample(one, 0, 1.0, 0, one, None, 0, one, None, None, None, 1, 8, 1, None) == 1
 
 
 def test_ops_refuse_cpu_tensors():

@@ -398,3 +398,40 @@ def test_skinny_linear(B, K, N, norm, act):
         assert rel_err(y.float().cpu(), ref.float().cpu()) <= 8e-3
     y0 = ops.skinny_linear(x, W)                                              # no bias, nothing fused
     assert rel_err(y0.float().cpu(), F.linear(x.float(), W.float()).cpu()) <= 4e-3
+
+
+def test_decode_embed_and_sampler():
+    """The single-launch ends of the decode step: embedding sum; Gumbel-max draws that are greedy at temperature 0,
+    reproducible from (seed, step), recorded at the running index, and distributed as softmax(logits / temp)."""
+    g = torch.Generator().manual_seed(3)
+    E = torch.randn(50, 64, generator=g).to(DEV).to(torch.bfloat16)
+    P = torch.randn(12, 64, generator=g).to(DEV).to(torch.bfloat16)
+    tok = torch.tensor([[3], [49], [0]], device=DEV)
+    pos = torch.tensor([7], device=DEV)
+    assert torch.equal(ops.decode_embed(tok, pos, E, P), E[tok.view(-1)] + P[7])
+    B, V, n = 64, 16, 400
+    p = torch.softmax(torch.randn(V, generator=g) * 1.5, -1)
+    logits = p.log().expand(B, V).contiguous().to(DEV)
+    def run(seed, temp):
+        t = torch.zeros(B, dtype=torch.long, device=DEV)
+        cnt = torch.zeros(1, dtype=torch.long, device=DEV)
+        ticket = torch.zeros(1, dtype=torch.int32, device=DEV)
+        hist = torch.full((B, n), -1, dtype=torch.long, device=DEV)
+        posd = torch.tensor([10], device=DEV); shift = torch.tensor(5.0, device=DEV)
+        for i in range(n):
+            ops.decode_sample(logits * temp, temp, seed, t, cnt, ticket, hist=hist, pos=posd, shift=shift, ctx=12)
+            if i == 0:
+                assert posd.item() == 10 and shift.item() == 5.0          # the first draw leaves the prompt's position alone
+        assert cnt.item() == n and ticket.item() == 0 and posd.item() == (10 + n - 1) % 12 and shift.item() == 1.0
+        assert torch.equal(hist[:, -1], t)
+        return hist
+    h1, h2, h3 = run(1, 1.0), run(1, 1.0), run(2, 0.5)
+    assert torch.equal(h1, h2) and not torch.equal(h1, h3)
+    for h in (h1, h3):                                                    # temperature cancels: same target distribution
+        freq = torch.bincount(h.reshape(-1).cpu(), minlength=V).double() / h.numel()
+        sigma = (p.double() * (1 - p.double()) / h.numel()).sqrt()
+        assert ((freq - p.double()).abs() <= 5 * sigma + 1e-4).all(), (freq, p)
+    t = torch.zeros(B, dtype=torch.long, device=DEV)
+    lg = torch.randn(B, 1000, generator=g).to(DEV)
+    ops.decode_sample(lg.to(torch.bfloat16), 0.0, 9, t, torch.zeros(1, dtype=torch.long, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV))
+    assert torch.equal(t, lg.to(torch.bfloat16).float().argmax(-1))

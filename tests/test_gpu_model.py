@@ -144,6 +144,15 @@ def test_generate_runs_and_is_seeded():
     g1 = Decoder(m, batch=3, use_graph=False).generate(prompt, 12, temp=0.0)
     g2 = Decoder(m, batch=3, use_graph=True).generate(prompt, 12, temp=0.0)
     assert torch.equal(g1, g2)
+    c = Decoder(m, batch=3, use_graph=False).generate(prompt, 12, temp=1.0, seed=5)
+    assert torch.equal(a, c)                                  # one graph replay per token draws what the eager loop draws
+    assert not torch.equal(a, Decoder(m, batch=3).generate(prompt, 12, temp=1.0, seed=6))
+    d = Decoder(m, batch=3)
+    first = d.generate(prompt, 12, temp=1.0, seed=5)
+    nxt = d.step(first[:, -1] * 0 + 7)                        # the decoder stays usable: position and shift are in step
+    e = Decoder(m, batch=3, use_graph=False)
+    e.generate(prompt, 12, temp=1.0, seed=5)
+    close(nxt, e.step(first[:, -1] * 0 + 7), 2e-4, "step after generate")
 
 
 @pytest.mark.parametrize("mixer,norm", [("aspin", "rms"), ("dspin", "ln")])
