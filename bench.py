@@ -42,8 +42,9 @@ def peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         d = json.loads(p.read_text())
-        return dict(hbm_gbs=float(d["hbm_gbs"]), tflops=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), src="measured")
-    return dict(hbm_gbs=6650.0, tflops=1590.0, src="fallback")
+        return dict(hbm_gbs=float(d["hbm_gbs"]), tflops=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                    tflops_burst=float(d["bf16_tflops"]), src="measured")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, tflops_burst=1590.0, src="fallback")
 
 
 class ClockSampler:
@@ -253,6 +254,10 @@ def kernel_rooflines(pk):
         us, alg = kb.time_case(name)
         out.append(dict(kernel=name, what=kb.CASES[name][1], bound="hbm", achieved=alg / us / 1e3, peak=pk["hbm_gbs"], unit="GB/s",
                         frac=alg / us / 1e3 / pk["hbm_gbs"], us_per_launch=us, algorithmic_bytes=alg))
+    for name, flops in kb.FLOPS.items():                              # the tensor-bound kernels against the measured GEMM rate
+        us, alg = kb.time_case(name)
+        out.append(dict(kernel=name, what=kb.CASES[name][1], bound="tensor", achieved=flops / us / 1e6, peak=pk["tflops_burst"],
+                        unit="TFLOP/s", frac=flops / us / 1e6 / pk["tflops_burst"], us_per_launch=us, algorithmic_bytes=alg))
     roof = dict(out[0])
     big = NCU_TRAFFIC_BYTES.get("layer_prefill")
     roof["traffic"] = None if big is None else big * (16 * 12 * 512) / (64 * 12 * 1024)

@@ -217,6 +217,16 @@ int pgb_decode_sample(const void *logits, int dtype, float temp, unsigned long l
                       int hist_cols, long long *count, long long *pos, float *shift, unsigned int *ticket, int B, int V, int ctx,
                       void *stream);
 
+/* ---------------------------------------------------------------------------------------------------------
+ * y = act(x W^T + bias) as one tcgen05 GEMM with the bias and the activation applied on the accumulator in the epilogue.
+ * Replaces the Linear(d, 4d) + GELU pair of the MLP block (src/model.py:552-560) in the prefill pass, where the separate
+ * activation is a second pass over the hidden tensor. bf16, fp32 accumulate; the pre-activation is rounded to bf16 first,
+ * as the separate Linear would.
+ *   x [M][K], W [N][K] (torch.nn.Linear layout), bias [N] or NULL, y [M][N]; act 0: none, 1: GELU (erf).
+ *   N and K multiples of 8; x, W, y, bias 16-byte aligned. Bounded waits as in the prefill kernels (pgb_tc_error_flag).
+ * ------------------------------------------------------------------------------------------------------- */
+int pgb_linear_act(const void *x, const void *W, const void *bias, void *y, long long M, int N, int K, int act, void *stream);
+
 /* Health check of the tensor-core prefill kernel: every wait inside it is bounded, and a wait that runs out sets a
  * device-side flag instead of hanging. This reads the flag into *out_host (0 = no wait ever ran out) and clears it.
  * Unlike every other entry point it SYNCHRONISES the device. No counterpart in the reference. */

@@ -33,6 +33,8 @@ int rot_table_launch(const float *, float *, int, int, int, cudaStream_t);
 int decode_embed_launch(const long long *, const long long *, const void *, const void *, void *, int, int, int, int, cudaStream_t);
 int decode_sample_launch(const void *, int, float, unsigned long long, long long *, long long *, int, long long *, long long *, float *,
                          unsigned int *, int, int, int, cudaStream_t);
+int linear_gelu_launch(const void *, const void *, const void *, void *, long long, int, int, int, cudaStream_t);
+int linear_gelu_error_flag(int *);
 int skinny_linear_launch(const void *, const void *, const void *, const void *, int, float, const void *, const void *, int, void *,
                          void *, int, int, int, cudaStream_t);
 int add_norm_launch(const void *, const void *, const void *, const void *, float, int, void *, void *, long long, int, int,
@@ -220,6 +222,14 @@ int pgb_decode_sample(const void *logits, int dtype, float temp, unsigned long l
                                 (cudaStream_t)stream);
 }
 
+int pgb_linear_act(const void *x, const void *W, const void *bias, void *y, long long M, int N, int K, int act, void *stream) {
+    if (!x || !W || !y) return PGB_ERR_NULL_POINTER;
+    if (M < 1 || N < 8 || K < 8 || (N % 8) != 0 || (K % 8) != 0 || act < 0 || act > 1) return PGB_ERR_BAD_SHAPE;
+    if (M > 0x7fffffffLL) return PGB_ERR_TOO_LARGE;
+    if (!aligned(x, 16) || !aligned(W, 16) || !aligned(y, 16) || (bias && !aligned(bias, 16))) return PGB_ERR_MISALIGNED;
+    return linear_gelu_launch(x, W, bias, y, M, N, K, act, (cudaStream_t)stream);
+}
+
 int pgb_skinny_linear(const void *x, const void *delta, const void *norm_weight, const void *norm_bias, int norm_kind, float eps,
                       const void *W, const void *bias, int act, void *y, void *x_out, int B, int K, int N, void *stream) {
     if (!x || !W || !y) return PGB_ERR_NULL_POINTER;
@@ -260,7 +270,10 @@ int pgb_tc_error_flag(int *out_host) {
     if (rc == PGB_OK) rc = tc_delta_error_flag(&b);
     int c = 0;
     if (rc == PGB_OK) rc = tc_ws_error_flag(&c);
+    int d = 0;
+    if (rc == PGB_OK) rc = linear_gelu_error_flag(&d);
     b = b > c ? b : c;
+    b = b > d ? b : d;
     *out_host = a > b ? a : b;
     return rc;
 }

@@ -1,0 +1,180 @@
+// y = act(x W^T + bias) for the up-projection of the MLP block (src/model.py:552-560: Linear(d, 4d) followed by GELU), as one
+// persistent tcgen05 GEMM whose epilogue applies the bias and the erf-GELU on the accumulator as it leaves tensor memory.
+// As two ops the activation is a second pass over the 4d-wide hidden tensor (read + write of 2 x M x 4d x 2 bytes, about as
+// long as the GEMM itself at d = 768); fused it costs nothing but epilogue arithmetic that overlaps the next tile's MMAs.
+//
+//   x [M][K] bf16 (K contiguous)  -> A operand, K-major;   W [N][K] bf16 (torch.nn.Linear layout) -> B operand, K-major
+//   tile 128 x 256 x 64, four TMA stages of 48 KiB (128-byte swizzle), accumulators 128 lanes x 256 fp32 columns in tensor
+//   memory, two of them (512 columns) so that the epilogue of tile i runs under the MMAs of tile i + 1.
+//   warp 0: TMA producer;  warp 1: MMA issuer (one elected lane of the converged warp), owns the tensor-memory allocation;
+//   warps 2-9: epilogue -- warp w reads TMEM lanes 32 (w mod 4) .. +31 (one output row per thread) and column half (w-2)/4,
+//   32 columns at a time: + bias, round to bf16 (where the separate Linear would round), GELU in fp32, round, 64-byte stores.
+//   One CTA per SM walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (column blocks fastest, so the CTAs running together
+//   share rows of x in L2). Every mbarrier wait is bounded; a wait that runs out sets the error flag and the CTA winds down.
+#include "tc_common.cuh"
+
+namespace pgb {
+
+constexpr int LG_BM = 128, LG_BN = 256, LG_BK = 64, LG_STAGES = 4;
+constexpr int LG_EPI = 8;                                             // epilogue warps
+constexpr int LG_NT = (2 + LG_EPI) * 32;
+constexpr int LG_A_BYTES = LG_BM * LG_BK * 2, LG_B_BYTES = LG_BN * LG_BK * 2, LG_STAGE = LG_A_BYTES + LG_B_BYTES;
+constexpr int LG_SMEM = LG_STAGES * LG_STAGE + 1024 + 1024;           // stages, barriers, alignment slack
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(0) : "memory");
+}
+__device__ __forceinline__ void lg_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+    uint32_t e;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(e));
+    return e != 0;
+}
+
+__global__ void __launch_bounds__(LG_NT, 1) linear_gelu_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant__ CUtensorMap mw,
+                                                              const __nv_bfloat16 *__restrict__ bias, __nv_bfloat16 *__restrict__ y,
+                                                              long long M, int N, int K, int act) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *sm = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t mb = base + LG_STAGES * LG_STAGE;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + LG_STAGES * LG_STAGE + 128);
+    auto bar_full = [&](int s) { return mb + 8 * s; };
+    auto bar_empty = [&](int s) { return mb + 32 + 8 * s; };
+    auto bar_acc_full = [&](int a) { return mb + 64 + 8 * a; };
+    auto bar_acc_empty = [&](int a) { return mb + 80 + 8 * a; };
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tiles_n = (N + LG_BN - 1) / LG_BN;
+    const long long tiles = ((M + LG_BM - 1) / LG_BM) * tiles_n;
+    const int KB = (K + LG_BK - 1) / LG_BK;
+
+    if (tid == 0) {
+        for (int s = 0; s < LG_STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(bar_acc_full(a), 1); mbar_init(bar_acc_empty(a), LG_EPI); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------------------------------ producer
+        const bool leader = elect_one();
+        uint32_t it = 0;
+        bool ok = true;
+        for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+            const int m0 = (int)(t / tiles_n) * LG_BM, n0 = (int)(t % tiles_n) * LG_BN;
+            for (int kb = 0; kb < KB && ok; ++kb, ++it) {
+                const int s = it % LG_STAGES;
+                if (it >= LG_STAGES) ok = __all_sync(0xffffffffu, mbar_wait(bar_empty(s), ((it / LG_STAGES) + 1) & 1, 71));
+                if (ok && leader) {
+                    const uint32_t sa = base + s * LG_STAGE;
+                    mbar_expect_tx(bar_full(s), LG_STAGE);
+                    tma_load_2d(sa, &mx, bar_full(s), kb * LG_BK, m0);
+                    tma_load_2d(sa + LG_A_BYTES, &mw, bar_full(s), kb * LG_BK, n0);
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------------------------------ MMA issuer
+        constexpr uint32_t IDESC = idesc_bf16(LG_BM, LG_BN, 0, 0);
+        uint32_t it = 0, ti = 0;
+        bool ok = true;
+        for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++ti) {
+            const uint32_t a = ti & 1;
+            if (ti >= 2) ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_empty(a), ((ti >> 1) + 1) & 1, 72));
+            tc_fence_after();
+            for (int kb = 0; kb < KB && ok; ++kb, ++it) {
+                const int s = it % LG_STAGES;
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_full(s), (it / LG_STAGES) & 1, 73));
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t sa = base + s * LG_STAGE;
+                const uint64_t da = smem_desc(sa, 16, 1024), db = smem_desc(sa + LG_A_BYTES, 16, 1024);
+#pragma unroll
+                for (int k = 0; k < LG_BK / 16; ++k) mma_bf16_elect(tmem + a * LG_BN, da + k * 2, db + k * 2, IDESC, (kb | k) != 0);
+                mma_commit_elect(bar_empty(s));                       // the stage is free once these MMAs have read it
+            }
+            if (ok) mma_commit_elect(bar_acc_full(a));
+        }
+    } else {
+        // ------------------------------------------------------------------------------------------ epilogue
+        const int sub = warp & 3, half = (warp - 2) >> 2;
+        const uint32_t lane_base = (uint32_t)(32 * sub) << 16;
+        uint32_t ti = 0;
+        bool ok = true;
+        for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++ti) {
+            const uint32_t a = ti & 1;
+            const long long row = (t / tiles_n) * LG_BM + 32 * sub + lane;
+            const int n0 = (int)(t % tiles_n) * LG_BN + half * (LG_BN / 2);
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full(a), (ti >> 1) & 1, 74));
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < LG_BN / 2; c += 32) {
+                float v[32];
+                tmem_ld32(tmem + lane_base + a * LG_BN + half * (LG_BN / 2) + c, v);
+                tmem_ld_wait();
+                const int col = n0 + c;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {                          // 8 columns = one 16-byte store
+                    if (col + 8 * g < N) {
+                        float bv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                        if (bias != nullptr) {
+                            const uint4 braw = __ldg(reinterpret_cast<const uint4 *>(bias + col + 8 * g));
+                            const __nv_bfloat162 *b2 = reinterpret_cast<const __nv_bfloat162 *>(&braw);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(b2[i]); bv[2 * i] = f.x; bv[2 * i + 1] = f.y; }
+                        }
+                        uint4 outv;
+                        __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(&outv);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            float x0 = __bfloat162float(__float2bfloat16_rn(v[8 * g + 2 * i] + bv[2 * i]));
+                            float x1 = __bfloat162float(__float2bfloat16_rn(v[8 * g + 2 * i + 1] + bv[2 * i + 1]));
+                            if (act == 1) {
+                                x0 = 0.5f * x0 * (1.0f + erff(x0 * 0.70710678118654752f));
+                                x1 = 0.5f * x1 * (1.0f + erff(x1 * 0.70710678118654752f));
+                            }
+                            o2[i] = __floats2bfloat162_rn(x0, x1);
+                        }
+                        if (row < M) *reinterpret_cast<uint4 *>(y + (size_t)row * N + col + 8 * g) = outv;
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) lg_arrive(bar_acc_empty(a));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+int linear_gelu_launch(const void *x, const void *W, const void *bias, void *y, long long M, int N, int K, int act, cudaStream_t stream) {
+    CUtensorMap mx, mw;
+    if (!tc_make_map(&mx, x, 1, M, K, K, (long long)M * K, LG_BM) || !tc_make_map(&mw, W, 1, N, K, K, (long long)N * K, LG_BN)) {
+        set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
+        return PGB_ERR_CUDA;
+    }
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long tiles = ((M + LG_BM - 1) / LG_BM) * ((N + LG_BN - 1) / LG_BN);
+    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+    cudaError_t e = cudaFuncSetAttribute(linear_gelu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LG_SMEM);
+    if (e != cudaSuccess) { set_cuda_error(e, "linear_gelu smem attribute"); return PGB_ERR_CUDA; }
+    linear_gelu_kernel<<<grid, LG_NT, LG_SMEM, stream>>>(mx, mw, (const __nv_bfloat16 *)bias, (__nv_bfloat16 *)y, M, N, K, act);
+    return check_launch("linear_gelu_kernel");
+}
+
+int linear_gelu_error_flag(int *out) { return tc_read_error_flag(out); }
+
+}  // namespace pgb

@@ -104,7 +104,29 @@ CASES = {
     "lambda": (lambda: _lambda(64, 1024, 768), "per-token lambda scan, per-token angle: B64 T1024 D768 fp32"),
     "lambda_bcast": (lambda: _lambda(64, 1024, 768, True), "per-token lambda scan, one angle per channel: B64 T1024 D768 fp32"),
     "add_norm": (lambda: _add_norm(8192, 768), "residual add + RMS norm: 8192 rows of 768 bf16"),
+    "mlp_up": (lambda: _linear_act(8192, 768, 3072), "MLP up-projection + bias + erf-GELU as one tensor-core GEMM: M8192 K768 N3072 bf16"),
+    "skinny": (lambda: _skinny(1, 768, 3072), "decode-step linear (add + RMS norm + linear + GELU) at batch 1: K768 N3072 bf16"),
 }
+
+# floating-point operations per launch of the cases that are bound by the tensor pipe rather than by HBM
+FLOPS = {"mlp_up": 2 * 8192 * 768 * 3072}
+
+
+def _linear_act(M, K, N):
+    dev = "cuda"
+    x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    W = (torch.randn(N, K, device=dev) * K ** -0.5).to(torch.bfloat16)
+    b = torch.randn(N, device=dev).to(torch.bfloat16)
+    return (lambda: ops.linear_act(x, W, b, act="gelu")), (M * K + N * K + N + M * N) * 2
+
+
+def _skinny(B, K, N):
+    dev = "cuda"
+    x, dl = (torch.randn(B, K, device=dev).to(torch.bfloat16) for _ in range(2))
+    W = (torch.randn(N, K, device=dev) * K ** -0.5).to(torch.bfloat16)
+    b = torch.randn(N, device=dev).to(torch.bfloat16)
+    norm = torch.nn.RMSNorm(K).to(dev).to(torch.bfloat16)
+    return (lambda: ops.skinny_linear(x, W, b, delta=dl, norm=norm, act="gelu")), (N * K + N + 3 * B * K + B * N) * 2
 
 
 def time_case(name: str, iters: int = 20, flush_mb: int = 256):

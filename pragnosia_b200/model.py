@@ -24,8 +24,13 @@ class MLP(nn.Module):
     def forward(self, x):
         return x + self.ff(self.n(x))
 
+    fused_up = False    # (off until measured) bf16 on CUDA: Linear(d, mult*d) + GELU as one tensor-core GEMM with the activation in its epilogue
+
     def ff(self, z):
         """The block without its norm and residual add."""
+        if (self.fused_up and z.is_cuda and z.dtype == torch.bfloat16 and self.a.weight.dtype == torch.bfloat16
+                and z.shape[-1] % 8 == 0 and self.a.weight.shape[0] % 8 == 0 and z.numel() // z.shape[-1] >= 128):
+            return self.b(ops.linear_act(z, self.a.weight, self.a.bias, act="gelu"))
         return self.b(F.gelu(self.a(z)))
 
 

@@ -347,3 +347,17 @@ def decode_sample(logits, temp, seed, tok, count, ticket, hist=None, pos=None, s
                                   cols, ptr(count), ptr(pos), ptr(shift), ptr(ticket), B, V, int(ctx), stream_of(logits)),
           "pgb_decode_sample")
     return tok
+
+
+def linear_act(x, W, bias=None, act: Optional[str] = "gelu"):
+    """act(x W^T + bias) as one tensor-core GEMM with the bias and the (erf) GELU in its epilogue; x (..., K) bf16, W (N, K)."""
+    need_cuda(x, W)
+    if x.dtype != torch.bfloat16 or W.dtype != torch.bfloat16:
+        raise ValueError("linear_act: bf16 only")
+    K, N = x.shape[-1], W.shape[0]
+    x2 = x.reshape(-1, K).contiguous()
+    y = torch.empty(x2.shape[0], N, device=x.device, dtype=x.dtype)
+    b = None if bias is None else bias.to(x.dtype).contiguous()
+    check(lib().pgb_linear_act(ptr(x2), ptr(W.contiguous()), ptr(b), ptr(y), x2.shape[0], N, K, 1 if act == "gelu" else 0,
+                               stream_of(x)), "pgb_linear_act")
+    return y.view(*x.shape[:-1], N)

@@ -1,4 +1,6 @@
 """Parity of the CUDA kernels (called through the C ABI) against the CPU oracle and the reference-generated fixtures."""
+import ctypes
+
 import pytest
 import torch
 import torch.nn.functional as F
@@ -435,3 +437,27 @@ def test_decode_embed_and_sampler():
     lg = torch.randn(B, 1000, generator=g).to(DEV)
     ops.decode_sample(lg.to(torch.bfloat16), 0.0, 9, t, torch.zeros(1, dtype=torch.long, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV))
     assert torch.equal(t, lg.to(torch.bfloat16).float().argmax(-1))
+
+
+@pytest.mark.parametrize("M,K,N", [(8192, 768, 3072), (300, 768, 3072), (128, 64, 256), (1000, 200, 520)])
+@pytest.mark.parametrize("act", ["gelu", None])
+def test_linear_act_tensor_core_gemm(M, K, N, act):
+    """The fused Linear + bias + erf-GELU GEMM (the MLP up-projection of src/model.py:552-560) against the separate torch
+    ops in bf16 and against the fp32 product of the same rounded operands; ragged M, K, N exercise the zero-filled tiles."""
+    g = torch.Generator().manual_seed(M + K + N)
+    bf = lambda t: t.to(DEV).to(torch.bfloat16)
+    x, W, b = bf(torch.randn(M, K, generator=g)), bf(torch.randn(N, K, generator=g) * K ** -0.5), bf(0.2 * torch.randn(N, generator=g))
+    y = ops.linear_act(x, W, b, act=act)
+    assert y.dtype == torch.bfloat16 and tuple(y.shape) == (M, N)
+    pre = F.linear(x.float(), W.float(), b.float()).to(torch.bfloat16).float()
+    exact = F.gelu(pre) if act == "gelu" else pre
+    assert rel_err(y.float().cpu(), exact.cpu()) <= 4e-3                      # one bf16 ulp of the largest value
+    ref = F.linear(x, W, b)
+    ref = F.gelu(ref) if act == "gelu" else ref
+    assert rel_err(y.float().cpu(), ref.float().cpu()) <= 8e-3
+    assert torch.equal(y, ops.linear_act(x, W, b, act=act))                   # deterministic
+    y3 = ops.linear_act(x.view(-1, 1, K) if M % 1 == 0 else x, W, None, act=act)
+    assert tuple(y3.shape) == (M, 1, N)
+    out = ctypes.c_int(-1)
+    _lib.check(_lib.lib().pgb_tc_error_flag(ctypes.byref(out)), "pgb_tc_error_flag")
+    assert out.value == 0
