@@ -52,6 +52,8 @@ __global__ void __launch_bounds__(AN_WARPS * 32)
 add_norm_kernel(const T_ *__restrict__ x, const T_ *__restrict__ delta, const T_ *__restrict__ w, const T_ *__restrict__ b,
                 float eps, T_ *__restrict__ y, T_ *__restrict__ z, long long rows, int d) {
     constexpr int N = Piece<T_>::N;
+    pdl_wait();                                                    // launched as a programmatic dependent (a no-op otherwise)
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * AN_WARPS + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -110,7 +112,8 @@ int add_norm_launch(const void *x, const void *delta, const void *w, const void 
     if (ctas > 0x7fffffffLL) return PGB_ERR_TOO_LARGE;
     // 16-byte pieces per lane: 1, 2, 3, 4 or 8 (the row stays in registers, so the buffer is sized to the row)
     const int n = dtype == PGB_BF16 ? 8 : 4, need = (d / n + 31) / 32;
-#define PGB_AN2(T_, K_, C_) add_norm_kernel<T_, K_, C_><<<(unsigned)ctas, AN_WARPS * 32, 0, stream>>>( \
+    cudaError_t le = cudaSuccess;
+#define PGB_AN2(T_, K_, C_) le = pdl_launch(add_norm_kernel<T_, K_, C_>, dim3((unsigned)ctas), dim3(AN_WARPS * 32), 0, stream, \
         (const T_ *)x, (const T_ *)delta, (const T_ *)w, (const T_ *)b, eps, (T_ *)y, (T_ *)z, rows, d)
 #define PGB_AN(T_, K_) do { if (need <= 1) PGB_AN2(T_, K_, 1); else if (need <= 2) PGB_AN2(T_, K_, 2); else if (need <= 3) PGB_AN2(T_, K_, 3); \
         else if (need <= 4) PGB_AN2(T_, K_, 4); else PGB_AN2(T_, K_, 8); } while (0)
@@ -118,6 +121,7 @@ int add_norm_launch(const void *x, const void *delta, const void *w, const void 
     else { if (kind == 0) PGB_AN(float, 0); else PGB_AN(float, 1); }
 #undef PGB_AN
 #undef PGB_AN2
+    if (le != cudaSuccess) { set_cuda_error(le, "add_norm launch"); return PGB_ERR_CUDA; }
     return check_launch("add_norm_kernel");
 }
 

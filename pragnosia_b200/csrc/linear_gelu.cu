@@ -74,6 +74,9 @@ __global__ void __launch_bounds__(LG_NT, 1) linear_gelu_kernel(const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    // Launched as a programmatic dependent: the set-up above overlaps the tail of the kernel that produces x.
+    pdl_wait();
+    pdl_launch_dependents();
 
     if (warp == 0) {
         // ------------------------------------------------------------------------------------------ producer
@@ -184,7 +187,9 @@ int linear_gelu_launch(const void *x, const void *W, const void *bias, void *y, 
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
     cudaError_t e = cudaFuncSetAttribute(linear_gelu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LG_SMEM);
     if (e != cudaSuccess) { set_cuda_error(e, "linear_gelu smem attribute"); return PGB_ERR_CUDA; }
-    linear_gelu_kernel<<<grid, LG_NT, LG_SMEM, stream>>>(mx, mw, (const __nv_bfloat16 *)bias, (__nv_bfloat16 *)y, M, N, K, act);
+    e = pdl_launch(linear_gelu_kernel, dim3(grid), dim3(LG_NT), (size_t)LG_SMEM, stream, mx, mw, (const __nv_bfloat16 *)bias,
+                   (__nv_bfloat16 *)y, M, N, K, act);
+    if (e != cudaSuccess) { set_cuda_error(e, "linear_gelu launch"); return PGB_ERR_CUDA; }
     return check_launch("linear_gelu_kernel");
 }
 

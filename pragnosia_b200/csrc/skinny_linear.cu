@@ -81,10 +81,12 @@ __global__ void __launch_bounds__(SK_WARPS * 32) skinny_linear_kernel(SkinnyArgs
     // ---- z for every row of the batch (skipped when there is nothing to add or normalise: z is x, read in place)
     const bool direct = a.delta == nullptr && a.norm_kind == 0 && a.x_out == nullptr;
     if (!direct) {
-        for (int b = warp; b < a.nb; b += SK_WARPS) {
+        // One row (B = 1): every warp builds the whole row for itself -- a lane later reads back exactly the pieces it wrote
+        // (the warps store identical values to the same places), so no warp waits for another. More rows: a warp per row.
+        for (int b = (B == 1 ? 0 : warp); b < a.nb; b += (B == 1 ? 1 : SK_WARPS)) {
             const uint4 *xr = reinterpret_cast<const uint4 *>(a.x + (size_t)b * a.K);
             const uint4 *dr = a.delta != nullptr ? reinterpret_cast<const uint4 *>(a.delta + (size_t)b * a.K) : nullptr;
-            uint4 *xo = (a.x_out != nullptr && blockIdx.x == 0) ? reinterpret_cast<uint4 *>(a.x_out + (size_t)b * a.K) : nullptr;
+            uint4 *xo = (a.x_out != nullptr && blockIdx.x == 0 && (B > 1 || warp == 0)) ? reinterpret_cast<uint4 *>(a.x_out + (size_t)b * a.K) : nullptr;
             float v[SK_ROWREG][8];                                    // the lane's pieces of the row (K <= 1024), else re-read from zs
             float s1 = 0.f, s2 = 0.f;
 #pragma unroll
@@ -169,7 +171,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32) skinny_linear_kernel(SkinnyArgs
                 }
             }
         }
-        __syncthreads();
+        if (B == 1) __syncwarp(); else __syncthreads();
     }
 
     // ---- this warp's output rows
