@@ -216,8 +216,9 @@ def product_arm(args):
                    "parallelism": f"batch-sharded x{world}, no data-path collective"},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": ids_host.numel() * 8,
                 "d2h_bytes_per_step": out_host.numel() * 2},
-        # this library's kernels per step: per window and layer one fused prefill and two add+norm, plus the final norm
-        "gpu_launches": args.steps * ((T_TOTAL // WINDOW) * CFG["layers"] * 3 + 1),
+        # this library's kernels per step: per window and layer one fused prefill, one fused up-projection GEMM and two
+        # add+norm, plus the final norm before the head
+        "gpu_launches": args.steps * ((T_TOTAL // WINDOW) * CFG["layers"] * 4 + 1),
         "clocks": clocks,
     }
     if rank == 0 and args.step_only:
