@@ -138,6 +138,10 @@ __global__ void __launch_bounds__(WS_NT, 1) prefill_tc_ws_kernel(const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    // Launched as a programmatic dependent: the set-up above may overlap the tail of the kernel that produces q, k, v;
+    // nothing it produced is read, and nothing is written, before this point.
+    pdl_wait();
+    pdl_launch_dependents();
 
     if (warp < WS_FRONT) {
         // =========================================================================================== front
@@ -591,12 +595,13 @@ int prefill_tc_ws_launch(const PrefillArgs &a, int o_dtype, cudaStream_t stream)
     if (a.raw) {
         e = cudaFuncSetAttribute(prefill_tc_ws_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, WsSmem::bytes);
         if (e != cudaSuccess) { set_cuda_error(e, "prefill_tc_ws smem attribute"); return PGB_ERR_CUDA; }
-        prefill_tc_ws_kernel<true><<<(unsigned)BH, WS_NT, WsSmem::bytes, stream>>>(mq, mk, mv, p);
+        e = pdl_launch(prefill_tc_ws_kernel<true>, dim3((unsigned)BH), dim3(WS_NT), (size_t)WsSmem::bytes, stream, mq, mk, mv, p);
     } else {
         e = cudaFuncSetAttribute(prefill_tc_ws_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, WsSmem::bytes);
         if (e != cudaSuccess) { set_cuda_error(e, "prefill_tc_ws smem attribute"); return PGB_ERR_CUDA; }
-        prefill_tc_ws_kernel<false><<<(unsigned)BH, WS_NT, WsSmem::bytes, stream>>>(mq, mk, mv, p);
+        e = pdl_launch(prefill_tc_ws_kernel<false>, dim3((unsigned)BH), dim3(WS_NT), (size_t)WsSmem::bytes, stream, mq, mk, mv, p);
     }
+    if (e != cudaSuccess) { set_cuda_error(e, "prefill_tc_ws launch"); return PGB_ERR_CUDA; }
     return check_launch("prefill_tc_ws_kernel");
 }
 
