@@ -341,7 +341,7 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
         tc_fence_before();
         __syncthreads();
         TD_MARK(3);
-        // ---- round 1: P = Q K^T, KS = K S, O2 = Q S
+        // ---- first product group: P = Q K^T, KS = K S, O2 = Q S
         const uint64_t dsh = smem_desc(base + SM::off_sh, 16, 1024), dsl = smem_desc(base + SM::off_sl, 16, 1024);
         // Everyone waits for the round, so issue time counts: the three products go out from three warps (one accumulator
         // each, so no ordering between them is needed), each through one elected lane of the converged warp, which keeps the
@@ -409,7 +409,7 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
         tc_fence_before();
         __syncthreads();
         TD_MARK(6);
-        // ---- round 2: W = X rhs  (head*head + head*tail + tail*head)
+        // ---- second product group: W = X rhs  (head*head + head*tail + tail*head)
         const uint64_t dwh = smem_desc(base + SM::off_wh, 16, 1024), dwl = smem_desc(base + SM::off_wl, 16, 1024);
         if (warp == 0 && __all_sync(0xffffffffu, ok)) {               // the whole warp, converged: one elected lane issues
             tc_fence_after();
@@ -446,7 +446,7 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
         tc_fence_before();
         __syncthreads();
         TD_MARK(9);
-        // ---- round 3: O1 = A W, U = (K w)^T W
+        // ---- third product group: O1 = A W, U = (K w)^T W
         if (warp < 2 && __all_sync(0xffffffffu, ok)) {                // O1 from one warp's elected lane, U from another's
             tc_fence_after();
             constexpr uint32_t I_O = idesc_bf16(64, 64, 0, 1), I_U = idesc_bf16(D, 64, 1, 1);

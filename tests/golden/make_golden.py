@@ -19,7 +19,9 @@ import torch.nn.functional as F
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
 sys.path.insert(0, str(ROOT))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of the reference repository>")
+REF = sys.argv[1]
 sys.path.insert(0, REF)
 
 import oracle                                                    # noqa: E402
