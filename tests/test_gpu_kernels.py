@@ -461,3 +461,26 @@ def test_linear_act_tensor_core_gemm(M, K, N, act):
     out = ctypes.c_int(-1)
     _lib.check(_lib.lib().pgb_tc_error_flag(ctypes.byref(out)), "pgb_tc_error_flag")
     assert out.value == 0
+
+
+def test_windowed_walks_equal_single_calls():
+    """pragnosia_b200.sharded on one GPU (gather disabled): walking a sequence window by window with the carried state
+    gives the single call's outputs and final state, for the prefill (both rules) and the lambda scan."""
+    from pragnosia_b200 import sharded
+    d = lambda t: t.to(DEV)
+    x = synth.assoc_op_inputs(2, 3, 320, 64, seed=31, delta=True, with_state=True)
+    q, k, v = (d(x[n]).to(torch.bfloat16) for n in "qkv")
+    la, be, S0 = d(x["la"]), d(x["beta"]), d(x["S0"])
+    for beta in (None, be):
+        o, S, _ = ops.prefill(q, k, v, la, beta, S0, out_dtype=torch.bfloat16)
+        outs, Sw = sharded.prefill_windows(q, k, v, la, 128, beta=beta, S0=S0)
+        assert [t.shape[2] for t in outs] == [128, 128, 64]
+        assert rel_err(torch.cat(outs, 2).float().cpu(), o.float().cpu()) <= 1e-5 and rel_err(Sw.cpu(), S.cpu()) <= 1e-5
+    y = synth.lambda_scan_inputs(3, 300, 96, seed=32, with_state=True)
+    u, lm, an, h0 = d(y["u"]), d(y["logmag"]), d(y["ang"]), tuple(d(t) for t in y["h0"])
+    full, hf = ops.lambda_scan(u, lm, an, h0=h0)
+    ys, hw = sharded.lambda_scan_windows(u, lm, an, 128, h0=h0)
+    assert rel_err(torch.cat(ys, 1).cpu(), full.cpu()) <= 1e-5
+    assert rel_err(hw[0].cpu(), hf[0].cpu()) <= 1e-5 and rel_err(hw[1].cpu(), hf[1].cpu()) <= 1e-5
+    got = sharded.run_windows(lambda w: u[:, w * 100:(w + 1) * 100].contiguous(), 3)
+    assert torch.equal(torch.cat(got, 1), u)
