@@ -232,6 +232,11 @@ int pgb_linear_act(const void *x, const void *W, const void *bias, void *y, long
  * Unlike every other entry point it SYNCHRONISES the device. No counterpart in the reference. */
 int pgb_tc_error_flag(int *out_host);
 
+/* Self-test of that failure path: launches one thread that waits, with the kernels' bounded loop, on an mbarrier nothing
+ * arrives at. After `limit_cycles` of the SM clock (1 .. 2^31) the wait gives up, the flag reads 99 and the kernel returns
+ * normally -- the context stays usable. Nothing faults, traps or hangs. No counterpart in the reference. */
+int pgb_tc_wait_selftest(long long limit_cycles, void *stream);
+
 /* Which plain-rule tensor-core kernel head dim 64 uses: 0 (default) = the warp-specialised pipeline, 1 = the single-role
  * kernel that head dim 128 always uses. Process-wide; for A/B timing and tests. No counterpart in the reference. */
 int pgb_tc_set_variant(int variant);

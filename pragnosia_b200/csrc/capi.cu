@@ -22,6 +22,7 @@ int prefill_tc_launch(const PrefillArgs &, int, int, cudaStream_t);
 bool prefill_tc_supported(int io_dtype, int D, bool delta);
 int decode_launch(const DecodeArgs &, int, int, int, int, cudaStream_t);
 int tc_error_flag(int *out);
+int tc_wait_selftest_launch(long long, cudaStream_t);
 int tc_delta_error_flag(int *out);
 int tc_ws_error_flag(int *out);
 int prefill_tc_ws_launch(const PrefillArgs &, int, cudaStream_t);
@@ -261,6 +262,11 @@ int pgb_tc_set_variant(int variant) {
     if (variant != 0 && variant != 1) return PGB_ERR_BAD_SHAPE;
     g_tc_variant = variant;
     return PGB_OK;
+}
+
+int pgb_tc_wait_selftest(long long limit_cycles, void *stream) {
+    if (limit_cycles < 1 || limit_cycles > (1ll << 31)) return PGB_ERR_BAD_SHAPE;      // at most about a second of SM clock
+    return tc_wait_selftest_launch(limit_cycles, (cudaStream_t)stream);
 }
 
 int pgb_tc_error_flag(int *out_host) {

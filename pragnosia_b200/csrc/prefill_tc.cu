@@ -557,4 +557,26 @@ int tc_phase_dump(unsigned long long *out16) {
 
 int tc_error_flag(int *out) { return tc_read_error_flag(out); }
 
+// Self-test of the failure path every tensor-core kernel here relies on: one thread waits, with the same bounded loop, on
+// an mbarrier that nothing ever arrives at; the wait runs out after `limit_cycles` of the SM clock, the error flag is set
+// to 99 and the kernel returns normally, leaving the context usable.
+__global__ void tc_wait_selftest_kernel(long long limit_cycles) {
+    __shared__ __align__(8) unsigned long long bar;
+    if (threadIdx.x != 0) return;
+    const uint32_t b = smem_u32(&bar);
+    mbar_init(b, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const long long t0 = clock64();
+    bool flipped = false;
+    do {
+        for (int i = 0; i < 32 && !flipped; ++i) flipped = mbar_try(b, 0);
+    } while (!flipped && clock64() - t0 < limit_cycles);
+    if (!flipped) atomicExch(&g_tc_error, 99);
+}
+
+int tc_wait_selftest_launch(long long limit_cycles, cudaStream_t stream) {
+    tc_wait_selftest_kernel<<<1, 32, 0, stream>>>(limit_cycles);
+    return check_launch("tc_wait_selftest_kernel");
+}
+
 }  // namespace pgb

@@ -168,3 +168,19 @@ def test_delta_known_answers_tensor_cores(golden):
     r2, rS2 = oracle.assoc_scan(q.float(), k.float(), v.float(), la, S0, beta=be)
     check(torch.cat([a[0], b[0]], 2), b[1], r2, rS2, "delta two windows")
     assert flag() == 0
+
+
+def test_a_wait_that_runs_out_sets_the_flag_and_leaves_the_context_usable():
+    """Failure detection without a fault: a wait on an mbarrier that nothing sets gives up after its cycle limit, the
+    kernel returns normally, the flag reads 99 once (reading clears it), and the next launch works as usual."""
+    L = _lib.lib()
+    assert flag() == 0
+    _lib.check(L.pgb_tc_wait_selftest(1 << 20, None), "pgb_tc_wait_selftest")       # about half a millisecond
+    torch.cuda.synchronize()
+    assert flag() == 99 and flag() == 0
+    assert L.pgb_tc_wait_selftest(0, None) == 2
+    q, k, v, la, _ = inputs(1, 2, 128, 64, seed=5, with_state=False)
+    ro, rS = oracle.assoc_scan(q.float(), k.float(), v.float(), la, None)
+    o, S, _ = run(q, k, v, la, None, out_dtype=torch.float32)
+    check(o, S, ro, rS, "after the timed-out wait")
+    assert flag() == 0
