@@ -183,7 +183,11 @@ struct TdSmem {
     static constexpr int SQ = TC_C * TC_C * 2;                        // a 64 x 64 bf16 tile (V slice, X, A, rhs / W)
     static constexpr int STAGE = 2 * QK + 3 * SQ;                     // Q, K, V slice, X head, X tail
     static constexpr int off_stage = 0;                               // [2]
-    static constexpr int off_kwh = 2 * STAGE;
+    // Head dim 128 double-buffers the tiles and fills the SM with one CTA. Head dim 64 keeps ONE stage (its next load is
+    // issued as soon as the second product group has consumed the tiles and lands under the rest of the chunk), which
+    // brings the CTA to 108 KiB: two CTAs share an SM and fill each other's tensor-core and barrier waits.
+    static constexpr int NSTAGE = D == 64 ? 1 : 2;
+    static constexpr int off_kwh = NSTAGE * STAGE;
     static constexpr int off_kwl = off_kwh + QK;
     static constexpr int off_ah = off_kwl + QK;
     static constexpr int off_al = off_ah + SQ;
@@ -289,12 +293,12 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
     TD_MARK_INIT;
 
     for (int c = 0; c < NC && ok; ++c) {
-        const int t0 = c * TC_C, st = c & 1;
+        const int t0 = c * TC_C, st = SM::NSTAGE == 2 ? (c & 1) : 0;
         TD_MARK(0);
         const uint32_t sb = base + SM::off_stage + st * SM::STAGE;
         const uint32_t qs = sb, ks = sb + SM::QK, vs = sb + 2 * SM::QK, xh = vs + SM::SQ, xl = xh + SM::SQ;
         uint8_t *ks_ptr = sm + SM::off_stage + st * SM::STAGE + SM::QK, *vs_ptr = ks_ptr + SM::QK;
-        if (tid == 0 && c + 1 < NC) load_stage(c + 1, st ^ 1);
+        if (SM::NSTAGE == 2 && tid == 0 && c + 1 < NC) load_stage(c + 1, st ^ 1);
         const float *Ls = stats + (c & 1) * 256, *eLs = Ls + 64, *wts = eLs + 64, *bes = wts + 64;
         // ---- entering state slice as an MN-major B operand (rows = key index), head and tail
         {
@@ -316,7 +320,7 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
                 }
         }
         TD_MARK(1);
-        if (!mbar_wait(st ? bar_full1 : bar_full0, (c >> 1) & 1, 21)) ok = false;
+        if (!mbar_wait(st ? bar_full1 : bar_full0, (SM::NSTAGE == 2 ? (c >> 1) : c) & 1, 21)) ok = false;
         __syncthreads();
         TD_MARK(2);
         const float aC = expf(Ls[TC_C - 1]);
@@ -426,6 +430,9 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
         TD_MARK(7);
         if (ok && !mbar_wait(bar_b, c & 1, 23)) ok = false;
         tc_fence_after();
+        // single stage: Q, K, V and X of this chunk are consumed (the first two product groups are complete, the generic
+        // reads of K and V ended before the barrier ahead of the second), so the next chunk's tiles may overwrite them
+        if (SM::NSTAGE == 1 && tid == 0 && ok && c + 1 < NC) load_stage(c + 1, 0);
         TD_MARK(8);
         if (ok) {
             // ---- W back to shared memory (over rhs), head and tail
