@@ -60,6 +60,28 @@ int pgb_lambda_scan_fwd_ex(const float *u, const float *logmag, const float *ang
                            long long ang_stride_t, const float *h0r, const float *h0i, float *y, float *hr_out,
                            float *hi_out, int B, int T, int D, int time_segments, void *stream);
 
+/* The number of time segments a warp scans in parallel that pgb_lambda_scan_fwd picks for this shape on a GPU with
+ * sm_count multiprocessors (host arithmetic only; 0 for a bad shape): more segments when channels are too few to fill the
+ * GPU, never more than the sequence has pieces to hand out. No counterpart in the reference. */
+int pgb_lambda_scan_time_segments(int B, int T, int D, int sm_count);
+
+/* The same forward pass for a caller that will differentiate through it: additionally stores Im h_t for every token
+ * (hi_all [B][T][D] fp32), which the adjoint needs. Replaces _Scan.forward, src/scan_kernel.py:105-119, which saves both
+ * components. */
+int pgb_lambda_scan_fwd_train(const float *u, const float *logmag, const float *ang, long long ang_stride_b,
+                              long long ang_stride_t, const float *h0r, const float *h0i, float *y, float *hi_all,
+                              float *hr_out, float *hi_out, int B, int T, int D, void *stream);
+/* Adjoint of the recurrence, run backwards in time as a chunked shuffle scan.
+ * Replaces src/scan_kernel.py:54-101 _bwd (driven by _Scan.backward :121-140).
+ *   g [B][T][D]: gradient on Re h_t (the caller has already added the gradient on the final Re state to g[:, T-1]);
+ *   g_last_i [B][D] or NULL: gradient on the final Im state.  u, logmag, ang: the forward inputs; hr_all (= y), hi_all:
+ *   the forward outputs of pgb_lambda_scan_fwd_train.
+ *   du, dlogmag, dang [B][T][D] fp32 (dang is per token even when ang was one value per channel: the caller sums).
+ *   dh0r, dh0i [B][D]: gradient on the entering state, or both NULL. */
+int pgb_lambda_scan_bwd(const float *g, const float *u, const float *logmag, const float *ang, long long ang_stride_b,
+                        long long ang_stride_t, const float *hr_all, const float *hi_all, const float *g_last_i, float *du,
+                        float *dlogmag, float *dang, float *dh0r, float *dh0i, int B, int T, int D, void *stream);
+
 /* ---------------------------------------------------------------------------------------------------------
  * Fused plumbing before the scan: L2-normalise q, k, v per head, scale k by sigmoid(gate), rotate q and k by
  * pos[t] * theta[h][i] per channel pair, cast, and transpose (B,T,H,D) -> (B,H,T,D).
@@ -73,6 +95,55 @@ int pgb_aspin_prep_fwd(const void *qp, const void *kp, const void *vp, int in_dt
                        long long in_stride_t, long long in_stride_h, const void *gate, long long gate_stride_b,
                        long long gate_stride_t, const float *theta, const long long *pos, void *q, void *k,
                        void *v, int out_dtype, int B, int T, int H, int D, void *stream);
+
+/* Gradient of pgb_aspin_prep_fwd. Replaces src/assoc_kernel.py:774-826 _prep_bwd (op membrae::assoc_prep_bwd :850).
+ *   qp, kp, vp, gate, theta, pos: the forward inputs, same strides.  dq, dk, dv: grad_dtype, contiguous (B,H,T,D).
+ *   dqp, dkp, dvp: in_dtype, contiguous (B,T,H,D).  dgate [B][T][H] fp32 (required when gate is given).
+ *   dtheta_partial [B * pgb_aspin_prep_bwd_tiles(T)][H][D/2] fp32: one partial per CTA; theta's gradient is their sum
+ *   over the first axis (a fixed summation order, so results repeat bit for bit). */
+int pgb_aspin_prep_bwd(const void *qp, const void *kp, const void *vp, int in_dtype, long long in_stride_b, long long in_stride_t,
+                       long long in_stride_h, const void *gate, long long gate_stride_b, long long gate_stride_t, const float *theta,
+                       const long long *pos, const void *dq, const void *dk, const void *dv, int grad_dtype, void *dqp, void *dkp,
+                       void *dvp, float *dgate, float *dtheta_partial, int B, int T, int H, int D, void *stream);
+int pgb_aspin_prep_bwd_tiles(int T);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * The reference's op-level pieces of the chunked scan as stand-alone operators with its argument lists. The fused
+ * prefill above replaces all of them on the product path; these serve code written against the individual ops.
+ * Plain fp32 arithmetic; sent / X / W are bf16 as the reference stores them. D in {64,128}; B*H <= 65535.
+ *
+ * pgb_assoc_out_fwd    replaces membrae::assoc_out (src/assoc_kernel.py:128-138, kernel _fwd_out :49-70):
+ *   o = ((q k^T) * dec) v + (q e^L) sent[c] per 64-token chunk.  q, k, v, o [B][H][T][D] io_dtype; la [B][H][T];
+ *   sent [B][H][ceil(T/64)][D][D] bf16 (the state entering each chunk).
+ * pgb_prefix_scan_fwd  replaces membrae::prefix_scan (:231-244, kernels _chunk_kv :223, _prefix_fwd :189-202):
+ *   sent[c] = S;  S = exp(a_log[c]) S + (k w)^T v.  k, v [B][H][NC*64][D] (whole chunks); w [B][H][NC][64];
+ *   a_log [B][H][NC]; S0 [B][H][D][D] fp32 or NULL; outputs sent (bf16) and sfin [B][H][D][D] fp32.
+ * pgb_delta_inv_fwd    replaces membrae::delta_inv (:658-667, kernels _inv_build :556, _inv_solve :571-622):
+ *   X [B][H][ceil(T/64)][64][64] bf16 = (I + beta strictly_lower((k k^T) dec))^-1; k bf16 [B][H][T][D], 16-byte aligned.
+ * pgb_delta_loop_fwd   replaces membrae::delta_loop_fwd (:363-378, kernel _delta_loop_fwd :333-360):
+ *   per chunk rhs = beta (v - e^L k S), W = X rhs, S = e^{L_C} S + (k w)^T W; outputs W [B][H][T][D] bf16, sent, sfin.
+ * ------------------------------------------------------------------------------------------------------- */
+int pgb_assoc_out_fwd(const void *q, const void *k, const void *v, int io_dtype, const float *la, const void *sent, void *o, int B,
+                      int H, int T, int D, void *stream);
+int pgb_prefix_scan_fwd(const void *k, const void *v, int io_dtype, const float *w, const float *a_log, const float *S0, void *sent,
+                        float *sfin, int B, int H, int NC, int D, void *stream);
+int pgb_delta_inv_fwd(const void *k, const float *la, const float *beta, void *X, int B, int H, int T, int D, void *stream);
+int pgb_delta_loop_fwd(const void *k, const void *v, int io_dtype, const float *la, const float *beta, const void *X, const float *S0,
+                       void *W, void *sent, float *sfin, int B, int H, int T, int D, void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Optional steps of the layer between its projections and the scan.
+ * pgb_key_topk_mask  (src/assoc.py:435-439): in place, keep the topk largest-magnitude coordinates of every key row and
+ *   zero the rest.  kp: dtype view (B,T,H,D) with element strides (stride_b, stride_t, stride_h), unit over D.
+ * pgb_short_conv_fwd (src/assoc.py:361-382 _sconv): depthwise causal convolution over the last K tokens of the
+ *   concatenated q|k|v projections.  x: view (B,T,C) with strides (stride_b, stride_t), C = 3d; w [C][K];
+ *   cache_in [B][C][K-1] (the previous call's last K-1 inputs) or NULL; y [B][T][C]; cache_out [B][C][K-1] (must not be
+ *   cache_in).  y[t] = sum_j w[:, j] x[t + j - (K-1)].
+ * ------------------------------------------------------------------------------------------------------- */
+int pgb_key_topk_mask(void *kp, int dtype, long long stride_b, long long stride_t, long long stride_h, int B, int T, int H, int D,
+                      int topk, void *stream);
+int pgb_short_conv_fwd(const void *x, int dtype, long long stride_b, long long stride_t, const void *w, const void *cache_in, void *y,
+                       void *cache_out, int B, int T, int C, int K, void *stream);
 
 /* ---------------------------------------------------------------------------------------------------------
  * Chunked prefill of the associative carrier, plain rule (beta == NULL) or delta rule, one fused pass:
@@ -196,6 +267,14 @@ int pgb_add_norm(const void *x, const void *delta, const void *weight, const voi
  * ------------------------------------------------------------------------------------------------------- */
 int pgb_skinny_linear(const void *x, const void *delta, const void *norm_weight, const void *norm_bias, int norm_kind, float eps,
                       const void *W, const void *bias, int act, void *y, void *x_out, int B, int K, int N, void *stream);
+/* The kernel is launched as a programmatic dependent of whatever precedes it on the stream and requests W, the norm
+ * vectors and the bias BEFORE it waits for that predecessor: they must already be complete when the preceding kernel
+ * was launched (model weights are). If the preceding kernel on the stream may have written any of them (a dtype cast, a
+ * freshly concatenated weight), pass PGB_SKINNY_FRESH_CONSTANTS in flags and every such load moves behind the wait. */
+enum { PGB_SKINNY_FRESH_CONSTANTS = 1 };
+int pgb_skinny_linear_ex(const void *x, const void *delta, const void *norm_weight, const void *norm_bias, int norm_kind, float eps,
+                         const void *W, const void *bias, int act, void *y, void *x_out, int B, int K, int N, int flags,
+                         void *stream);
 
 /* ---------------------------------------------------------------------------------------------------------
  * The two ends of a decode step as single launches, so that a token is a fixed kernel sequence with no work on the host
@@ -216,6 +295,11 @@ int pgb_decode_embed(const long long *tok, const long long *pos, const void *E, 
 int pgb_decode_sample(const void *logits, int dtype, float temp, unsigned long long seed, long long *tok, long long *hist,
                       int hist_cols, long long *count, long long *pos, float *shift, unsigned int *ticket, int B, int V, int ctx,
                       void *stream);
+/* The same draw with min-p filtering (src/bench.py:38, 79-86 MEMBRAE_MIN_P): ids whose probability is below min_p times the
+ * most likely id's are dropped before the draw; min_p in [0, 1], 0 = off. */
+int pgb_decode_sample_ex(const void *logits, int dtype, float temp, float min_p, unsigned long long seed, long long *tok,
+                         long long *hist, int hist_cols, long long *count, long long *pos, float *shift, unsigned int *ticket,
+                         int B, int V, int ctx, void *stream);
 
 /* ---------------------------------------------------------------------------------------------------------
  * y = act(x W^T + bias) as one tcgen05 GEMM with the bias and the activation applied on the accumulator in the epilogue.

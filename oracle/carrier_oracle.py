@@ -17,7 +17,7 @@ __all__ = [
     "rotate", "plain_literal", "delta_literal", "unit_lower_inverse", "assoc_scan", "lambda_literal",
     "lambda_scan", "decode_step", "assoc_layer", "fspin_layer", "mlp_block", "lm_layers", "lm_forward_carried",
     "lm_prefill", "lm_decode_step", "init_lm_params", "init_assoc_params", "init_fspin_params", "lm_config",
-    "rel_err", "decode_rebase",
+    "rel_err", "decode_rebase", "short_conv", "lambda_scan_grads", "prep_ref", "rounding",
 ]
 
 
@@ -206,6 +206,25 @@ def lambda_scan(u, logmag, ang, h0=None, chunk: int = 16):
     return torch.cat(pieces, 1).to(out_dtype), (hr.to(out_dtype), hi.to(out_dtype))
 
 
+def lambda_scan_grads(u, logmag, ang, h0, w_y, w_r, w_i):
+    """Gradients of  (Re h * w_y).sum() + (Re h_T * w_r).sum() + (Im h_T * w_i).sum()  with respect to u, logmag, ang and
+    the entering state, by autograd through the literal recurrence in fp64 (the check of tests/test_spin.py:237-246)."""
+    with torch.enable_grad():
+        a = [t.detach().double().requires_grad_(True) for t in (u, logmag, ang, h0[0], h0[1])]
+        y, (hr, hi) = lambda_literal(a[0], a[1], a[2], (a[3], a[4]))
+        loss = (y * w_y.double()).sum() + (hr * w_r.double()).sum() + (hi * w_i.double()).sum()
+        return torch.autograd.grad(loss, a)
+
+
+def prep_ref(qp, kp, vp, gl, theta, pos):
+    """The plumbing before the scan in plain torch (tests/test_assoc.py:189-193): normalise q, k, v per head, scale k by
+    the write gate, rotate q and k; (B,T,H,D) in, fp32 (B,H,T,D) out. Differentiable by autograd."""
+    q_, k_, v_ = [F.normalize(t.transpose(1, 2).float(), dim=-1) for t in (qp, kp, vp)]
+    if gl is not None:
+        k_ = k_ * torch.sigmoid(gl.float()).transpose(1, 2).unsqueeze(-1)
+    return rotate(q_, theta, pos), rotate(k_, theta, pos), v_
+
+
 # ----------------------------------------------------------------------------------------------------------
 # one recurrent decode step on already prepared vectors
 # ----------------------------------------------------------------------------------------------------------
@@ -232,44 +251,101 @@ def decode_step(S, shift, q, k, v, la, theta, beta=None):
 # ----------------------------------------------------------------------------------------------------------
 # layers and the language model (functional, reference state_dict names)
 # ----------------------------------------------------------------------------------------------------------
+# Where a bf16 run of the model rounds. The reference under autocast, and the product with bf16 weights, keep activations in
+# bf16: every linear layer, norm, activation and residual add hands on a value rounded to 8 bits of mantissa, while the
+# scan's state and accumulations stay fp32. With `rounding(torch.bfloat16)` active the functions below round at exactly
+# those hand-overs (and nowhere else), so a bf16 product run can be held to a tolerance that reflects its kernels rather
+# than the accumulated rounding of twelve layers. Off by default: the oracle is then the plain fp32 / fp64 arithmetic.
+_ROUND = [None]
+
+
+class rounding:
+    def __init__(self, dtype):
+        self.dtype = dtype
+
+    def __enter__(self):
+        self.prev, _ROUND[0] = _ROUND[0], self.dtype
+
+    def __exit__(self, *a):
+        _ROUND[0] = self.prev
+
+
+def _r(x):
+    return x if _ROUND[0] is None else x.to(_ROUND[0]).to(x.dtype)
+
+
 def _norm(P, name, x, kind):
     w = P[name + ".weight"]
     if kind == "rms":
         eps = torch.finfo(x.dtype).eps                                  # nn.RMSNorm(eps=None)
-        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w
-    return F.layer_norm(x, (x.shape[-1],), w, P[name + ".bias"], 1e-5)
+        return _r(x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w)
+    return _r(F.layer_norm(x, (x.shape[-1],), w, P[name + ".bias"], 1e-5))
 
 
 def _lin(P, name, x):
-    return F.linear(x, P[name + ".weight"], P.get(name + ".bias"))
+    return _r(F.linear(x, P[name + ".weight"], P.get(name + ".bias")))
 
 
-def assoc_layer(P, pre, x, h0=None, *, heads: int, delta: bool = False, chunk: int = 64, norm: str = "ln"):
-    """AssocCarrier.forward on its PyTorch path (src/assoc.py:384-512 with kernel off, no short convolution, no
-    key_topk, no hl_floor, no write_all).  x (B,T,d); h0 = (S, p0) or None.  Returns (out, (S, T))."""
+def short_conv(P, pre, qo, ko, vo, cc):
+    """The depthwise causal convolution over the last K tokens on q, k, v (B,T,d each) with the previous call's last K-1
+    inputs as left context (src/assoc.py:375-382 _sconv). Returns q, k, v and the new context (B,3d,K-1)."""
+    w = P[pre + "sconv"]
+    d, K = qo.shape[-1], w.shape[1]
+    x = torch.cat([qo, ko, vo], dim=-1).transpose(1, 2)                          # (B,3d,T)
+    pad = cc.to(x.dtype) if cc is not None else x.new_zeros(x.shape[0], 3 * d, K - 1)
+    xp = torch.cat([pad, x], dim=-1)
+    y = F.conv1d(xp, w.to(x.dtype).unsqueeze(1), groups=3 * d).transpose(1, 2)
+    return y[..., :d], y[..., d:2 * d], y[..., 2 * d:], xp[..., -(K - 1):]
+
+
+def assoc_layer(P, pre, x, h0=None, *, heads: int, delta: bool = False, chunk: int = 64, norm: str = "ln", key_topk: int = 0,
+                hl_floor: bool = False, write_all: bool = False, pos_wrap=None, beta_scale=None):
+    """AssocCarrier.forward on its PyTorch path (src/assoc.py:384-512 with kernel off).  x (B,T,d); h0 = (S, p0[, conv
+    cache]) or None.  Options as the reference's: key_topk (:435-439), hl_floor (:339-343, :357), write_all (:463, :472-478),
+    pos_wrap (:406-410), beta_scale (:468-471); a short convolution is on when P holds pre + "sconv" (:361-382).
+    Returns (out, (S, T[, conv cache]))."""
     B, T, d = x.shape
     dk = d // heads
     theta = P[pre + "theta"]
     z = _norm(P, pre + "ln", x, norm)
-    S0 = None
+    S0, cc = None, None
     if h0 is not None:
         S0, p0 = h0[0], h0[1]
+        cc = h0[2] if len(h0) == 3 else None
         if not (isinstance(p0, int) and p0 == 0):
             S0 = decode_rebase(S0, theta.float(), float(p0))
     pos = torch.arange(T)
+    if pos_wrap:
+        pos = pos % pos_wrap
+    qo, ko, vo = (_lin(P, pre + n, z) for n in ("q", "k", "v"))
+    sc = (pre + "sconv") in P
+    if sc:
+        qo, ko, vo, cc = short_conv(P, pre, qo, ko, vo, cc)
     split = lambda t: t.reshape(B, T, heads, dk).transpose(1, 2)
-    q, k, v = (F.normalize(split(_lin(P, pre + n, z)), dim=-1) for n in ("q", "k", "v"))
-    if not delta:
+    kp = ko.reshape(B, T, heads, dk)
+    if key_topk:
+        m = torch.zeros_like(kp).scatter_(-1, kp.abs().topk(key_topk, dim=-1).indices, 1.0)
+        kp = kp * m
+    q, k, v = (F.normalize(t, dim=-1) for t in (split(qo), kp.transpose(1, 2), split(vo)))
+    if not delta and not write_all:
         k = k * torch.sigmoid(_lin(P, pre + "wi", z)).transpose(1, 2).unsqueeze(-1)
-    q, k = rotate(q, theta, pos), rotate(k, theta, pos)
-    la = (-F.softplus(_lin(P, pre + "wa", z)) * P[pre + "A"].exp()).transpose(1, 2)
+    q, k, v = _r(rotate(q, theta, pos)), _r(rotate(k, theta, pos)), _r(v)      # the scan's operands (bf16 in a bf16 run)
+    la = -F.softplus(_lin(P, pre + "wa", z)) * P[pre + "A"].exp()
+    if hl_floor:
+        hl = torch.logspace(math.log10(8.0), math.log10(131072.0), heads)
+        la = la.clamp(min=(-math.log(2.0) / hl).to(la.dtype))
+    la = la.transpose(1, 2)
     bt = torch.sigmoid(_lin(P, pre + "wb", z)).transpose(1, 2) if delta else None
+    if beta_scale is not None and bt is not None:
+        bt = bt * beta_scale.to(bt.dtype)
+    if delta and write_all:
+        bt = bt.clamp(min=0.75)
     o, S = assoc_scan(q, k, v, la, S0, chunk=chunk, beta=bt)
     eps = torch.finfo(o.dtype).eps
-    o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * P[pre + "on.weight"]
+    o = _r(o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * P[pre + "on.weight"])
     o = o.transpose(1, 2).reshape(B, T, d)
-    out = x + F.linear(o, P[pre + "o.weight"] * torch.sigmoid(P[pre + "gate"]))
-    return out, (S, T)
+    out = _r(x + _r(F.linear(o, _r(P[pre + "o.weight"] * torch.sigmoid(P[pre + "gate"])))))
+    return out, ((S, T, cc) if sc else (S, T))
 
 
 def decode_rebase(S0, theta, shift: float):
@@ -293,7 +369,7 @@ def fspin_layer(P, pre, x, h0=None, *, norm: str = "ln", chunk: int = 16):
 
 def mlp_block(P, pre, x, norm: str = "ln"):
     """norm -> Linear(4d) -> GELU (erf) -> Linear(d), residual (src/model.py:552-560)."""
-    return x + _lin(P, pre + "b", F.gelu(_lin(P, pre + "a", _norm(P, pre + "n", x, norm))))
+    return _r(x + _lin(P, pre + "b", _r(F.gelu(_lin(P, pre + "a", _norm(P, pre + "n", x, norm))))))
 
 
 _MIXERS = {  # mixer name -> (family, delta, head_dim)   (src/model.py:631-699, the pure-carrier entries)
@@ -397,9 +473,9 @@ def lm_prefill(P, cfg, x, window: Optional[int] = None, states: Optional[list] =
     logits = None
     for s in range(0, x.shape[1], window):
         xw = x[:, s:s + window]
-        h = F.embedding(xw, P["e.weight"]) + P["p.weight"][: xw.shape[1]]
+        h = _r(F.embedding(xw, P["e.weight"]) + P["p.weight"][: xw.shape[1]])
         h = lm_layers(P, cfg, h, states)
-        logits = F.linear(_norm(P, "n", h, cfg["norm"]), P["e.weight"])
+        logits = _r(F.linear(_norm(P, "n", h, cfg["norm"]), P["e.weight"]))
     return logits, states
 
 
@@ -411,6 +487,6 @@ def lm_forward_carried(P, cfg, x, window: Optional[int] = None):
 def lm_decode_step(P, cfg, tok, pos: int, states: list):
     """One eager decode step for a batch of sequences (src/bench.py:231-238 made batch-generic): tok (B,) ids at
     window position `pos`; returns logits (B,V); states are updated in the list."""
-    h = F.embedding(tok.reshape(-1, 1), P["e.weight"]) + P["p.weight"][pos]
+    h = _r(F.embedding(tok.reshape(-1, 1), P["e.weight"]) + P["p.weight"][pos])
     h = lm_layers(P, cfg, h, states)
-    return F.linear(_norm(P, "n", h, cfg["norm"]), P["e.weight"])[:, -1]
+    return _r(F.linear(_norm(P, "n", h, cfg["norm"]), P["e.weight"]))[:, -1]

@@ -35,12 +35,26 @@ SIGNATURES = {
     "pgb_add_norm": [_vp, _vp, _vp, _vp, _f, _i, _vp, _vp, _ll, _i, _i, _vp],
     "pgb_decode_embed": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "pgb_decode_sample": [_vp, _i, _f, C.c_ulonglong, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "pgb_decode_sample_ex": [_vp, _i, _f, _f, C.c_ulonglong, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "pgb_tc_wait_selftest": [_ll, _vp],
     "pgb_linear_act": [_vp, _vp, _vp, _vp, _ll, _i, _i, _i, _vp],
     "pgb_skinny_linear": [_vp, _vp, _vp, _vp, _i, _f, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _vp],
     "pgb_tc_error_flag": [_vp],
     "pgb_tc_set_variant": [_i],
     "pgb_rotate_pairs": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "pgb_skinny_linear_ex": [_vp, _vp, _vp, _vp, _i, _f, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp],
+    "pgb_lambda_scan_time_segments": [_i, _i, _i, _i],
+    "pgb_lambda_scan_fwd_train": [_vp, _vp, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "pgb_lambda_scan_bwd": [_vp, _vp, _vp, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+    "pgb_aspin_prep_bwd": [_vp, _vp, _vp, _i, _ll, _ll, _ll, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp,
+                           _i, _i, _i, _i, _vp],
+    "pgb_aspin_prep_bwd_tiles": [_i],
+    "pgb_assoc_out_fwd": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "pgb_prefix_scan_fwd": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "pgb_delta_inv_fwd": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "pgb_delta_loop_fwd": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "pgb_key_topk_mask": [_vp, _i, _ll, _ll, _ll, _i, _i, _i, _i, _i, _vp],
+    "pgb_short_conv_fwd": [_vp, _i, _ll, _ll, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "pgb_aspin_decode_step": [_vp, _vp, _vp, _i, _ll, _i, _vp, _ll, _i, _i, _vp, _ll, _vp, _vp, _vp, _f, _vp, _vp, _vp,
                               _f, _vp, _i, _ll, _i, _i, _i, _vp],
 }
@@ -88,6 +102,26 @@ def ptr(t) -> int | None:
 
 def stream_of(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def on_device_of(fn):
+    """Decorator for the tensor-level wrappers: the library reads CUDA's CURRENT device (SM count, kernel attributes, its
+    per-device scratch array and error flags), so a call whose first tensor lives on another GPU runs with that GPU made
+    current for its duration. Same device (the usual case): no context switch, no cost."""
+    import functools
+
+    @functools.wraps(fn)
+    def run(*args, **kw):
+        if torch.compiler.is_compiling():
+            return fn(*args, **kw)
+        for a in args:
+            if torch.is_tensor(a):
+                if a.is_cuda and a.device.index != torch.cuda.current_device():
+                    with torch.cuda.device(a.device):
+                        return fn(*args, **kw)
+                break
+        return fn(*args, **kw)
+    return run
 
 
 def need_cuda(*ts) -> None:

@@ -14,7 +14,22 @@ void set_cuda_error(cudaError_t e, const char *where) {
 
 
 int lambda_scan_launch(const float *, const float *, const float *, long long, long long, const float *, const float *,
-                       float *, float *, float *, int, int, int, int, cudaStream_t);
+                       float *, float *, float *, float *, int, int, int, int, cudaStream_t);
+int lambda_scan_bwd_launch(const float *, const float *, const float *, const float *, long long, long long, const float *, const float *,
+                           const float *, float *, float *, float *, float *, float *, int, int, int, cudaStream_t);
+int prep_bwd_launch(const void *, const void *, const void *, int, long long, long long, long long, const void *, long long, long long,
+                    const float *, const long long *, const void *, const void *, const void *, int, void *, void *, void *, float *,
+                    float *, int, int, int, int, cudaStream_t);
+int prep_bwd_tiles(int T);
+int assoc_out_launch(const void *, const void *, const void *, int, const float *, const void *, void *, int, int, int, cudaStream_t);
+int prefix_scan_launch(const void *, const void *, int, const float *, const float *, const float *, void *, float *, int, int, int,
+                       cudaStream_t);
+int delta_loop_launch(const void *, const void *, int, const float *, const float *, const void *, const float *, void *, void *, float *,
+                      int, int, int, cudaStream_t);
+int delta_inv_launch(const void *, const float *, const float *, void *, int, int, int, cudaStream_t);
+int key_topk_launch(void *, int, long long, long long, long long, int, int, int, int, int, cudaStream_t);
+int short_conv_launch(const void *, int, long long, long long, const void *, const void *, void *, void *, int, int, int, int, cudaStream_t);
+int lambda_scan_pick_ts(int B, int T, int D, int vec, int sms, int force_ts);
 int prep_launch(const void *, const void *, const void *, int, long long, long long, long long, const void *, long long,
                 long long, const float *, const long long *, void *, void *, void *, int, int, int, int, int, cudaStream_t);
 int prefill_fp32_launch(const PrefillArgs &, int, int, int, cudaStream_t);
@@ -32,12 +47,12 @@ int prefill_tc_delta_static_launch(const PrefillArgs &, int, int, cudaStream_t);
 long long prefill_tc_delta_static_capacity();
 int rot_table_launch(const float *, float *, int, int, int, cudaStream_t);
 int decode_embed_launch(const long long *, const long long *, const void *, const void *, void *, int, int, int, int, cudaStream_t);
-int decode_sample_launch(const void *, int, float, unsigned long long, long long *, long long *, int, long long *, long long *, float *,
+int decode_sample_launch(const void *, int, float, float, unsigned long long, long long *, long long *, int, long long *, long long *, float *,
                          unsigned int *, int, int, int, cudaStream_t);
 int linear_gelu_launch(const void *, const void *, const void *, void *, long long, int, int, int, cudaStream_t);
 int linear_gelu_error_flag(int *);
 int skinny_linear_launch(const void *, const void *, const void *, const void *, int, float, const void *, const void *, int, void *,
-                         void *, int, int, int, cudaStream_t);
+                         void *, int, int, int, int, cudaStream_t);
 int add_norm_launch(const void *, const void *, const void *, const void *, float, int, void *, void *, long long, int, int,
                     cudaStream_t);
 int rotate_launch(const void *, int, const float *, const float *, void *, int, int, int, int, cudaStream_t);
@@ -82,17 +97,114 @@ const char *pgb_last_cuda_error(void) { return g_err; }
 
 int pgb_abi_version(void) { return 1; }
 
-int pgb_lambda_scan_fwd_ex(const float *u, const float *logmag, const float *ang, long long ang_stride_b,
-                           long long ang_stride_t, const float *h0r, const float *h0i, float *y, float *hr_out,
-                           float *hi_out, int B, int T, int D, int time_segments, void *stream) {
+static int lambda_scan_checked(const float *u, const float *logmag, const float *ang, long long ang_stride_b,
+                               long long ang_stride_t, const float *h0r, const float *h0i, float *y, float *hr_out,
+                               float *hi_out, float *hi_all, int B, int T, int D, int time_segments, void *stream) {
     if (!u || !logmag || !ang || !y || !hr_out || !hi_out) return PGB_ERR_NULL_POINTER;
     if ((h0r == nullptr) != (h0i == nullptr)) return PGB_ERR_NULL_POINTER;
     if (B <= 0 || T <= 0 || D <= 0 || ang_stride_b < 0 || ang_stride_t < 0) return PGB_ERR_BAD_SHAPE;
     if (time_segments != 0 && (time_segments < 1 || time_segments > 32 || (time_segments & (time_segments - 1))))
         return PGB_ERR_BAD_SHAPE;
     if (!aligned(u, 4) || !aligned(logmag, 4) || !aligned(ang, 4) || !aligned(y, 4)) return PGB_ERR_MISALIGNED;
-    return lambda_scan_launch(u, logmag, ang, ang_stride_b, ang_stride_t, h0r, h0i, y, hr_out, hi_out, B, T, D,
+    return lambda_scan_launch(u, logmag, ang, ang_stride_b, ang_stride_t, h0r, h0i, y, hr_out, hi_out, hi_all, B, T, D,
                               time_segments, (cudaStream_t)stream);
+}
+
+int pgb_lambda_scan_fwd_ex(const float *u, const float *logmag, const float *ang, long long ang_stride_b,
+                           long long ang_stride_t, const float *h0r, const float *h0i, float *y, float *hr_out,
+                           float *hi_out, int B, int T, int D, int time_segments, void *stream) {
+    return lambda_scan_checked(u, logmag, ang, ang_stride_b, ang_stride_t, h0r, h0i, y, hr_out, hi_out, nullptr, B, T, D,
+                               time_segments, stream);
+}
+
+int pgb_lambda_scan_fwd_train(const float *u, const float *logmag, const float *ang, long long ang_stride_b,
+                              long long ang_stride_t, const float *h0r, const float *h0i, float *y, float *hi_all, float *hr_out,
+                              float *hi_out, int B, int T, int D, void *stream) {
+    if (!hi_all) return PGB_ERR_NULL_POINTER;
+    return lambda_scan_checked(u, logmag, ang, ang_stride_b, ang_stride_t, h0r, h0i, y, hr_out, hi_out, hi_all, B, T, D, 0, stream);
+}
+
+int pgb_lambda_scan_bwd(const float *g, const float *u, const float *logmag, const float *ang, long long ang_stride_b,
+                        long long ang_stride_t, const float *hr_all, const float *hi_all, const float *g_last_i, float *du,
+                        float *dlogmag, float *dang, float *dh0r, float *dh0i, int B, int T, int D, void *stream) {
+    if (!g || !u || !logmag || !ang || !hr_all || !hi_all || !du || !dlogmag || !dang) return PGB_ERR_NULL_POINTER;
+    if ((dh0r == nullptr) != (dh0i == nullptr)) return PGB_ERR_NULL_POINTER;
+    if (B <= 0 || T <= 0 || D <= 0 || ang_stride_b < 0 || ang_stride_t < 0) return PGB_ERR_BAD_SHAPE;
+    return lambda_scan_bwd_launch(g, u, logmag, ang, ang_stride_b, ang_stride_t, hr_all, hi_all, g_last_i, du, dlogmag, dang, dh0r,
+                                  dh0i, B, T, D, (cudaStream_t)stream);
+}
+
+int pgb_lambda_scan_time_segments(int B, int T, int D, int sm_count) {
+    if (B <= 0 || T <= 0 || D <= 0 || sm_count <= 0) return 0;
+    return lambda_scan_pick_ts(B, T, D, (D % 4 == 0) ? 4 : 1, sm_count, 0);
+}
+
+int pgb_aspin_prep_bwd_tiles(int T) { return T > 0 ? prep_bwd_tiles(T) : 0; }
+
+int pgb_aspin_prep_bwd(const void *qp, const void *kp, const void *vp, int in_dtype, long long in_stride_b, long long in_stride_t,
+                       long long in_stride_h, const void *gate, long long gate_stride_b, long long gate_stride_t, const float *theta,
+                       const long long *pos, const void *dq, const void *dk, const void *dv, int grad_dtype, void *dqp, void *dkp,
+                       void *dvp, float *dgate, float *dtheta_partial, int B, int T, int H, int D, void *stream) {
+    if (!qp || !kp || !vp || !theta || !pos || !dq || !dk || !dv || !dqp || !dkp || !dvp || !dtheta_partial) return PGB_ERR_NULL_POINTER;
+    if (gate && !dgate) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(in_dtype) || !dtype_ok(grad_dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || T <= 0 || H <= 0 || (long long)B * H > 65535) return PGB_ERR_BAD_SHAPE;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    return prep_bwd_launch(qp, kp, vp, in_dtype, in_stride_b, in_stride_t, in_stride_h, gate, gate_stride_b, gate_stride_t, theta, pos,
+                           dq, dk, dv, grad_dtype, dqp, dkp, dvp, dgate, dtheta_partial, B, T, H, D, (cudaStream_t)stream);
+}
+
+int pgb_assoc_out_fwd(const void *q, const void *k, const void *v, int io_dtype, const float *la, const void *sent, void *o, int B,
+                      int H, int T, int D, void *stream) {
+    if (!q || !k || !v || !la || !sent || !o) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(io_dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || H <= 0 || T <= 0 || (long long)B * H > 65535) return PGB_ERR_BAD_SHAPE;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    return assoc_out_launch(q, k, v, io_dtype, la, sent, o, B * H, T, D, (cudaStream_t)stream);
+}
+
+int pgb_prefix_scan_fwd(const void *k, const void *v, int io_dtype, const float *w, const float *a_log, const float *S0, void *sent,
+                        float *sfin, int B, int H, int NC, int D, void *stream) {
+    if (!k || !v || !w || !a_log || !sent || !sfin) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(io_dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || H <= 0 || NC <= 0 || (long long)B * H > 65535) return PGB_ERR_BAD_SHAPE;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    return prefix_scan_launch(k, v, io_dtype, w, a_log, S0, sent, sfin, B * H, NC, D, (cudaStream_t)stream);
+}
+
+int pgb_delta_inv_fwd(const void *k, const float *la, const float *beta, void *X, int B, int H, int T, int D, void *stream) {
+    if (!k || !la || !beta || !X) return PGB_ERR_NULL_POINTER;
+    if (B <= 0 || H <= 0 || T <= 0) return PGB_ERR_BAD_SHAPE;
+    if ((long long)B * H > 65535 || (T + 63) / 64 > 65535) return PGB_ERR_TOO_LARGE;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    if (!aligned(k, 16) || !aligned(X, 16)) return PGB_ERR_MISALIGNED;
+    return delta_inv_launch(k, la, beta, X, B * H, T, D, (cudaStream_t)stream);
+}
+
+int pgb_delta_loop_fwd(const void *k, const void *v, int io_dtype, const float *la, const float *beta, const void *X, const float *S0,
+                       void *W, void *sent, float *sfin, int B, int H, int T, int D, void *stream) {
+    if (!k || !v || !la || !beta || !X || !W || !sent || !sfin) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(io_dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || H <= 0 || T <= 0 || (long long)B * H > 65535) return PGB_ERR_BAD_SHAPE;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    return delta_loop_launch(k, v, io_dtype, la, beta, X, S0, W, sent, sfin, B * H, T, D, (cudaStream_t)stream);
+}
+
+int pgb_key_topk_mask(void *kp, int dtype, long long stride_b, long long stride_t, long long stride_h, int B, int T, int H, int D,
+                      int topk, void *stream) {
+    if (!kp) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || T <= 0 || H <= 0 || topk < 1 || topk > D) return PGB_ERR_BAD_SHAPE;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    return key_topk_launch(kp, dtype, stride_b, stride_t, stride_h, B, T, H, D, topk, (cudaStream_t)stream);
+}
+
+int pgb_short_conv_fwd(const void *x, int dtype, long long stride_b, long long stride_t, const void *w, const void *cache_in, void *y,
+                       void *cache_out, int B, int T, int C, int K, void *stream) {
+    if (!x || !w || !y || !cache_out) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || T <= 0 || C <= 0 || K < 2 || K > 64 || cache_in == cache_out) return PGB_ERR_BAD_SHAPE;
+    return short_conv_launch(x, dtype, stride_b, stride_t, w, cache_in, y, cache_out, B, T, C, K, (cudaStream_t)stream);
 }
 
 int pgb_lambda_scan_fwd(const float *u, const float *logmag, const float *ang, long long ang_stride_b,
@@ -214,12 +326,18 @@ int pgb_decode_embed(const long long *tok, const long long *pos, const void *E, 
 int pgb_decode_sample(const void *logits, int dtype, float temp, unsigned long long seed, long long *tok, long long *hist,
                       int hist_cols, long long *count, long long *pos, float *shift, unsigned int *ticket, int B, int V, int ctx,
                       void *stream) {
+    return pgb_decode_sample_ex(logits, dtype, temp, 0.f, seed, tok, hist, hist_cols, count, pos, shift, ticket, B, V, ctx, stream);
+}
+
+int pgb_decode_sample_ex(const void *logits, int dtype, float temp, float min_p, unsigned long long seed, long long *tok,
+                         long long *hist, int hist_cols, long long *count, long long *pos, float *shift, unsigned int *ticket,
+                         int B, int V, int ctx, void *stream) {
     if (!logits || !tok || !count || !ticket) return PGB_ERR_NULL_POINTER;
     if (dtype != PGB_F32 && dtype != PGB_BF16) return PGB_ERR_BAD_DTYPE;
-    if (B < 1 || V < 1 || ctx < 1 || hist_cols < 0 || !(temp >= 0.f)) return PGB_ERR_BAD_SHAPE;
+    if (B < 1 || V < 1 || ctx < 1 || hist_cols < 0 || !(temp >= 0.f) || !(min_p >= 0.f && min_p <= 1.f)) return PGB_ERR_BAD_SHAPE;
     if (!aligned(tok, 8) || !aligned(count, 8) || (hist && !aligned(hist, 8)) || (pos && !aligned(pos, 8)) || !aligned(ticket, 4))
         return PGB_ERR_MISALIGNED;
-    return decode_sample_launch(logits, dtype, temp, seed, tok, hist, hist_cols, count, pos, shift, ticket, B, V, ctx,
+    return decode_sample_launch(logits, dtype, temp, min_p, seed, tok, hist, hist_cols, count, pos, shift, ticket, B, V, ctx,
                                 (cudaStream_t)stream);
 }
 
@@ -231,8 +349,8 @@ int pgb_linear_act(const void *x, const void *W, const void *bias, void *y, long
     return linear_gelu_launch(x, W, bias, y, M, N, K, act, (cudaStream_t)stream);
 }
 
-int pgb_skinny_linear(const void *x, const void *delta, const void *norm_weight, const void *norm_bias, int norm_kind, float eps,
-                      const void *W, const void *bias, int act, void *y, void *x_out, int B, int K, int N, void *stream) {
+int pgb_skinny_linear_ex(const void *x, const void *delta, const void *norm_weight, const void *norm_bias, int norm_kind, float eps,
+                         const void *W, const void *bias, int act, void *y, void *x_out, int B, int K, int N, int flags, void *stream) {
     if (!x || !W || !y) return PGB_ERR_NULL_POINTER;
     if (norm_kind < 0 || norm_kind > 2 || act < 0 || act > 1) return PGB_ERR_BAD_SHAPE;
     if ((norm_kind != 0 && !norm_weight) || (norm_kind == 2 && !norm_bias)) return PGB_ERR_NULL_POINTER;
@@ -241,7 +359,14 @@ int pgb_skinny_linear(const void *x, const void *delta, const void *norm_weight,
     if (!aligned(x, 16) || !aligned(W, 16) || (delta && !aligned(delta, 16)) || (x_out && !aligned(x_out, 16)) ||
         (norm_weight && !aligned(norm_weight, 16)) || (norm_bias && !aligned(norm_bias, 16)))
         return PGB_ERR_MISALIGNED;
-    return skinny_linear_launch(x, delta, norm_weight, norm_bias, norm_kind, eps, W, bias, act, y, x_out, B, K, N, (cudaStream_t)stream);
+    if (flags & ~PGB_SKINNY_FRESH_CONSTANTS) return PGB_ERR_BAD_SHAPE;
+    return skinny_linear_launch(x, delta, norm_weight, norm_bias, norm_kind, eps, W, bias, act, y, x_out, B, K, N,
+                                (flags & PGB_SKINNY_FRESH_CONSTANTS) ? 1 : 0, (cudaStream_t)stream);
+}
+
+int pgb_skinny_linear(const void *x, const void *delta, const void *norm_weight, const void *norm_bias, int norm_kind, float eps,
+                      const void *W, const void *bias, int act, void *y, void *x_out, int B, int K, int N, void *stream) {
+    return pgb_skinny_linear_ex(x, delta, norm_weight, norm_bias, norm_kind, eps, W, bias, act, y, x_out, B, K, N, 0, stream);
 }
 
 int pgb_add_norm(const void *x, const void *delta, const void *weight, const void *bias, float eps, int kind, void *y, void *z,

@@ -3,7 +3,8 @@
 // src/bench.py:79-86, 193-239, which syncs with the host for every token).
 //
 //   embed:   x[b][:] = E[tok[b]][:] + P[pos][:]                               (src/model.py:859: token + wrapped position)
-//   sample:  tok[b] ~ softmax(logits[b] / temp)   (temp = 0: argmax), recorded in hist[b][count]. The position and the
+//   sample:  tok[b] ~ softmax(logits[b] / temp)   (temp = 0: argmax), recorded in hist[b][count]; with min_p > 0 the ids
+//            whose probability is below min_p times the largest are dropped first (src/bench.py:79-86). The position and the
 //            rebase shift belong to the token being fed to the model, so from the second draw on (count > 0) the kernel
 //            first advances them for the previous token: pos = (pos + 1) mod ctx, shift = 1; the CTA that finishes last
 //            then does count += 1.
@@ -50,7 +51,7 @@ __device__ __forceinline__ unsigned long long mix64(unsigned long long z) {     
 constexpr int SAMPLE_NT = 256;
 
 template <typename T_>
-__global__ void __launch_bounds__(SAMPLE_NT) decode_sample_kernel(const T_ *__restrict__ logits, float temp, unsigned long long seed,
+__global__ void __launch_bounds__(SAMPLE_NT) decode_sample_kernel(const T_ *__restrict__ logits, float temp, float min_p, unsigned long long seed,
                                                                   long long *__restrict__ tok, long long *__restrict__ hist, int hist_cols,
                                                                   long long *__restrict__ count, long long *__restrict__ pos,
                                                                   float *__restrict__ shift, unsigned int *__restrict__ ticket,
@@ -68,12 +69,31 @@ __global__ void __launch_bounds__(SAMPLE_NT) decode_sample_kernel(const T_ *__re
     const T_ *row = logits + (size_t)b * V;
     const float inv_t = temp > 0.f ? 1.0f / temp : 1.0f;
     const unsigned long long key = mix64(seed ^ mix64((unsigned long long)step * 0x100000001b3ull + (unsigned long long)b));
+    // min-p: p_v >= min_p * p_max  <=>  logit_v / temp >= max_w logit_w / temp + log(min_p); one extra pass for the maximum
+    float floor_s = -INFINITY;
+    if (temp > 0.f && min_p > 0.f) {
+        __shared__ float smax[SAMPLE_NT / 32];
+        float m = -INFINITY;
+        for (int v = tid; v < V; v += SAMPLE_NT) {
+            float s;
+            if constexpr (sizeof(T_) == 2) s = __bfloat162float(row[v]); else s = row[v];
+            m = fmaxf(m, s * inv_t);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) smax[warp] = m;
+        __syncthreads();
+        m = smax[0];
+        for (int w = 1; w < SAMPLE_NT / 32; ++w) m = fmaxf(m, smax[w]);
+        floor_s = m + logf(min_p);
+    }
     float best = -INFINITY;
     int arg = V;                                                      // ties go to the smallest index
     for (int v = tid; v < V; v += SAMPLE_NT) {
         float s;
         if constexpr (sizeof(T_) == 2) s = __bfloat162float(row[v]); else s = row[v];
         s *= inv_t;
+        if (s < floor_s) continue;                                    // dropped by min-p
         if (temp > 0.f) {
             const unsigned long long r = mix64(key + (unsigned long long)v);
             const float u = ((float)(r >> 40) + 0.5f) * (1.0f / 16777216.0f);          // (0, 1), 24 bits
@@ -111,15 +131,15 @@ int decode_embed_launch(const long long *tok, const long long *pos, const void *
     return check_launch("decode_embed_kernel");
 }
 
-int decode_sample_launch(const void *logits, int dtype, float temp, unsigned long long seed, long long *tok, long long *hist,
+int decode_sample_launch(const void *logits, int dtype, float temp, float min_p, unsigned long long seed, long long *tok, long long *hist,
                          int hist_cols, long long *count, long long *pos, float *shift, unsigned int *ticket, int B, int V, int ctx,
                          cudaStream_t stream) {
     cudaError_t e;
     if (dtype == PGB_BF16)
         e = pdl_launch(decode_sample_kernel<__nv_bfloat16>, dim3((unsigned)B), dim3(SAMPLE_NT), 0, stream, (const __nv_bfloat16 *)logits,
-                       temp, seed, tok, hist, hist_cols, count, pos, shift, ticket, V, ctx);
+                       temp, min_p, seed, tok, hist, hist_cols, count, pos, shift, ticket, V, ctx);
     else
-        e = pdl_launch(decode_sample_kernel<float>, dim3((unsigned)B), dim3(SAMPLE_NT), 0, stream, (const float *)logits, temp, seed,
+        e = pdl_launch(decode_sample_kernel<float>, dim3((unsigned)B), dim3(SAMPLE_NT), 0, stream, (const float *)logits, temp, min_p, seed,
                        tok, hist, hist_cols, count, pos, shift, ticket, V, ctx);
     if (e != cudaSuccess) { set_cuda_error(e, "decode_sample launch"); return PGB_ERR_CUDA; }
     return check_launch("decode_sample_kernel");

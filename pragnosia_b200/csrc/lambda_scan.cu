@@ -46,7 +46,8 @@ template <int VEC, int TS, bool ANG_BCAST, int SEG>
 __global__ void __launch_bounds__(LS_WARPS * 32, TS == 32 ? LS_CTAS_PER_SM - 1 : LS_CTAS_PER_SM)   // 32 segments are chosen when warps are scarce: registers over occupancy
 lambda_scan_kernel(const float *__restrict__ u, const float *__restrict__ lm, const float *__restrict__ an,
                    long long an_sb, long long an_st, const float *__restrict__ h0r, const float *__restrict__ h0i,
-                   float *__restrict__ y, float *__restrict__ hr_out, float *__restrict__ hi_out, int B, int T, int D) {
+                   float *__restrict__ y, float *__restrict__ hr_out, float *__restrict__ hi_out, float *__restrict__ hi_all,
+                   int B, int T, int D) {
     constexpr int CQ = 32 / TS;
     constexpr unsigned FULL = 0xffffffffu;
     const int lane = threadIdx.x & 31;
@@ -170,7 +171,10 @@ lambda_scan_kernel(const float *__restrict__ u, const float *__restrict__ lm, co
                 const float ni = s[i][v] * hsr[v] + c[i][v] * hsi[v];
                 hsr[v] = nr; hsi[v] = ni; out[v] = nr;
             }
-            if (live && t < T) st_vec<VEC>(y + (row0 + t) * D + d0, out);
+            if (live && t < T) {
+                st_vec<VEC>(y + (row0 + t) * D + d0, out);
+                if (hi_all != nullptr) st_vec<VEC>(hi_all + (row0 + t) * D + d0, hsi);   // Im h, kept only for a backward pass
+            }
         }
         // state leaving the tile: the last segment's final state
 #pragma unroll
@@ -202,29 +206,29 @@ DevInfo dev_info() {
 
 template <int VEC, int TS, int SEG>
 int launch_ts(const float *u, const float *lm, const float *an, long long sb, long long st, const float *h0r,
-              const float *h0i, float *y, float *hro, float *hio, int B, int T, int D, cudaStream_t stream) {
+              const float *h0i, float *y, float *hro, float *hio, float *hia, int B, int T, int D, cudaStream_t stream) {
     constexpr int CQ = 32 / TS;
     const int ngroups = (D + VEC - 1) / VEC;
     const long long warps = (long long)B * ((ngroups + CQ - 1) / CQ);
     const long long ctas = (warps + LS_WARPS - 1) / LS_WARPS;
     if (ctas > 0x7fffffffLL) return PGB_ERR_TOO_LARGE;
     if (sb == 0 && st == 0)
-        lambda_scan_kernel<VEC, TS, true, SEG><<<(unsigned)ctas, LS_WARPS * 32, 0, stream>>>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D);
+        lambda_scan_kernel<VEC, TS, true, SEG><<<(unsigned)ctas, LS_WARPS * 32, 0, stream>>>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, hia, B, T, D);
     else
-        lambda_scan_kernel<VEC, TS, false, SEG><<<(unsigned)ctas, LS_WARPS * 32, 0, stream>>>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D);
+        lambda_scan_kernel<VEC, TS, false, SEG><<<(unsigned)ctas, LS_WARPS * 32, 0, stream>>>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, hia, B, T, D);
     return check_launch("lambda_scan_kernel");
 }
 
 template <int VEC, int SEG>
 int launch_vec(int ts, const float *u, const float *lm, const float *an, long long sb, long long st, const float *h0r,
-               const float *h0i, float *y, float *hro, float *hio, int B, int T, int D, cudaStream_t stream) {
+               const float *h0i, float *y, float *hro, float *hio, float *hia, int B, int T, int D, cudaStream_t stream) {
     switch (ts) {
-        case 1:  return launch_ts<VEC, 1, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
-        case 2:  return launch_ts<VEC, 2, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
-        case 4:  return launch_ts<VEC, 4, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
-        case 8:  return launch_ts<VEC, 8, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
-        case 16: return launch_ts<VEC, 16, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
-        default: return launch_ts<VEC, 32, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
+        case 1:  return launch_ts<VEC, 1, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, hia, B, T, D, stream);
+        case 2:  return launch_ts<VEC, 2, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, hia, B, T, D, stream);
+        case 4:  return launch_ts<VEC, 4, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, hia, B, T, D, stream);
+        case 8:  return launch_ts<VEC, 8, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, hia, B, T, D, stream);
+        case 16: return launch_ts<VEC, 16, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, hia, B, T, D, stream);
+        default: return launch_ts<VEC, 32, SEG>(u, lm, an, sb, st, h0r, h0i, y, hro, hio, hia, B, T, D, stream);
     }
 }
 
@@ -256,16 +260,16 @@ int lambda_scan_pick_ts(int B, int T, int D, int vec, int sms, int force_ts) {
 }
 
 int lambda_scan_launch(const float *u, const float *lm, const float *an, long long sb, long long st, const float *h0r,
-                       const float *h0i, float *y, float *hro, float *hio, int B, int T, int D, int force_ts,
+                       const float *h0i, float *y, float *hro, float *hio, float *hia, int B, int T, int D, int force_ts,
                        cudaStream_t stream) {
     DevInfo di = dev_info();
     const int sms = di.ok ? di.sms : 148;
-    const bool v4 = (D % 4 == 0) && aligned(u, 16) && aligned(lm, 16) && aligned(an, 16) && aligned(y, 16) &&
+    const bool v4 = (D % 4 == 0) && aligned(u, 16) && aligned(lm, 16) && aligned(an, 16) && aligned(y, 16) && aligned(hia, 16) &&
                     aligned(hro, 16) && aligned(hio, 16) && (h0r == nullptr || (aligned(h0r, 16) && aligned(h0i, 16))) &&
                     (sb % 4 == 0) && (st % 4 == 0);
     const int ts = lambda_scan_pick_ts(B, T, D, v4 ? 4 : 1, sms, force_ts);
-    return v4 ? launch_vec<4, LS_SEG_VEC4>(ts, u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream)
-              : launch_vec<1, LS_SEG_VEC1>(ts, u, lm, an, sb, st, h0r, h0i, y, hro, hio, B, T, D, stream);
+    return v4 ? launch_vec<4, LS_SEG_VEC4>(ts, u, lm, an, sb, st, h0r, h0i, y, hro, hio, hia, B, T, D, stream)
+              : launch_vec<1, LS_SEG_VEC1>(ts, u, lm, an, sb, st, h0r, h0i, y, hro, hio, hia, B, T, D, stream);
 }
 
 }  // namespace pgb

@@ -60,7 +60,8 @@ struct InvSmem {
 
 template <int D>
 __global__ void __launch_bounds__(128) delta_inv_kernel(const __grid_constant__ CUtensorMap mk, const float *__restrict__ la_all,
-                                                        const float *__restrict__ beta_all, __nv_bfloat16 *__restrict__ X, int T) {
+                                                        const float *__restrict__ beta_all, __nv_bfloat16 *__restrict__ X, int T,
+                                                        int with_tail) {
     using SM = InvSmem<D>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -143,12 +144,13 @@ __global__ void __launch_bounds__(128) delta_inv_kernel(const __grid_constant__ 
         }
     }
     __syncthreads();
-    // ---- head then tail, 8 KB each, to the scratch buffer
+    // ---- head then tail, 8 KB each, to the scratch buffer; or the head alone, densely packed (the stand-alone operator)
     {
-        uint4 *dst = reinterpret_cast<uint4 *>(X + ((size_t)bh * NC + c) * (2 * TC_C * TC_C));
+        uint4 *dst = reinterpret_cast<uint4 *>(X + ((size_t)bh * NC + c) * ((with_tail ? 2 : 1) * TC_C * TC_C));
         const uint4 *src = reinterpret_cast<const uint4 *>(Xh);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) dst[tid + 128 * i] = src[tid + 128 * i];
+        for (int i = 0; i < 8; ++i)
+            if (with_tail || i < 4) dst[tid + 128 * i] = src[tid + 128 * i];
     }
 }
 
@@ -544,7 +546,7 @@ static int delta_go(const PrefillArgs &a, int o_dtype, void *x_scratch, cudaStre
     cudaError_t e = cudaFuncSetAttribute(inv, cudaFuncAttributeMaxDynamicSharedMemorySize, InvSmem<D>::bytes);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(walk, cudaFuncAttributeMaxDynamicSharedMemorySize, TdSmem<D>::bytes);
     if (e != cudaSuccess) { set_cuda_error(e, "prefill_tc_delta smem attribute"); return PGB_ERR_CUDA; }
-    inv<<<dim3(NC, BH), 128, InvSmem<D>::bytes, stream>>>(mk, a.la, a.beta, (__nv_bfloat16 *)x_scratch, a.T);
+    inv<<<dim3(NC, BH), 128, InvSmem<D>::bytes, stream>>>(mk, a.la, a.beta, (__nv_bfloat16 *)x_scratch, a.T, 1);
     int rc = check_launch("delta_inv_kernel");
     if (rc != PGB_OK) return rc;
     TdParams p{a.la, a.beta, a.S0, a.theta, a.shift_dev, a.shift_host, a.o, a.S_out, a.sent, a.H, a.T, o_dtype == PGB_F32};
@@ -562,6 +564,23 @@ int prefill_tc_delta_launch(const PrefillArgs &a, int o_dtype, int D, void *x_sc
 }
 
 int tc_delta_error_flag(int *out) { return tc_read_error_flag(out); }
+
+// The inverse alone, as the reference's stand-alone operator returns it (src/assoc_kernel.py:658-667 membrae::delta_inv):
+// X [B*H][NC][64][64] bf16, the rounded heads only.
+template <int D>
+static int delta_inv_go(const void *k, const float *la, const float *beta, void *X, int BH, int T, cudaStream_t stream) {
+    const int NC = (T + TC_C - 1) / TC_C;
+    CUtensorMap mk;
+    if (!tc_make_map(&mk, k, BH, T, D, D, (long long)T * D)) { set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled"); return PGB_ERR_CUDA; }
+    auto inv = delta_inv_kernel<D>;
+    cudaError_t e = cudaFuncSetAttribute(inv, cudaFuncAttributeMaxDynamicSharedMemorySize, InvSmem<D>::bytes);
+    if (e != cudaSuccess) { set_cuda_error(e, "delta_inv smem attribute"); return PGB_ERR_CUDA; }
+    inv<<<dim3(NC, BH), 128, InvSmem<D>::bytes, stream>>>(mk, la, beta, (__nv_bfloat16 *)X, T, 0);
+    return check_launch("delta_inv_kernel");
+}
+int delta_inv_launch(const void *k, const float *la, const float *beta, void *X, int BH, int T, int D, cudaStream_t stream) {
+    return D == 64 ? delta_inv_go<64>(k, la, beta, X, BH, T, stream) : delta_inv_go<128>(k, la, beta, X, BH, T, stream);
+}
 
 // ------------------------------------------------------------------------------------------------ built-in scratch
 // The same delta prefill for callers that have no way to hand over a scratch buffer. The chunk inverses then live in

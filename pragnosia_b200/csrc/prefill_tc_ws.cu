@@ -133,14 +133,15 @@ __global__ void __launch_bounds__(WS_NT, 1) prefill_tc_ws_kernel(const __grid_co
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == WS_ISSUER) tmem_alloc(smem_u32(tmem_slot), TM_COLS);
+    // Launched as a programmatic dependent: the set-up above (barriers, tensor memory) may overlap the tail of the kernel
+    // before this one on the stream. No global memory is read or written before this wait -- not even the small constant
+    // vectors, which that kernel may have produced (a dtype cast of the norm weight, say).
+    pdl_wait();
     if (p.rms_w != nullptr && tid < D) rmsw[tid] = p.rms_w[tid];
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    // Launched as a programmatic dependent: the set-up above may overlap the tail of the kernel that produces q, k, v;
-    // nothing it produced is read, and nothing is written, before this point.
-    pdl_wait();
     pdl_launch_dependents();
 
     if (warp < WS_FRONT) {

@@ -40,49 +40,59 @@ struct SkinnyArgs {
     __nv_bfloat16 *y, *x_out;
     float eps;
     int norm_kind, act, K, N, nb;                                      // nb: rows actually present (<= the instantiation's B)
+    int late_consts;                                                   // the norm vectors / bias may be the preceding kernel's output
 };
 
 // Launched with the programmatic-dependent-launch attribute: weights do not depend on the preceding kernel, so the first
 // pieces of this warp's rows of W are requested before pdl_wait(); activations are read and results written after it.
+// The norm vectors and the bias are requested early too. When the caller says (late_consts) that the kernel just before
+// this one on the stream may have produced any of them (a dtype cast, a rebuilt fused weight), all of these loads move
+// behind the wait: a predecessor's writes are visible only after it.
 constexpr int SK_PRE = 3;                                             // pieces of each row of W requested before the wait (K <= 768: all)
 constexpr int SK_ROWREG = 4;                                          // pieces of an activation row a lane keeps in registers (K <= 1024)
 
 template <int B>
 __global__ void __launch_bounds__(SK_WARPS * 32) skinny_linear_kernel(SkinnyArgs a) {
     extern __shared__ uint4 sk_smem[];
-    uint4 *zs = sk_smem;                                              // [B][K / 8] pieces of 8 bf16
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int K8 = a.K >> 3;
+    // [B][K / 8] pieces of 8 bf16. One row (B = 1): every warp builds the row for itself in a slice of its own, so no warp
+    // ever reads a piece another warp is still rewriting (raw sum first, normalised value second, for rows longer than
+    // the register buffer).
+    uint4 *zs = sk_smem + (B == 1 ? warp * K8 : 0);
     const int n0 = (blockIdx.x * SK_WARPS + warp) * SK_R;
     const bool rows_live = n0 < a.N;
     const uint4 *w0 = reinterpret_cast<const uint4 *>(a.W + (size_t)(rows_live ? n0 : 0) * a.K);
     const uint4 *w1 = reinterpret_cast<const uint4 *>(a.W + (size_t)(n0 + 1 < a.N ? n0 + 1 : (rows_live ? n0 : 0)) * a.K);
     uint4 pw0[SK_PRE], pw1[SK_PRE];
-#pragma unroll
-    for (int i = 0; i < SK_PRE; ++i) {
-        const int k8 = lane + 32 * i;
-        pw0[i] = pw1[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (k8 < K8) { pw0[i] = __ldg(w0 + k8); pw1[i] = __ldg(w1 + k8); }
-    }
     // the other constants this thread will need: its pieces of the norm vectors and the bias of the output it finishes
     uint4 pnw[SK_ROWREG], pnb[SK_ROWREG];
-#pragma unroll
-    for (int i = 0; i < SK_ROWREG; ++i) {
-        const int k8 = lane + 32 * i;
-        pnw[i] = pnb[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (a.norm_kind != 0 && k8 < K8) pnw[i] = __ldg(reinterpret_cast<const uint4 *>(a.norm_w) + k8);
-        if (a.norm_kind == 2 && k8 < K8) pnb[i] = __ldg(reinterpret_cast<const uint4 *>(a.norm_b) + k8);
-    }
     float my_bias = 0.f;
-    if (a.bias != nullptr && lane < SK_R * B && n0 + lane / B < a.N) my_bias = __bfloat162float(a.bias[n0 + lane / B]);
+    auto load_consts = [&]() {
+#pragma unroll
+        for (int i = 0; i < SK_PRE; ++i) {
+            const int k8 = lane + 32 * i;
+            pw0[i] = pw1[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (k8 < K8) { pw0[i] = w0[k8]; pw1[i] = w1[k8]; }
+        }
+#pragma unroll
+        for (int i = 0; i < SK_ROWREG; ++i) {
+            const int k8 = lane + 32 * i;
+            pnw[i] = pnb[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (a.norm_kind != 0 && k8 < K8) pnw[i] = reinterpret_cast<const uint4 *>(a.norm_w)[k8];
+            if (a.norm_kind == 2 && k8 < K8) pnb[i] = reinterpret_cast<const uint4 *>(a.norm_b)[k8];
+        }
+        if (a.bias != nullptr && lane < SK_R * B && n0 + lane / B < a.N) my_bias = __bfloat162float(a.bias[n0 + lane / B]);
+    };
+    if (!a.late_consts) load_consts();
     pdl_launch_dependents();
     pdl_wait();
+    if (a.late_consts) load_consts();
 
     // ---- z for every row of the batch (skipped when there is nothing to add or normalise: z is x, read in place)
     const bool direct = a.delta == nullptr && a.norm_kind == 0 && a.x_out == nullptr;
     if (!direct) {
-        // One row (B = 1): every warp builds the whole row for itself -- a lane later reads back exactly the pieces it wrote
-        // (the warps store identical values to the same places), so no warp waits for another. More rows: a warp per row.
+        // One row (B = 1): every warp builds the whole row for itself, in its own slice. More rows: a warp per row.
         for (int b = (B == 1 ? 0 : warp); b < a.nb; b += (B == 1 ? 1 : SK_WARPS)) {
             const uint4 *xr = reinterpret_cast<const uint4 *>(a.x + (size_t)b * a.K);
             const uint4 *dr = a.delta != nullptr ? reinterpret_cast<const uint4 *>(a.delta + (size_t)b * a.K) : nullptr;
@@ -167,7 +177,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32) skinny_linear_kernel(SkinnyArgs
                 for (int k8 = lane + 32 * SK_ROWREG; k8 < K8; k8 += 32) {
                     float t[8];
                     unpack8(zs[b * K8 + k8], t);
-                    norm_piece(t, k8, __ldg(wr + k8), br != nullptr ? __ldg(br + k8) : make_uint4(0u, 0u, 0u, 0u));
+                    norm_piece(t, k8, wr[k8], br != nullptr ? br[k8] : make_uint4(0u, 0u, 0u, 0u));
                 }
             }
         }
@@ -197,7 +207,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32) skinny_linear_kernel(SkinnyArgs
 #pragma unroll
     for (int i = 0; i < SK_PRE; ++i)
         if (lane + 32 * i < K8) piece(pw0[i], pw1[i], lane + 32 * i);
-    for (int k8 = lane + 32 * SK_PRE; k8 < K8; k8 += 32) piece(__ldg(w0 + k8), __ldg(w1 + k8), k8);
+    for (int k8 = lane + 32 * SK_PRE; k8 < K8; k8 += 32) piece(w0[k8], w1[k8], k8);
 #pragma unroll
     for (int r = 0; r < SK_R; ++r)
 #pragma unroll
@@ -225,12 +235,13 @@ static cudaError_t skinny_go(const SkinnyArgs &a, int ctas, size_t smem, cudaStr
 }
 
 int skinny_linear_launch(const void *x, const void *delta, const void *norm_w, const void *norm_b, int norm_kind, float eps,
-                         const void *W, const void *bias, int act, void *y, void *x_out, int B, int K, int N, cudaStream_t stream) {
+                         const void *W, const void *bias, int act, void *y, void *x_out, int B, int K, int N, int late_consts,
+                         cudaStream_t stream) {
     SkinnyArgs a{(const __nv_bfloat16 *)x, (const __nv_bfloat16 *)delta, (const __nv_bfloat16 *)norm_w, (const __nv_bfloat16 *)norm_b,
-                 (const __nv_bfloat16 *)W, (const __nv_bfloat16 *)bias, (__nv_bfloat16 *)y, (__nv_bfloat16 *)x_out, eps, norm_kind, act, K, N, B};
+                 (const __nv_bfloat16 *)W, (const __nv_bfloat16 *)bias, (__nv_bfloat16 *)y, (__nv_bfloat16 *)x_out, eps, norm_kind, act, K, N, B, late_consts};
     const int ctas = (N + SK_WARPS * SK_R - 1) / (SK_WARPS * SK_R);
     const int Bp = B <= 1 ? 1 : (B <= 2 ? 2 : (B <= 4 ? 4 : 8));          // kernel instantiation; its rows beyond B are computed
-    const size_t smem = (size_t)Bp * K * 2;                               // on whatever shared memory holds and never written
+    const size_t smem = (size_t)(Bp == 1 ? SK_WARPS : Bp) * K * 2;        // on whatever shared memory holds and never written
     cudaError_t e;
     switch (Bp) {
         case 1: e = skinny_go<1>(a, ctas, smem, stream); break;

@@ -17,8 +17,9 @@ from .assoc import AssocCarrier
 
 
 class Decoder:
-    def __init__(self, model, batch: int, use_graph: bool = True, fused: bool = True):
+    def __init__(self, model, batch: int, use_graph: bool = True, fused: bool = True, min_p: float = 0.0):
         self.m = model.eval()
+        self.min_p = float(min_p)                            # drop ids below min_p x the most likely one's probability (src/bench.py:38)
         self.B = batch
         self.use_graph = use_graph
         self.fused = fused                                   # small-batch bf16 step through the fused linear kernel
@@ -26,6 +27,7 @@ class Decoder:
         self.w = model.ctx
         self.states = None
         self._graph = None
+        self._stamp = None
         self.tok = torch.zeros(batch, 1, dtype=torch.long, device=self.dev)
         self.pos = torch.zeros(1, dtype=torch.long, device=self.dev)
         self.shift = torch.zeros((), dtype=torch.float32, device=self.dev)    # positions the states are rotated back by
@@ -36,6 +38,11 @@ class Decoder:
     def prefill(self, ids: torch.Tensor):
         """ids (B,Tp): consume the prompt window by window; returns the logits after its last token (B,V)."""
         m, w = self.m, self.w
+        # the captured step holds parameter addresses and the mixers' derived constants: weights that changed since the
+        # capture (load_state_dict, an in-place update, a dtype change) retire it
+        stamp = m.weights_stamp()
+        if stamp != self._stamp:
+            self._graph, self._gen_key, self._stamp = None, None, stamp
         states = [None] * m.layers
         h = None; n = 0
         for s in range(0, ids.shape[1], w):
@@ -62,7 +69,17 @@ class Decoder:
         the library path wins)."""
         m = self.m
         return (self.fused and self.B <= 4 and m.e.weight.dtype == torch.bfloat16 and m.d % 8 == 0 and
-                all(isinstance(mx, AssocCarrier) for mx in m.mix))
+                all(isinstance(mx, AssocCarrier) and mx.plain_step for mx in m.mix))
+
+    @property
+    def launches_per_token(self):
+        """Kernels in one token's graph: this library's on the fused path (draw, embedding, five per layer, head); on the
+        library-GEMM path the count includes the GEMMs and the copies around them."""
+        L = self.m.layers
+        if self._fused_ok():
+            return 1 + 1 + 5 * L + 1
+        per_layer = 2 + 1 + 1 + 1 + 1 + 1 + 1            # two add+norm, projection, state step, output projection, MLP up (+GELU) and down
+        return 1 + 3 + per_layer * L + 2 + 1               # draw; embedding gather x2 + add; layers; final add+norm, head; logits copy
 
     def _step_fused(self, advance: bool = True):
         """Every linear layer of the step as one launch that also does the residual add and norm before it and the
@@ -93,8 +110,10 @@ class Decoder:
             x, z = m._add_norm(x, delta, mx.ln)
             if isinstance(mx, AssocCarrier):
                 mx.inplace_state = True
-                delta, _ = mx.mix(z, (st[0], self.shift))
+                delta, new = mx.mix(z, (st[0], self.shift) + tuple(st[2:]))
                 mx.inplace_state = False
+                if len(st) == 3:                               # the short convolution's context comes back as a new tensor
+                    st[2].copy_(new[2])
             else:
                 delta, new = mx.mix(z, st)
                 for a, b in zip(st, new): a.copy_(b)
@@ -130,7 +149,7 @@ class Decoder:
 
     @staticmethod
     def sample(lg: torch.Tensor, temp: float, g: Optional[torch.Generator]):
-        """Greedy at temp 0, else one draw from softmax(lg / temp) per row (src/bench.py:79-86 without min-p); on device."""
+        """Greedy at temp 0, else one draw from softmax(lg / temp) per row (src/bench.py:79-86); on device."""
         if temp == 0:
             return lg.argmax(-1)
         return torch.multinomial(torch.softmax(lg.float() / temp, -1), 1, generator=g).squeeze(-1)
@@ -147,7 +166,7 @@ class Decoder:
         ticket = torch.zeros(1, dtype=torch.int32, device=self.dev)
         nxt = torch.empty(self.B, dtype=torch.long, device=self.dev)
         for _ in range(n):                                   # the same draws as the graphed loop, launched one by one
-            ops.decode_sample(lg, temp, seed, nxt, cnt, ticket, hist=out)
+            ops.decode_sample(lg, temp, seed, nxt, cnt, ticket, hist=out, min_p=self.min_p)
             lg = self.step(nxt)
         return out[:, :n]
 
@@ -156,11 +175,11 @@ class Decoder:
         logits waiting: a fixed kernel sequence, nothing on the host. The position and the rebase shift belong to the token
         being fed, so the draw kernel advances them for the PREVIOUS token (from the second token on) before the step."""
         ops.decode_sample(self._lg_in, temp, seed, self.tok, self._cnt, self._ticket, hist=self._hist, pos=self.pos,
-                          shift=self.shift, ctx=self.w)
+                          shift=self.shift, ctx=self.w, min_p=self.min_p)
         self._lg_in.copy_(self._step(advance=False))
 
     def _generate_graphed(self, lg, n: int, temp: float, seed: int):
-        key = (n, float(temp), int(seed))
+        key = (n, float(temp), int(seed), self.min_p)
         if getattr(self, "_gen_key", None) != key:
             V = lg.shape[-1]
             self._lg_in = torch.empty(self.B, V, dtype=torch.float32, device=self.dev)

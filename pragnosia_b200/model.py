@@ -54,6 +54,7 @@ class LM(nn.Module):
         self.n = nn.LayerNorm(d)
         self.use_graphs = True          # CUDA: replay one captured graph per window in forward_carried
         self._graphs = {}
+        self._graphs_stamp = None
         if norm == "rms":                      # every residual-stream LayerNorm becomes an RMSNorm of the same width
             for mod in list(self.modules()):
                 for nm, child in list(mod.named_children()):
@@ -67,6 +68,12 @@ class LM(nn.Module):
             nn.init.normal_(m.weight, 0.0, 0.02)
             if getattr(m, "bias", None) is not None:
                 nn.init.zeros_(m.bias)
+
+    def weights_stamp(self):
+        """Changes whenever a captured graph of this model would compute with something stale: a parameter that moved
+        (another dtype or device) or a mixer whose derived constants must be rebuilt (an in-place update, load_state_dict)."""
+        ptrs = tuple(p.data_ptr() for p in self.parameters())
+        return ptrs, tuple(mx.consts_key() for mx in self.mix if isinstance(mx, AssocCarrier))
 
     def _embed(self, x):
         return self.e(x) + self.p(torch.arange(x.shape[1], device=x.device) % self.p.num_embeddings)
@@ -112,6 +119,12 @@ class LM(nn.Module):
         window = window or self.ctx
         B, T = x.shape
         if self.use_graphs and x.is_cuda and T % window == 0 and T >= window:
+            # A captured graph holds the addresses of the parameters and of the constants the mixers derive from them
+            # (the concatenated projection weight, the gated output weight): any change of either retires every graph.
+            stamp = self.weights_stamp()
+            if stamp != self._graphs_stamp:
+                self._graphs.clear()
+                self._graphs_stamp = stamp
             key = (B, window, x.device, self.e.weight.dtype)
             run = self._graphs.get(key)
             if run is None:

@@ -205,7 +205,95 @@ def lm():
     save("lm", out)
 
 
+# ------------------------------------------------------------------ 8. the layer's options
+def options():
+    """AssocCarrier with each option of src/assoc.py on: one 70-token pass, two carried windows, ten T=1 steps."""
+    out = {}
+    cases = (("topk", dict(key_topk=8), False), ("floor", dict(hl_floor=True), False), ("write_all", dict(write_all=True), False),
+             ("write_all_delta", dict(write_all=True), True), ("pos_wrap", {}, False), ("beta_scale", {}, True),
+             ("sconv", {}, False), ("sconv_delta_topk", dict(key_topk=16), True))
+    for name, kw, delta in cases:
+        g = torch.Generator().manual_seed(1000 + len(name))
+        d, heads = 128, 2
+        P = oracle.init_assoc_params({}, "", d, heads, delta, g, jitter=0.3)
+        m = AssocCarrier(d, heads=heads, delta=delta, **kw)
+        if name.startswith("sconv"):
+            m.add_short_conv(4)
+            P["sconv"] = m.sconv.detach().clone() + 0.3 * torch.randn(3 * d, 4, generator=g)
+        m.load_state_dict(P, strict=True)
+        if name == "pos_wrap":
+            m.pos_wrap = 16
+        x = torch.randn(2, 70, d, generator=g)
+        extra = {}
+        if name == "beta_scale":
+            extra["beta_scale"] = torch.rand(2, heads, 70, generator=g)
+            m.beta_scale = extra["beta_scale"]
+            y, st = m(x)
+            out[name] = dict(check=checksum(x, *P.values()), y=y, S=st[0], **extra)
+            continue
+        y, st = m(x)
+        ya, sa = m(x[:, :30]); yb, sb = m(x[:, 30:], h0=sa)
+        cur = sa; steps = []
+        for t in range(30, 40):
+            yt, cur = m(x[:, t:t + 1], h0=cur); steps.append(yt)
+        rec = dict(check=checksum(x, *P.values()), y=y, S=st[0], y_windows=torch.cat([ya, yb], 1), S_windows=sb[0],
+                   y_steps=torch.cat(steps, 1), S_steps=cur[0])
+        if name.startswith("sconv"):
+            rec["cc"] = st[2]; rec["cc_steps"] = cur[2]
+        out[name] = rec
+    save("options", out)
+
+
+# ------------------------------------------------------------------ 9. gradients of the two simplest operators
+def grads():
+    """The reference's gradients for the lambda scan (tests/test_spin.py:237-246: B2 T45 D300, carried h0, loss through
+    Re h, the final Re and the final Im state; autograd through its fp64 scan_gated) and for the plumbing before the scan
+    (tests/test_assoc.py:189-212: its torch form prep_ref, differentiated by autograd)."""
+    out = {}
+    torch.set_grad_enabled(True)
+    g = torch.Generator().manual_seed(6)
+    B, T, D = 2, 45, 300
+    u = torch.randn(B, T, D, generator=g); lm = -torch.rand(B, T, D, generator=g) * 8; an = torch.randn(B, T, D, generator=g)
+    h0 = (torch.randn(B, D, generator=g), torch.randn(B, D, generator=g))
+    w, wl, wi = torch.randn(B, T, D, generator=g), torch.randn(B, D, generator=g), torch.randn(B, D, generator=g)
+    a64 = [t.double().requires_grad_(True) for t in (u, lm, an, h0[0], h0[1])]
+    y, (r, i) = SpinCarrier.scan_gated(a64[0], a64[1], a64[2], (a64[3], a64[4]), chunk=8)
+    ((y * w).sum() + (r * wl).sum() + (i * wi).sum()).backward()
+    out["lambda"] = dict(check=checksum(u, lm, an, *h0, w, wl, wi), grads=[t.grad.float() for t in a64])
+
+    def prep_ref(qp, kp, vp, gl, theta, pos):                     # tests/test_assoc.py:189-193
+        q_, k_, v_ = [F.normalize(t.transpose(1, 2).float(), dim=-1) for t in (qp, kp, vp)]
+        if gl is not None:
+            k_ = k_ * torch.sigmoid(gl.float()).transpose(1, 2).unsqueeze(-1)
+        return rotate(q_, theta, pos), rotate(k_, theta, pos), v_
+    out["prep"] = {}
+    for Dk, Tp, gate, p0 in ((64, 2048, True, 0), (64, 333, False, 1000), (128, 512, True, 4096)):
+        g = torch.Generator().manual_seed(Dk + Tp)
+        Hp = 3
+        mk = lambda: (torch.randn(2, Tp, Hp, Dk, generator=g) * 3).to(torch.bfloat16).requires_grad_()
+        qp, kp, vp = mk(), mk(), mk()
+        gl = (torch.randn(2, Tp, Hp, generator=g) * 2).to(torch.bfloat16).requires_grad_() if gate else None
+        th = (10000.0 ** (-torch.arange(0, Dk, 2).float() / Dk)).unsqueeze(0).repeat(Hp, 1).requires_grad_()
+        pos = p0 + torch.arange(Tp)
+        refs = prep_ref(qp, kp, vp, gl, th, pos)
+        ws = [torch.randn(r.shape, generator=g) for r in refs]
+        ins = [qp, kp, vp, th] + ([gl] if gate else [])
+        gr = torch.autograd.grad(sum((r * w_).sum() for r, w_ in zip(refs, ws)), ins)
+        st = max(1, Tp // 64)                                     # keep every st-th token of the big tensors
+        out["prep"][(Dk, Tp, gate, p0)] = dict(
+            check=checksum(qp.detach().float(), kp.detach().float(), vp.detach().float(), *ws),
+            outs=[r.detach()[:, :, ::st].to(torch.bfloat16).clone() for r in refs],
+            dqp=gr[0][:, ::st].float().clone(), dkp=gr[1][:, ::st].float().clone(), dvp=gr[2][:, ::st].float().clone(),
+            dth=gr[3].float().clone(), dgl=(gr[4][:, ::st].float().clone() if gate else None))
+    torch.set_grad_enabled(False)
+    save("grads", out)
+
+
+ALL = (plain_fp64, cfg0, ragged, delta_kat, lam, layers, lm, options, grads)
+
 if __name__ == "__main__":
     print(f"reference at {REF}, torch {torch.__version__}")
-    for fn in (plain_fp64, cfg0, ragged, delta_kat, lam, layers, lm):
-        print(fn.__name__); fn()
+    want = set(sys.argv[2:])                                      # optional: names of the fixtures to (re)make
+    for fn in ALL:
+        if not want or fn.__name__ in want:
+            print(fn.__name__); fn()

@@ -102,9 +102,33 @@ def test_model_loads_reference_named_checkpoints():
         LM(mixer="attn")
 
 
-def test_lambda_scan_segment_choice():
-    """The host picks more time segments when there are few channels and never more than the sequence has."""
-    from pragnosia_b200 import _lib
-    L = _lib.lib()
-    # not exported through the C ABI table; reach the C++ symbol only if present (it is an internal helper)
-    assert L.pgb_abi_version() == 1
+def test_lambda_scan_segment_choice(L):
+    """The host picks more time segments when there are few channels and never more than the sequence has pieces."""
+    ts = lambda B, T, D: L.pgb_lambda_scan_time_segments(B, T, D, 148)
+    assert ts(64, 32768, 768) == 8                             # 12288 channel quads x 8 segments: whole rounds of resident warps
+    assert ts(1, 32768, 64) == 32                              # 16 quads: the time axis must supply the parallelism
+    assert ts(1, 32768, 64) >= ts(8, 32768, 768) >= ts(64, 32768, 768)
+    assert ts(2, 1, 300) == 1 and ts(2, 6, 300) <= 2           # a short sequence has nothing to split
+    for B, T, D in ((2, 45, 300), (16, 512, 704), (3, 1000, 24)):
+        t = ts(B, T, D)
+        assert t in (1, 2, 4, 8, 16, 32)
+    assert ts(0, 5, 5) == 0 and L.pgb_lambda_scan_time_segments(1, 5, 5, 0) == 0
+
+
+def test_new_entry_points_reject_bad_calls(L):
+    one = ctypes.c_void_p(0x1000)
+    assert L.pgb_assoc_out_fwd(one, one, one, 0, one, None, one, 1, 1, 8, 64, None) == 1
+    assert L.pgb_assoc_out_fwd(one, one, one, 0, one, one, one, 1, 1, 8, 96, None) == 3
+    assert L.pgb_prefix_scan_fwd(one, one, 9, one, one, None, one, one, 1, 1, 1, 64, None) == 5
+    assert L.pgb_delta_inv_fwd(ctypes.c_void_p(0x1004), one, one, one, 1, 1, 8, 64, None) == 4
+    assert L.pgb_delta_loop_fwd(one, one, 0, one, None, one, None, one, one, one, 1, 1, 8, 64, None) == 1
+    assert L.pgb_key_topk_mask(one, 0, 64, 64, 64, 1, 1, 1, 64, 0, None) == 2
+    assert L.pgb_key_topk_mask(one, 0, 64, 64, 64, 1, 1, 1, 64, 65, None) == 2
+    assert L.pgb_short_conv_fwd(one, 0, 8, 8, one, one, one, one, 1, 1, 8, 4, None) == 2       # cache_in == cache_out
+    assert L.pgb_lambda_scan_bwd(one, one, one, one, 0, 0, one, None, None, one, one, one, None, None, 1, 1, 4, None) == 1
+    assert L.pgb_lambda_scan_bwd(one, one, one, one, 0, 0, one, one, None, one, one, one, one, None, 1, 1, 4, None) == 1
+    assert L.pgb_aspin_prep_bwd(one, one, one, 0, 64, 64, 64, one, 1, 1, one, one, one, one, one, 0, one, one, one, None, one,
+                                1, 1, 1, 64, None) == 1                                          # a gate without room for its gradient
+    assert L.pgb_decode_sample_ex(one, 0, 1.0, 1.5, 0, one, None, 0, one, None, None, one, 1, 8, 1, None) == 2
+    assert L.pgb_skinny_linear_ex(one, None, None, None, 0, 1e-5, one, None, 0, one, None, 1, 768, 16, 4, None) == 2
+    assert L.pgb_aspin_prep_bwd_tiles(17) == 3

@@ -1,0 +1,83 @@
+"""Configuration 2 at its configuration: the 91.9 M-parameter aspin LM (d768, 12 layers, 12 x 64 heads, vocabulary 8192,
+bf16 weights, fp32 state), a 512-token prompt, then teacher-forced decode steps at batch 1 (every linear layer through the
+fused small-batch kernel: five launches a layer) and batch 64 (the library GEMM path), eager and under the captured graph,
+against the CPU oracle on the same bf16-rounded weights with the product's rounding points (src/bench.py:206-238 is the
+loop). Then the free-running sampled loop: 4096 steps stay finite and the graphed history equals an eager replay."""
+import pytest
+import torch
+
+import oracle
+from oracle import rel_err
+from pragnosia_b200 import synth
+from pragnosia_b200.generate import Decoder
+from pragnosia_b200.model import LM
+
+pytestmark = pytest.mark.gpu
+torch.set_grad_enabled(False)
+DEV = "cuda"
+CFG = dict(vocab=8192, d=768, layers=12, mlp_mult=4, ctx=512, mixer="aspin", norm="rms")
+STEPS = 16
+
+
+@pytest.fixture(scope="module")
+def lm():
+    cfg = oracle.lm_config(**CFG)
+    P = oracle.init_lm_params(cfg, seed=2)
+    m = LM(**CFG)
+    m.load_state_dict(P, strict=True)
+    assert abs(sum(p.numel() for p in m.parameters()) / 1e6 - 91.93) < 0.01
+    Pb = {k: v.to(torch.bfloat16).float() for k, v in P.items()}
+    return m.to(DEV).to(torch.bfloat16).eval(), Pb, cfg
+
+
+def oracle_run(Pb, cfg, ids):
+    """Prompt pass + STEPS teacher-forced steps on the CPU with bf16 hand-overs; logits per step and the layer-0 / layer-11
+    states at the end."""
+    with oracle.rounding(torch.bfloat16):
+        lg0, states = oracle.lm_prefill(Pb, cfg, ids[:, :512])
+        out = [lg0[:, -1]]
+        for t in range(512, 512 + STEPS):
+            out.append(oracle.lm_decode_step(Pb, cfg, ids[:, t], t % 512, states))
+    return torch.stack(out, 1), states[0][0], states[11][0]
+
+
+@pytest.mark.parametrize("B,rows", [(1, [0]), (64, [3, 41])])
+def test_config2_teacher_forced_decode(lm, B, rows):
+    m, Pb, cfg = lm
+    ids = synth.token_ids(B, 512 + STEPS + 1, 8192, seed=70 + B)
+    ref_lg, ref_S0, ref_S11 = oracle_run(Pb, cfg, ids[rows])
+    got = {}
+    for use_graph in (False, True):
+        dec = Decoder(m, batch=B, use_graph=use_graph)
+        assert dec._fused_ok() == (B <= 4)
+        lg = [dec.prefill(ids[:, :512].to(DEV))]
+        for t in range(512, 512 + STEPS):
+            lg.append(dec.step(ids[:, t].to(DEV)).clone())
+        lg = torch.stack(lg, 1)
+        got[use_graph] = lg
+        assert torch.isfinite(lg).all()
+        e = rel_err(lg[rows].float().cpu(), ref_lg)
+        es0, es11 = rel_err(dec.states[0][0][rows].cpu(), ref_S0), rel_err(dec.states[11][0][rows].cpu(), ref_S11)
+        assert e <= 1e-2 and es0 <= 5e-3 and es11 <= 1e-2, (B, use_graph, e, es0, es11)
+        # the decode steps alone, relative to the prompt's own error: a step adds no visible error of its own
+        step_err = [rel_err(lg[rows, i].float().cpu(), ref_lg[:, i]) for i in range(STEPS + 1)]
+        assert max(step_err[1:]) <= 2.5 * max(step_err[0], 2e-3), step_err
+    assert rel_err(got[True], got[False]) <= 1e-6                                     # a graph replay is the eager step
+
+
+@pytest.mark.parametrize("B", [1, 64])
+def test_config2_free_running_generation(lm, B):
+    m, _, _ = lm
+    prompt = synth.token_ids(B, 512, 8192, seed=9).to(DEV)
+    dec = Decoder(m, batch=B)
+    hist = dec.generate(prompt, 4096, temp=1.0, seed=0)
+    assert tuple(hist.shape) == (B, 4096) and int(hist.min()) >= 0 and int(hist.max()) < 8192
+    assert torch.isfinite(dec.step(hist[:, -1])).all()
+    for st in dec.states:
+        assert torch.isfinite(st[0]).all()
+    again = dec.generate(prompt, 4096, temp=1.0, seed=0)
+    assert torch.equal(hist, again)                                                  # seeded: the same 4096 tokens
+    n = 192                                                                           # eager replay of the same seed
+    eager = Decoder(m, batch=B, use_graph=False).generate(prompt, n, temp=1.0, seed=0)
+    assert torch.equal(eager, hist[:, :n])
+    assert len(torch.unique(hist[0])) > 500                                           # temperature 1 over 8192 ids: not stuck

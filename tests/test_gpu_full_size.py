@@ -124,8 +124,16 @@ def test_config1_lm_prefill_full_size_rows():
     assert tuple(lg.shape) == (16, 512, 8192) and states[0][0].dtype == torch.float32 and flag() == 0
     rows = [0, 11]
     Pb = {k: v.to(torch.bfloat16).float() for k, v in P.items()}
-    ref, rstates = oracle.lm_prefill(Pb, cfg, ids[rows])
-    assert rel_err(lg[rows].float().cpu(), ref) <= 3e-2
-    assert rel_err(states[0][0][rows].cpu(), rstates[0][0]) <= 3e-2
+    # (1) against the oracle that rounds where the product rounds (bf16 after every linear layer, norm, activation and
+    # residual add; fp32 state and accumulation): what remains is summation order inside the GEMMs and the kernels' own error
+    with oracle.rounding(torch.bfloat16):
+        ref, rstates = oracle.lm_prefill(Pb, cfg, ids[rows])
+    e_lg = rel_err(lg[rows].float().cpu(), ref)
+    e_s0, e_s11 = rel_err(states[0][0][rows].cpu(), rstates[0][0]), rel_err(states[11][0][rows].cpu(), rstates[11][0])
+    assert e_lg <= 5e-3 and e_s0 <= 2e-3 and e_s11 <= 5e-3, (e_lg, e_s0, e_s11)
+    # (2) against the plain fp32 oracle on the same weights: the distance a bf16 run of this depth has from fp32 arithmetic
+    ref32, rstates32 = oracle.lm_prefill(Pb, cfg, ids[rows])
+    assert rel_err(lg[rows].float().cpu(), ref32) <= 3e-2
+    assert rel_err(states[0][0][rows].cpu(), rstates32[0][0]) <= 3e-2
     lg2 = m.forward_carried(ids[rows].to(DEV))
     assert rel_err(lg2.float(), lg[rows].float()) <= 2e-2                      # GEMM tiling may differ with the batch size

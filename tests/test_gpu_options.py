@@ -1,0 +1,149 @@
+"""The layer's options on the GPU (short convolution, key_topk, hl_floor, write_all, pos_wrap, beta_scale: src/assoc.py
+:361-382, :406-410, :435-439, :463-478) against the reference module's own CPU outputs (options.pt); housekeeping checks
+that live beside them: weights changed after a captured graph, the one-row fused linear at long rows, min-p sampling."""
+import pytest
+import torch
+
+import oracle
+from oracle import rel_err
+from pragnosia_b200 import ops, synth
+from pragnosia_b200.assoc import AssocCarrier
+from pragnosia_b200.generate import Decoder
+from pragnosia_b200.model import LM
+from test_oracle_options_grads import CASES, option_inputs
+
+pytestmark = pytest.mark.gpu
+torch.set_grad_enabled(False)
+DEV = "cuda"
+
+
+def build(name, kw, delta, dtype=torch.float32):
+    P, x, bs = option_inputs(name, delta)
+    ctor = {k: v for k, v in kw.items() if k != "pos_wrap"}
+    m = AssocCarrier(128, heads=2, delta=delta, **ctor)
+    if name.startswith("sconv"):
+        m.add_short_conv(4)
+    m.load_state_dict(P, strict=True)
+    if "pos_wrap" in kw:
+        m.pos_wrap = kw["pos_wrap"]
+    return m.to(DEV).to(dtype).eval(), P, x, bs
+
+
+@pytest.mark.parametrize("name,kw,delta", CASES)
+def test_layer_options_match_the_reference_module(golden, name, kw, delta):
+    G = golden("options")[name]
+    m, P, x, bs = build(name, kw, delta)
+    xd = x.to(DEV)
+    if name == "beta_scale":
+        m.beta_scale = bs.to(DEV)
+        y, st = m(xd)
+        assert rel_err(y.cpu(), G["y"]) <= 1e-4 and rel_err(st[0].cpu(), G["S"]) <= 1e-4
+        return
+    y, st = m(xd)
+    assert rel_err(y.cpu(), G["y"]) <= 1e-4 and rel_err(st[0].cpu(), G["S"]) <= 1e-4
+    ya, sa = m(xd[:, :30]); yb, sb = m(xd[:, 30:], h0=sa)
+    assert rel_err(torch.cat([ya, yb], 1).cpu(), G["y_windows"]) <= 1e-4 and rel_err(sb[0].cpu(), G["S_windows"]) <= 1e-4
+    cur, steps = sa, []
+    for t in range(30, 40):
+        yt, cur = m(xd[:, t:t + 1], h0=cur); steps.append(yt)
+    assert rel_err(torch.cat(steps, 1).cpu(), G["y_steps"]) <= 1e-4 and rel_err(cur[0].cpu(), G["S_steps"]) <= 1e-4
+    if name.startswith("sconv"):
+        assert len(st) == 3 and rel_err(st[2].cpu(), G["cc"]) <= 1e-5 and rel_err(cur[2].cpu(), G["cc_steps"]) <= 1e-5
+
+
+@pytest.mark.parametrize("name,kw,delta", [c for c in CASES if c[0] in ("topk", "write_all", "pos_wrap", "sconv", "floor")])
+def test_layer_options_bf16_fused_path(name, kw, delta):
+    """The same options with bf16 weights (the fused between-GEMMs kernel where the option allows it) against the oracle run
+    on the bf16-rounded weights with the product's rounding points."""
+    m, P, x, _ = build(name, kw, delta, torch.bfloat16)
+    Pb = {k: v.to(torch.bfloat16).float() for k, v in P.items()}
+    xb = x.to(torch.bfloat16)
+    y, st = m(xb.to(DEV))
+    with oracle.rounding(torch.bfloat16):
+        ry, rst = oracle.assoc_layer(Pb, "", xb.float(), None, heads=2, delta=delta, **kw)
+    assert rel_err(y.float().cpu(), ry) <= 2e-2 and rel_err(st[0].cpu(), rst[0]) <= 2e-2
+
+
+def test_key_topk_and_short_conv_kernels():
+    g = torch.Generator().manual_seed(5)
+    for dtype, D in ((torch.float32, 64), (torch.bfloat16, 128)):
+        buf = torch.randn(2, 37, 3 * 2 * D + 8, generator=g).to(dtype)                # a view into a wider row, as in the layer
+        kp = buf[..., 2 * D:4 * D].unflatten(-1, (2, D))
+        ref = kp.float() * torch.zeros_like(kp.float()).scatter_(-1, kp.float().abs().topk(9, dim=-1).indices, 1.0)
+        bd = buf.to(DEV)
+        ops.key_topk_mask_(bd[..., 2 * D:4 * D].unflatten(-1, (2, D)), 9)
+        assert torch.equal(bd[..., 2 * D:4 * D].unflatten(-1, (2, D)).float().cpu(), ref)
+        assert torch.equal(bd[..., :2 * D].cpu(), buf[..., :2 * D])                   # nothing else touched
+    for T in (1, 2, 3, 50):
+        x = torch.randn(2, T, 96, generator=g); w = torch.randn(96, 4, generator=g); cc = torch.randn(2, 96, 3, generator=g)
+        for cache in (None, cc):
+            P = {"sconv": w}
+            q, k, v, new = oracle.short_conv(P, "", x[..., :32], x[..., 32:64], x[..., 64:], cache)
+            y, nd = ops.short_conv(x.to(DEV), w.to(DEV), None if cache is None else cache.to(DEV))
+            assert rel_err(y.cpu(), torch.cat([q, k, v], -1)) <= 1e-6 and torch.equal(nd.cpu(), new)
+
+
+def test_weights_changed_after_a_captured_graph():
+    """load_state_dict (and an in-place update) after the first graphed call: the next call computes with the NEW weights,
+    as a fresh model does -- the captured graphs held the old derived constants."""
+    cfg = oracle.lm_config(vocab=256, d=128, layers=2, mlp_mult=2, ctx=32, mixer="aspin", norm="rms")
+    P1, P2 = oracle.init_lm_params(cfg, seed=1, jitter=0.2), oracle.init_lm_params(cfg, seed=2, jitter=0.2)
+    mk = lambda: LM(vocab=256, d=128, layers=2, mlp_mult=2, ctx=32, mixer="aspin", norm="rms")
+    ids = synth.token_ids(2, 96, 256, seed=5).to(DEV)
+    for dtype in (torch.float32, torch.bfloat16):
+        m = mk(); m.load_state_dict(P1); m = m.to(DEV).to(dtype).eval()
+        first = m.forward_carried(ids).clone()
+        dec = Decoder(m, batch=2); dec.prefill(ids[:, :40]); dec.step(ids[:, 40])
+        m.load_state_dict(P2)
+        fresh = mk(); fresh.load_state_dict(P2); fresh = fresh.to(DEV).to(dtype).eval()
+        want = fresh.forward_carried(ids)
+        got = m.forward_carried(ids)
+        assert torch.equal(got, want) and not torch.equal(got, first)
+        d2 = Decoder(fresh, batch=2); d2.prefill(ids[:, :40])
+        dec.prefill(ids[:, :40])
+        assert torch.equal(dec.step(ids[:, 40]), d2.step(ids[:, 40]))
+        with torch.no_grad():
+            m.mix[0].theta.mul_(1.5); fresh.mix[0].theta.mul_(1.5)                    # in place: same address, new version
+        assert torch.equal(m.forward_carried(ids), fresh.forward_carried(ids))
+
+
+def test_one_row_fused_linear_long_rows_is_deterministic():
+    """One row with a norm and K beyond the per-lane register buffer (1024): every warp builds the row in its own slice of
+    shared memory, so repeated launches are bit-identical and equal the two-row instantiation's first row."""
+    g = torch.Generator().manual_seed(11)
+    for K in (2048, 6144):
+        for norm in (torch.nn.RMSNorm(K), torch.nn.LayerNorm(K)):
+            norm = norm.to(DEV).to(torch.bfloat16)
+            with torch.no_grad():
+                norm.weight.copy_(torch.randn(K, generator=g)); 
+                if hasattr(norm, "bias") and norm.bias is not None: norm.bias.copy_(torch.randn(K, generator=g) * 0.1)
+            x = torch.randn(2, K, generator=g).to(torch.bfloat16).to(DEV); dl = torch.randn(2, K, generator=g).to(torch.bfloat16).to(DEV)
+            W = (torch.randn(520, K, generator=g) * K ** -0.5).to(torch.bfloat16).to(DEV)
+            two, _ = ops.skinny_linear(x, W, None, delta=dl, norm=norm, act="gelu", want_sum=True)
+            outs = [ops.skinny_linear(x[:1], W, None, delta=dl[:1], norm=norm, act="gelu") for _ in range(40)]
+            assert all(torch.equal(o, outs[0]) for o in outs) and torch.equal(outs[0], two[:1])
+            ref = torch.nn.functional.gelu(torch.nn.functional.linear(norm((x[:1] + dl[:1])), W))
+            assert rel_err(outs[0].float(), ref.float()) <= 2e-2
+
+
+def test_min_p_sampling():
+    """src/bench.py:79-86 with MIN_P: ids below min_p x the top probability are never drawn; min_p = 0 changes nothing."""
+    g = torch.Generator().manual_seed(3)
+    lg = (torch.randn(4, 512, generator=g) * 3).to(DEV)
+    p = torch.softmax(lg, -1)
+    allowed = p >= 0.2 * p.max(-1, keepdim=True).values
+    tok = torch.zeros(4, dtype=torch.long, device=DEV); cnt = torch.zeros(1, dtype=torch.long, device=DEV)
+    ticket = torch.zeros(1, dtype=torch.int32, device=DEV)
+    seen = torch.zeros(4, 512, dtype=torch.bool, device=DEV)
+    for _ in range(300):
+        ops.decode_sample(lg, 1.0, 7, tok, cnt, ticket, min_p=0.2)
+        seen[torch.arange(4), tok] = True
+    assert not (seen & ~allowed).any() and (seen.sum(-1) > 1).all()
+    a, b = tok.clone(), tok.clone()
+    c1, c2 = torch.zeros(1, dtype=torch.long, device=DEV), torch.zeros(1, dtype=torch.long, device=DEV)
+    ops.decode_sample(lg, 1.0, 9, a, c1, ticket); ops.decode_sample(lg, 1.0, 9, b, c2, ticket, min_p=0.0)
+    assert torch.equal(a, b)
+    m = LM(vocab=256, d=128, layers=2, mlp_mult=2, ctx=32, mixer="aspin", norm="ln").to(DEV).eval()
+    prompt = synth.token_ids(2, 40, 256, seed=2).to(DEV)
+    out = Decoder(m, batch=2, min_p=0.3).generate(prompt, 10, temp=1.0, seed=1)
+    assert tuple(out.shape) == (2, 10) and torch.equal(out, Decoder(m, batch=2, min_p=0.3, use_graph=False).generate(prompt, 10, temp=1.0, seed=1))
