@@ -294,7 +294,7 @@ def short_conv(P, pre, qo, ko, vo, cc):
     x = torch.cat([qo, ko, vo], dim=-1).transpose(1, 2)                          # (B,3d,T)
     pad = cc.to(x.dtype) if cc is not None else x.new_zeros(x.shape[0], 3 * d, K - 1)
     xp = torch.cat([pad, x], dim=-1)
-    y = F.conv1d(xp, w.to(x.dtype).unsqueeze(1), groups=3 * d).transpose(1, 2)
+    y = _r(F.conv1d(xp, w.to(x.dtype).unsqueeze(1), groups=3 * d)).transpose(1, 2)
     return y[..., :d], y[..., d:2 * d], y[..., 2 * d:], xp[..., -(K - 1):]
 
 

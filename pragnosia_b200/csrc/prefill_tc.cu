@@ -34,16 +34,6 @@
 
 namespace pgb {
 
-// Phase timing for tuning builds only (-DPGB_TC_TIMING): CTA 0 accumulates clock64() deltas per phase.
-#ifdef PGB_TC_TIMING
-__device__ unsigned long long g_tc_phase[16];
-#define TC_MARK(i) do { if (blockIdx.x == 0 && threadIdx.x == 0) { const long long now_ = clock64(); \
-        atomicAdd(&g_tc_phase[i], (unsigned long long)(now_ - tmark_)); tmark_ = now_; } } while (0)
-#define TC_MARK_INIT long long tmark_ = clock64()
-#else
-#define TC_MARK(i) do {} while (0)
-#define TC_MARK_INIT do {} while (0)
-#endif
 
 template <int D>
 struct TcSmem {
@@ -176,7 +166,6 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
     float nx_own = 0.f, nx_other = 0.f, nx_gate = 0.f;
     if (warp < 2) { nx_own = fetch_decay(tid); nx_other = fetch_decay(tid ^ 32); nx_gate = fetch_gate(tid); }
 
-    TC_MARK_INIT;
     for (int c = 0; c < NC && ok; ++c) {
         const int t0 = c * TC_C, st = c & 1;
         const uint32_t qs = base + SM::off_q + st * SM::TILE, ks = base + SM::off_k + st * SM::TILE, vs = base + SM::off_v + st * SM::TILE;
@@ -191,7 +180,6 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
                 tma_load_3d(base + SM::off_v + o2 + s * 8192, &mv, nb, tma_c0 + 64 * s, t0 + TC_C, tma_c2);
             }
         }
-        TC_MARK(12);                                                  // next-chunk TMA issue
         // ---- decay statistics of the chunk: warps 0 and 1 each scan their 32 tokens and reduce the other half
         if (warp < 2) {
             // -softplus(gate logit) * exp(A_h) when the decay comes as logits (src/assoc.py:355-356); padding tokens: alpha = 1
@@ -214,7 +202,6 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
             eLs[tid] = expf(L);
             wts[tid] = (t0 + tid < T) ? expf(fminf(Ltot - L, 0.f)) : 0.f;
         }
-        TC_MARK(13);                                                  // decay statistics
         // ---- the entering state as an MN-major B operand, hi and lo (and to HBM if asked for)
         {
             uint8_t *sh = sm + SM::off_sh + (D == 128 ? wg * (D * 128) : 0), *sl = sm + SM::off_sl + (D == 128 ? wg * (D * 128) : 0);
@@ -235,12 +222,10 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
                     }
                 }
         }
-        TC_MARK(0);                                                   // stats + state split
         if (!mbar_wait(st ? bar_full1 : bar_full0, (c >> 1) & 1, 1)) { ok = false; }
         if (ROT_SMEM && ok && !mbar_wait(bar_rot, c & 1, 4)) ok = false;
-        TC_MARK(1);                                                   // TMA wait
+        ok = __syncthreads_and(ok);                                   // one verdict for the whole CTA: every thread leaves the loop at the same point
         __syncthreads();                                              // L, e^L, w are visible; the tiles have landed for everyone
-        TC_MARK(2);
         const float aC = expf(Ls[TC_C - 1]);
         if (ok) {
             if constexpr (RAW) {
@@ -325,11 +310,9 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
                 }
             }
         }
-        TC_MARK(3);                                                   // plumbing / K*w
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        TC_MARK(4);
         // ---- P, U, O2
         if (tid == 0 && ok) {
             tc_fence_after();
@@ -360,10 +343,9 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
             }
             mma_commit(bar_a);
         }
-        TC_MARK(5);                                                   // MMA issue
         if (ok && !mbar_wait(bar_a, c & 1, 2)) ok = false;
+        ok = __syncthreads_and(ok);
         tc_fence_after();
-        TC_MARK(6);                                                   // MMA wait
         if (ok) {
             // ---- A = P * decay, causal; hi and lo rows of the K-major A operand
             float pv[16];
@@ -395,11 +377,9 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
 #pragma unroll
                 for (int j = 0; j < 4 * NBO; ++j) S[g][j] = fmaf(aC, S[g][j], uv[g][j]);
         }
-        TC_MARK(7);                                                   // scores -> A, state update
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        TC_MARK(8);
         // ---- O1 = A V
         if (tid == 0 && ok) {
             tc_fence_after();
@@ -413,12 +393,12 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
             mma_commit(bar_b);
         }
         if (ok && !mbar_wait(bar_b, c & 1, 3)) ok = false;
+        ok = __syncthreads_and(ok);
         tc_fence_after();
         if (ROT_SMEM && tid == 0 && ok && c + 1 < NC) {              // A buffers are idle again: next chunk's (cos, sin) rows
             mbar_expect_tx(bar_rot, ROT_BYTES);
             bulk_load_1d(base + SM::off_ah, p.rot + ((size_t)h * p.rot_T + t0 + TC_C) * (D / 2), ROT_BYTES, bar_rot);
         }
-        TC_MARK(9);                                                   // O1 issue + wait
         // ---- o = O1 + e^{L_t} O2 [* rsqrt(mean(o^2) + eps) * w]
         float ov[4 * NBO];
         {
@@ -468,10 +448,8 @@ __global__ void __launch_bounds__(TC_NT) prefill_tc_kernel(const __grid_constant
                 }
             }
         }
-        TC_MARK(10);                                                  // epilogue
         tc_fence_before();
         __syncthreads();                                              // every TMEM read of this chunk is done before the next MMAs
-        TC_MARK(11);
     }
     // ---- final state
     if (ok) {
@@ -546,14 +524,6 @@ int rot_table_launch(const float *theta, float *table, int H, int T, int D, cuda
     return check_launch("rot_table_kernel");
 }
 
-#ifdef PGB_TC_TIMING
-int tc_phase_dump(unsigned long long *out16) {
-    unsigned long long zero[16] = {};
-    cudaMemcpyFromSymbol(out16, g_tc_phase, sizeof(zero));
-    cudaMemcpyToSymbol(g_tc_phase, zero, sizeof(zero));
-    return 0;
-}
-#endif
 
 int tc_error_flag(int *out) { return tc_read_error_flag(out); }
 

@@ -155,22 +155,6 @@ __global__ void __launch_bounds__(128) delta_inv_kernel(const __grid_constant__ 
 }
 
 // ------------------------------------------------------------------------------------------------ the chunk walk
-// Phase timing for tuning builds only (-DPGB_TC_TIMING): CTA (0,0) accumulates clock64() deltas per phase.
-#ifdef PGB_TC_TIMING
-__device__ unsigned long long g_td_phase[16];
-#define TD_MARK(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) { const long long now_ = clock64(); \
-        atomicAdd(&g_td_phase[i], (unsigned long long)(now_ - tmark_)); tmark_ = now_; } } while (0)
-#define TD_MARK_INIT long long tmark_ = clock64()
-int td_phase_dump(unsigned long long *out16) {
-    unsigned long long zero[16] = {};
-    cudaMemcpyFromSymbol(out16, g_td_phase, sizeof(zero));
-    cudaMemcpyToSymbol(g_td_phase, zero, sizeof(zero));
-    return 0;
-}
-#else
-#define TD_MARK(i) do {} while (0)
-#define TD_MARK_INIT do {} while (0)
-#endif
 
 struct TdParams {
     const float *la, *beta, *S0, *theta, *shift_dev;
@@ -292,11 +276,9 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
         chunk_stats(la, beta, c * TC_C, T, tid - 192, lane, warp - 6, L, L + 64, L + 128, L + 192);
     };
     if (warp >= 6) stats_of(0);
-    TD_MARK_INIT;
 
     for (int c = 0; c < NC && ok; ++c) {
         const int t0 = c * TC_C, st = SM::NSTAGE == 2 ? (c & 1) : 0;
-        TD_MARK(0);
         const uint32_t sb = base + SM::off_stage + st * SM::STAGE;
         const uint32_t qs = sb, ks = sb + SM::QK, vs = sb + 2 * SM::QK, xh = vs + SM::SQ, xl = xh + SM::SQ;
         uint8_t *ks_ptr = sm + SM::off_stage + st * SM::STAGE + SM::QK, *vs_ptr = ks_ptr + SM::QK;
@@ -321,10 +303,8 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
                     }
                 }
         }
-        TD_MARK(1);
         if (!mbar_wait(st ? bar_full1 : bar_full0, (SM::NSTAGE == 2 ? (c >> 1) : c) & 1, 21)) ok = false;
-        __syncthreads();
-        TD_MARK(2);
+        ok = __syncthreads_and(ok);                                   // one verdict for the whole CTA: every thread leaves the loop at the same point
         const float aC = expf(Ls[TC_C - 1]);
         // ---- K * w, head and tail, in K's own layout (an MN-major A operand)
         if (ok) {
@@ -346,7 +326,6 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        TD_MARK(3);
         // ---- first product group: P = Q K^T, KS = K S, O2 = Q S
         const uint64_t dsh = smem_desc(base + SM::off_sh, 16, 1024), dsl = smem_desc(base + SM::off_sl, 16, 1024);
         // Everyone waits for the round, so issue time counts: the three products go out from three warps (one accumulator
@@ -375,11 +354,10 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
             }
             mma_commit_elect(bar_a);
         }
-        TD_MARK(4);
         if (warp >= 6 && c + 1 < NC) stats_of(c + 1);
         if (ok && !mbar_wait(bar_a, c & 1, 22)) ok = false;
+        ok = __syncthreads_and(ok);
         tc_fence_after();
-        TD_MARK(5);
         if (ok) {
             // ---- A = P * decay (causal), head and tail; rhs = beta (V - e^{L_t} K S), head and tail
             float pv[16], kv[16];
@@ -414,7 +392,6 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        TD_MARK(6);
         // ---- second product group: W = X rhs  (head*head + head*tail + tail*head)
         const uint64_t dwh = smem_desc(base + SM::off_wh, 16, 1024), dwl = smem_desc(base + SM::off_wl, 16, 1024);
         if (warp == 0 && __all_sync(0xffffffffu, ok)) {               // the whole warp, converged: one elected lane issues
@@ -429,13 +406,12 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
             for (int k = 0; k < 4; ++k) mma_bf16_elect(tmem + TM_KS, dxl + k * 2, dwh + k * 128, I_W, 1);
             mma_commit_elect(bar_b);
         }
-        TD_MARK(7);
         if (ok && !mbar_wait(bar_b, c & 1, 23)) ok = false;
+        ok = __syncthreads_and(ok);
         tc_fence_after();
         // single stage: Q, K, V and X of this chunk are consumed (the first two product groups are complete, the generic
         // reads of K and V ended before the barrier ahead of the second), so the next chunk's tiles may overwrite them
         if (SM::NSTAGE == 1 && tid == 0 && ok && c + 1 < NC) load_stage(c + 1, 0);
-        TD_MARK(8);
         if (ok) {
             // ---- W back to shared memory (over rhs), head and tail
             float wv[16];
@@ -454,7 +430,6 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        TD_MARK(9);
         // ---- third product group: O1 = A W, U = (K w)^T W
         if (warp < 2 && __all_sync(0xffffffffu, ok)) {                // O1 from one warp's elected lane, U from another's
             tc_fence_after();
@@ -478,10 +453,9 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
             }
             mma_commit_elect(bar_c);
         }
-        TD_MARK(10);
         if (ok && !mbar_wait(bar_c, c & 1, 24)) ok = false;
+        ok = __syncthreads_and(ok);
         tc_fence_after();
-        TD_MARK(11);
         if (ok) {
             float ov[16], o2v[16], uv[NSG][16];
             tmem_ld_frag4(tmem + lane_base + TM_O1 + col0, ov);
@@ -512,7 +486,6 @@ __global__ void __launch_bounds__(TD_NT) prefill_tc_delta_kernel(const __grid_co
         }
         tc_fence_before();
         __syncthreads();
-        TD_MARK(12);
     }
     if (ok) {
 #pragma unroll

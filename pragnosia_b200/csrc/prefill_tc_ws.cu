@@ -69,20 +69,6 @@ __device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
     if (lane == 0) mbar_arrive(bar);
 }
 
-// Timeline trace for tuning builds only (-DPGB_TC_TIMING): CTA 0 stamps clock64() per role, chunk and event.
-#ifdef PGB_TC_TIMING
-__device__ long long g_ws_trace[64 * 16];
-#define WS_STAMP(c, ev) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (c) < 64) g_ws_trace[(c) * 16 + (ev)] = clock64(); } while (0)
-#else
-#define WS_STAMP(c, ev) do {} while (0)
-#endif
-#ifdef WS_TRACE_BACK                                                   // detail of the back role in the front's columns
-#define WS_STAMP_F(c, ev) do {} while (0)
-#define WS_STAMP_B(c, ev) WS_STAMP(c, ev)
-#else
-#define WS_STAMP_F(c, ev) WS_STAMP(c, ev)
-#define WS_STAMP_B(c, ev) do {} while (0)
-#endif
 
 template <bool RAW>
 __global__ void __launch_bounds__(WS_NT, 1) prefill_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
@@ -149,16 +135,12 @@ __global__ void __launch_bounds__(WS_NT, 1) prefill_tc_ws_kernel(const __grid_co
         for (int c = 0; c < NC; ++c) {
             const int s2 = c & 1, s3 = c % 3;
             const float *wts = stats + (c & 3) * 256 + 128, *gts = wts + 64;
-            if (warp == 0) WS_STAMP_F(c, 0);
             // the K*w slot and the P / U accumulators were last used by chunk c-2: free once the back has read U(c-2)
             bool fine = c < 2 || mbar_wait_warp(bar_free(s2), ((c >> 1) + 1) & 1, 31);
-            if (warp == 0) WS_STAMP_F(c, 1);
             fine = fine && mbar_wait_warp(bar_stats(c & 3), (c >> 2) & 1, 34);
-            if (warp == 0) WS_STAMP_F(c, 2);
             fine = fine && mbar_wait_warp(bar_full(s3), (c / 3) & 1, 32);
             if (RAW) fine = fine && mbar_wait_warp(bar_rot(s2), (c >> 1) & 1, 33);
             if (!fine) break;                                         // the other roles run out of their own waits
-            if (warp == 0) WS_STAMP_F(c, 3);
             uint8_t *qs_ptr = sm + SM::off_stage + s3 * STAGE_BYTES, *ks_ptr = qs_ptr + SM::TILE, *vs_ptr = ks_ptr + SM::TILE;
             uint8_t *kwh = sm + SM::off_kw + s2 * 2 * SM::TILE, *kwl = kwh + SM::TILE;
             if constexpr (RAW) {
@@ -239,7 +221,6 @@ __global__ void __launch_bounds__(WS_NT, 1) prefill_tc_ws_kernel(const __grid_co
                 }
             }
             warp_arrive(bar_ready(s2), lane);
-            if (warp == 0) WS_STAMP_F(c, 4);
         }
     } else if (warp < WS_FRONT + WS_BACK) {
         // =========================================================================================== back
@@ -295,10 +276,8 @@ __global__ void __launch_bounds__(WS_NT, 1) prefill_tc_ws_kernel(const __grid_co
         for (int c = 0; c < NC; ++c) {
             const int s2 = c & 1;
             const float *Ls = stats + (c & 3) * 256;
-            if (bw == 0) WS_STAMP(c, 5);
             ok = mbar_wait_warp(bar_stats(c & 3), (c >> 2) & 1, 41) && mbar_wait_warp(bar_pu(s2), (c >> 1) & 1, 42);
             if (!ok) break;
-            if (bw == 0) WS_STAMP(c, 6);
             tc_fence_after();
             float pv[16];
             tmem_ld_frag4(tmem + lane_base + TM_P + 64 * s2 + col0, pv);
@@ -313,7 +292,6 @@ __global__ void __launch_bounds__(WS_NT, 1) prefill_tc_ws_kernel(const __grid_co
             const float Lt0 = Ls[row0] * WS_LOG2E, Lt1 = Ls[row1] * WS_LOG2E;
             const float aC = expf(Ls[TC_C - 1]);
             tmem_ld_wait();
-            if (bw == 0) WS_STAMP_B(c, 0);
             {
                 uint8_t *ah = sm + SM::off_a + s2 * 2 * SM::TILE, *al = ah + SM::TILE;
                 uint32_t hi[8], lo[8];
@@ -334,9 +312,7 @@ __global__ void __launch_bounds__(WS_NT, 1) prefill_tc_ws_kernel(const __grid_co
                     *reinterpret_cast<uint32_t *>(ah + o1) = hi[2 * j + 1]; *reinterpret_cast<uint32_t *>(al + o1) = lo[2 * j + 1];
                 }
             }
-            if (bw == 0) WS_STAMP_B(c, 1);
             warp_arrive(bar_a(s2), lane);                             // A(c) is there: O1(c) may go
-            if (bw == 0) WS_STAMP(c, 7);
             float uv[16];
             tmem_ld_frag4(tmem + lane_base + TM_U + 64 * s2 + col0, uv);
             tmem_ld_wait();
@@ -347,12 +323,9 @@ __global__ void __launch_bounds__(WS_NT, 1) prefill_tc_ws_kernel(const __grid_co
             for (int j = 0; j < 16; ++j) S[j] = fmaf(aC, S[j], uv[j]);
             if (c + 1 < NC) {
                 // S slot (c+1)&1 was the operand of O2(c-1): finished once O1(c-1), issued after it, is
-                if (bw == 0) WS_STAMP_B(c, 2);
                 if (c >= 1 && !mbar_wait_warp(bar_o((c - 1) & 1), ((c - 1) >> 1) & 1, 44)) { ok = false; break; }
-                if (bw == 0) WS_STAMP_B(c, 3);
                 publish_state(c + 1);
             }
-            if (bw == 0) WS_STAMP(c, 11);
         }
         if (ok) {
 #pragma unroll
@@ -374,10 +347,8 @@ __global__ void __launch_bounds__(WS_NT, 1) prefill_tc_ws_kernel(const __grid_co
         for (int c = 0; c < NC; ++c) {
             const int t0 = c * TC_C, s2 = c & 1;
             const float *eLs = stats + (c & 3) * 256 + 64;
-            if (tw == 0) WS_STAMP(c, 8);
             bool fine = alive && mbar_wait_warp(bar_stats(c & 3), (c >> 2) & 1, 45) && mbar_wait_warp(bar_o(s2), (c >> 1) & 1, 43);
             if (!fine) { alive = false; abort_tail[sub] = 1; }
-            if (tw == 0) WS_STAMP(c, 9);
             tc_fence_after();
             float ov[16], o2v[16];
             tmem_ld_frag4(tmem + lane_base + TM_O1 + 64 * s2 + col0, ov);
@@ -426,7 +397,6 @@ __global__ void __launch_bounds__(WS_NT, 1) prefill_tc_ws_kernel(const __grid_co
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_done(c & 3));
-            if (tw == 0) WS_STAMP(c, 10);
         }
     } else if (warp == WS_STATS || warp == WS_STATS + 1) {
         // =========================================================================================== statistics
@@ -515,7 +485,6 @@ __global__ void __launch_bounds__(WS_NT, 1) prefill_tc_ws_kernel(const __grid_co
                 mma_commit(bar_pu(s2));
                 mma_commit(bar_empty(c % 3));                         // this issuer's half: P and U have read the chunk's tiles
                 mbar_arrive(bar_q(c & 3));                            // the other issuer may use the chunk's Q and V tiles
-                WS_STAMP(c, 12);
                 if (c + 2 < NC) load_rot(c + 2);                      // the front is done with this slot's rotation rows
                 ++pu_c; progress = true;
             }
@@ -547,7 +516,6 @@ __global__ void __launch_bounds__(WS_NT, 1) prefill_tc_ws_kernel(const __grid_co
                 for (int k = 0; k < 4; ++k) mma_bf16(tmem + TM_O2 + 64 * (c & 1), dq + k * 2, dsh + k * 128, I_O, k > 0);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) mma_bf16(tmem + TM_O2 + 64 * (c & 1), dq + k * 2, dsl + k * 128, I_O, 1);
-                WS_STAMP(c, 13);
                 ++o2_c; progress = true;
             }
             if (o1_c < o2_c && mbar_test(bar_a(o1_c & 1), (o1_c >> 1) & 1)) {
@@ -561,7 +529,6 @@ __global__ void __launch_bounds__(WS_NT, 1) prefill_tc_ws_kernel(const __grid_co
                 for (int k = 0; k < 4; ++k) mma_bf16(tmem + TM_O1 + 64 * (c & 1), dal + k * 2, dv + k * 128, I_O, 1);
                 mma_commit(bar_o(c & 1));
                 mma_commit(bar_empty(c % 3));                         // this issuer's half: O2 and O1 have read the chunk's tiles
-                WS_STAMP(c, 14);
                 ++o1_c; progress = true;
             }
             if (progress) idle = 0;
@@ -605,10 +572,6 @@ int prefill_tc_ws_launch(const PrefillArgs &a, int o_dtype, cudaStream_t stream)
     if (e != cudaSuccess) { set_cuda_error(e, "prefill_tc_ws launch"); return PGB_ERR_CUDA; }
     return check_launch("prefill_tc_ws_kernel");
 }
-
-#ifdef PGB_TC_TIMING
-int tc_ws_trace_dump(long long *out1024) { cudaMemcpyFromSymbol(out1024, g_ws_trace, sizeof(long long) * 64 * 16); return 0; }
-#endif
 
 int tc_ws_error_flag(int *out) { return tc_read_error_flag(out); }
 

@@ -25,7 +25,7 @@ def lm():
     P = oracle.init_lm_params(cfg, seed=2)
     m = LM(**CFG)
     m.load_state_dict(P, strict=True)
-    assert abs(sum(p.numel() for p in m.parameters()) / 1e6 - 91.93) < 0.01
+    assert abs(sum(p.numel() for p in m.parameters()) / 1e6 - 91.91) < 0.01         # 91.93 M with LayerNorm biases; RMSNorm has none
     Pb = {k: v.to(torch.bfloat16).float() for k, v in P.items()}
     return m.to(DEV).to(torch.bfloat16).eval(), Pb, cfg
 
@@ -56,13 +56,35 @@ def test_config2_teacher_forced_decode(lm, B, rows):
         lg = torch.stack(lg, 1)
         got[use_graph] = lg
         assert torch.isfinite(lg).all()
+        # logits of a random-init model are small sums of many bf16-rounded terms: two correct bf16 runs of this depth sit
+        # about 2e-2 of the largest logit apart (summation order decides each rounding); the fp32 states agree more closely
         e = rel_err(lg[rows].float().cpu(), ref_lg)
         es0, es11 = rel_err(dec.states[0][0][rows].cpu(), ref_S0), rel_err(dec.states[11][0][rows].cpu(), ref_S11)
-        assert e <= 1e-2 and es0 <= 5e-3 and es11 <= 1e-2, (B, use_graph, e, es0, es11)
+        assert e <= 3e-2 and es0 <= 2e-3 and es11 <= 1e-2, (B, use_graph, e, es0, es11)
         # the decode steps alone, relative to the prompt's own error: a step adds no visible error of its own
         step_err = [rel_err(lg[rows, i].float().cpu(), ref_lg[:, i]) for i in range(STEPS + 1)]
         assert max(step_err[1:]) <= 2.5 * max(step_err[0], 2e-3), step_err
     assert rel_err(got[True], got[False]) <= 1e-6                                     # a graph replay is the eager step
+
+
+def test_config2_decode_fp32_weights_pins_the_full_size_model():
+    """The same model and loop with fp32 weights (nothing rounds to bf16): prompt + teacher-forced steps at fp32 accuracy."""
+    cfg = oracle.lm_config(**CFG)
+    P = oracle.init_lm_params(cfg, seed=2)
+    m = LM(**CFG); m.load_state_dict(P, strict=True); m = m.to(DEV).eval()
+    ids = synth.token_ids(2, 512 + 9, 8192, seed=72)
+    lg0, states = oracle.lm_prefill(P, cfg, ids[:, :512])
+    ref = [lg0[:, -1]]
+    for t in range(512, 520):
+        ref.append(oracle.lm_decode_step(P, cfg, ids[:, t], t % 512, states))
+    for use_graph in (False, True):
+        dec = Decoder(m, batch=2, use_graph=use_graph)
+        out = [dec.prefill(ids[:, :512].to(DEV))]
+        for t in range(512, 520):
+            out.append(dec.step(ids[:, t].to(DEV)).clone())
+        e = rel_err(torch.stack(out, 1).cpu(), torch.stack(ref, 1))
+        es = rel_err(dec.states[11][0].cpu(), states[11][0])
+        assert e <= 5e-5 and es <= 1e-5, (use_graph, e, es)
 
 
 @pytest.mark.parametrize("B", [1, 64])

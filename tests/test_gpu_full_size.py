@@ -124,16 +124,30 @@ def test_config1_lm_prefill_full_size_rows():
     assert tuple(lg.shape) == (16, 512, 8192) and states[0][0].dtype == torch.float32 and flag() == 0
     rows = [0, 11]
     Pb = {k: v.to(torch.bfloat16).float() for k, v in P.items()}
-    # (1) against the oracle that rounds where the product rounds (bf16 after every linear layer, norm, activation and
-    # residual add; fp32 state and accumulation): what remains is summation order inside the GEMMs and the kernels' own error
+    # (1) The bf16 run against the oracle that rounds where the product rounds (bf16 after every linear layer, norm,
+    # activation and residual add; fp32 state and accumulation). With random-init weights the logits are small sums of
+    # many rounded terms, and which way each intermediate rounds depends on summation order: two correct bf16 runs of this
+    # depth differ by about 2e-2 of the largest logit (the rounding oracle itself sits 2.4e-2 from the fp32 one). The
+    # states, which accumulate in fp32, agree far more closely.
     with oracle.rounding(torch.bfloat16):
         ref, rstates = oracle.lm_prefill(Pb, cfg, ids[rows])
     e_lg = rel_err(lg[rows].float().cpu(), ref)
     e_s0, e_s11 = rel_err(states[0][0][rows].cpu(), rstates[0][0]), rel_err(states[11][0][rows].cpu(), rstates[11][0])
-    assert e_lg <= 5e-3 and e_s0 <= 2e-3 and e_s11 <= 5e-3, (e_lg, e_s0, e_s11)
-    # (2) against the plain fp32 oracle on the same weights: the distance a bf16 run of this depth has from fp32 arithmetic
+    agree = float((lg[rows].float().cpu().argmax(-1) == ref.argmax(-1)).float().mean())
+    assert e_lg <= 3e-2 and e_s0 <= 1e-3 and e_s11 <= 1e-2 and agree >= 0.9, (e_lg, e_s0, e_s11, agree)
+    # (2) against the plain fp32 oracle on the same weights
     ref32, rstates32 = oracle.lm_prefill(Pb, cfg, ids[rows])
     assert rel_err(lg[rows].float().cpu(), ref32) <= 3e-2
     assert rel_err(states[0][0][rows].cpu(), rstates32[0][0]) <= 3e-2
+    # (3) the same model, windows and kernels' fp32 variants with fp32 weights: nothing rounds to bf16, and the full-size
+    # model is pinned to the oracle at fp32 accuracy
+    m32 = LM(vocab=8192, d=768, layers=12, mlp_mult=4, ctx=512, mixer="aspin", norm="rms")
+    m32.load_state_dict(P, strict=True)
+    m32 = m32.to(DEV).eval()
+    lg32, st32 = m32.forward_carried(ids[rows].to(DEV), return_states=True)
+    rf, rs = oracle.lm_prefill(P, cfg, ids[rows])
+    e = (rel_err(lg32.cpu(), rf), rel_err(st32[0][0].cpu(), rs[0][0]), rel_err(st32[11][0].cpu(), rs[11][0]))
+    assert e[0] <= 5e-5 and e[1] <= 1e-5 and e[2] <= 1e-5, e
+    del m32
     lg2 = m.forward_carried(ids[rows].to(DEV))
     assert rel_err(lg2.float(), lg[rows].float()) <= 2e-2                      # GEMM tiling may differ with the batch size
