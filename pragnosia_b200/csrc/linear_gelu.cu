@@ -8,7 +8,10 @@
 //   memory, two of them (512 columns) so that the epilogue of tile i runs under the MMAs of tile i + 1.
 //   warp 0: TMA producer;  warp 1: MMA issuer (one elected lane of the converged warp), owns the tensor-memory allocation;
 //   warps 2-17: epilogue -- warp w reads TMEM lanes 32 (w mod 4) .. +31 (one output row per thread) and column quarter
-//   (w-2)/4, 32 columns at a time (four warps a scheduler: the erf chains of one hide behind the others): + bias, round to bf16 (where the separate Linear would round), GELU in fp32, round, 64-byte stores.
+//   (w-2)/4, 32 columns at a time with the next 32 already on their way from tensor memory: + bias (one packed pair per
+//   lane, fetched at the start of the tile and handed round by shuffles), round to bf16 (where the separate Linear would
+//   round), GELU in fp32, round, 64-byte stores. The epilogue's arithmetic is as long as the tile's MMAs, so its length
+//   per element decides the kernel's speed: see lg_gelu.
 //   One CTA per SM walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (column blocks fastest, so the CTAs running together
 //   share rows of x in L2). Every mbarrier wait is bounded; a wait that runs out sets the error flag and the CTA winds down.
 #include "tc_common.cuh"
@@ -19,7 +22,8 @@ constexpr int LG_BM = 128, LG_BN = 256, LG_BK = 64, LG_STAGES = 4;
 constexpr int LG_EPI = 16;                                            // epilogue warps: four per tensor-memory subpartition
 constexpr int LG_NT = (2 + LG_EPI) * 32;
 constexpr int LG_A_BYTES = LG_BM * LG_BK * 2, LG_B_BYTES = LG_BN * LG_BK * 2, LG_STAGE = LG_A_BYTES + LG_B_BYTES;
-constexpr int LG_SMEM = LG_STAGES * LG_STAGE + 1024 + 1024;           // stages, barriers, alignment slack
+constexpr int LG_OUT_BYTES = 32 * 64;                                 // per epilogue warp: 32 rows x 32 bf16 columns, staged for coalesced stores
+constexpr int LG_SMEM = LG_STAGES * LG_STAGE + 1024 + LG_EPI * LG_OUT_BYTES + 1024;   // stages, barriers, output staging, alignment slack
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
@@ -28,17 +32,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
 __device__ __forceinline__ void lg_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// erf by Abramowitz & Stegun 7.1.26 (|error| <= 1.5e-7, far below the bf16 rounding of the result) on the hardware
-// reciprocal and exp2: about a dozen instructions against the library routine's twenty-odd; the epilogue is ALU-bound.
-__device__ __forceinline__ float lg_erf(float x) {
-    const float ax = fabsf(x);
-    const float t = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
-    float p = fmaf(1.061405429f, t, -1.453152027f);
-    p = fmaf(p, t, 1.421413741f);
-    p = fmaf(p, t, -0.284496736f);
-    p = fmaf(p, t, 0.254829592f);
-    const float e = fast_exp2(-1.4426950408889634f * ax * ax);
-    return copysignf(fmaf(-p * t, e, 1.0f), x);
+// GELU(x) = x Phi(x) with Phi(x) = 0.5 (1 + erf(x / sqrt 2)) written as a logistic function of an odd polynomial,
+// Phi(x) ~= 1 / (1 + exp(-2 x p(x^2))): p fitted (minimax, |x| <= 6, beyond which Phi is 0 or 1 to 1e-9) so that the result
+// is within 3.3e-5 of the erf form everywhere -- a sixtieth of the bf16 rounding of a value near 1. The logistic form has
+// no cancellation in either tail (1 + tanh would), and costs a dozen instructions with two special-function issues
+// against about twenty for an erf polynomial.
+__device__ __forceinline__ float lg_gelu(float x) {
+    const float z = fminf(fmaxf(x, -6.0f), 6.0f), z2 = z * z;
+    float p = fmaf(-1.6031776e-05f, z2, -1.6010797e-04f);
+    p = fmaf(p, z2, 3.6451768e-02f);
+    p = fmaf(p, z2, 7.9785311e-01f);
+    const float e = fast_exp2(z * p * -2.8853900817779268f);         // exp(-2 z p(z^2))
+    return __fdividef(x, 1.0f + e);
 }
 __device__ __forceinline__ bool elect_one() {
     uint32_t e;
@@ -121,49 +126,57 @@ __global__ void __launch_bounds__(LG_NT, 1) linear_gelu_kernel(const __grid_cons
         }
     } else {
         // ------------------------------------------------------------------------------------------ epilogue
-        constexpr int CW = LG_BN / (LG_EPI / 4);                       // columns per warp
+        constexpr int CW = LG_BN / (LG_EPI / 4);                       // columns per warp: 64
+        static_assert(CW == 64, "one packed bias pair per lane covers 64 columns");
         const int sub = warp & 3, part = (warp - 2) >> 2;
         const uint32_t lane_base = (uint32_t)(32 * sub) << 16;
+        uint8_t *stage_out = sm + LG_STAGES * LG_STAGE + 1024 + (warp - 2) * LG_OUT_BYTES;
         uint32_t ti = 0;
         bool ok = true;
         for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++ti) {
             const uint32_t a = ti & 1;
-            const long long row = (t / tiles_n) * LG_BM + 32 * sub + lane;
+            const long long row0 = (t / tiles_n) * LG_BM + 32 * sub;
             const int n0 = (int)(t % tiles_n) * LG_BN + part * CW;
+            // this warp's 64 bias values, two per lane, requested before the accumulator is waited for
+            uint32_t bias2 = 0u;
+            if (bias != nullptr && n0 + 2 * lane < N) bias2 = *reinterpret_cast<const uint32_t *>(bias + n0 + 2 * lane);
             ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full(a), (ti >> 1) & 1, 74));
             if (!ok) break;
             tc_fence_after();
-#pragma unroll 1
-            for (int c = 0; c < CW; c += 32) {
-                float v[32];
-                tmem_ld32(tmem + lane_base + a * LG_BN + part * CW + c, v);
+            float v[2][32];
+            tmem_ld32_nowait(tmem + lane_base + a * LG_BN + part * CW, v[0]);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
                 tmem_ld_wait();
-                const int col = n0 + c;
+                if (h == 0) tmem_ld32_nowait(tmem + lane_base + a * LG_BN + part * CW + 32, v[1]);   // lands under the arithmetic below
+                const int col = n0 + 32 * h;
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {                          // 8 columns = one 16-byte store
-                    if (col + 8 * g < N) {
-                        float bv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                        if (bias != nullptr) {
-                            const uint4 braw = __ldg(reinterpret_cast<const uint4 *>(bias + col + 8 * g));
-                            const __nv_bfloat162 *b2 = reinterpret_cast<const __nv_bfloat162 *>(&braw);
+                    uint4 outv;
+                    __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(&outv);
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(b2[i]); bv[2 * i] = f.x; bv[2 * i + 1] = f.y; }
-                        }
-                        uint4 outv;
-                        __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(&outv);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            float x0 = __bfloat162float(__float2bfloat16_rn(v[8 * g + 2 * i] + bv[2 * i]));
-                            float x1 = __bfloat162float(__float2bfloat16_rn(v[8 * g + 2 * i + 1] + bv[2 * i + 1]));
-                            if (act == 1) {
-                                x0 = 0.5f * x0 * (1.0f + lg_erf(x0 * 0.70710678118654752f));
-                                x1 = 0.5f * x1 * (1.0f + lg_erf(x1 * 0.70710678118654752f));
-                            }
-                            o2[i] = __floats2bfloat162_rn(x0, x1);
-                        }
-                        if (row < M) *reinterpret_cast<uint4 *>(y + (size_t)row * N + col + 8 * g) = outv;
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t braw = __shfl_sync(0xffffffffu, bias2, 16 * h + 4 * g + i);
+                        const float2 bv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&braw));
+                        // the pre-activation, rounded to bf16 as the separate Linear would hand it on
+                        const float2 x = __bfloat1622float2(__floats2bfloat162_rn(v[h][8 * g + 2 * i] + bv.x, v[h][8 * g + 2 * i + 1] + bv.y));
+                        o2[i] = act == 1 ? __floats2bfloat162_rn(lg_gelu(x.x), lg_gelu(x.y)) : __floats2bfloat162_rn(x.x, x.y);
                     }
+                    // into the warp's staging block: row = lane, 16-byte piece g, pieces rotated by the row so that both this
+                    // write and the read-back below touch every bank once per 128 bytes
+                    *reinterpret_cast<uint4 *>(stage_out + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = outv;
                 }
+                __syncwarp();
+                // the block leaves as whole 64-byte row segments, eight rows per store instruction: a thread-per-row store
+                // would touch 32 lines per instruction and the load/store unit, not memory, would set the epilogue's pace
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int r = 8 * i + (lane >> 2), pc = lane & 3;
+                    const uint4 val = *reinterpret_cast<const uint4 *>(stage_out + r * 64 + ((pc ^ ((r >> 1) & 3)) << 4));
+                    const long long grow = row0 + r;
+                    if (grow < M && col + 8 * pc < N) *reinterpret_cast<uint4 *>(y + (size_t)grow * N + col + 8 * pc) = val;
+                }
+                __syncwarp();
             }
             tc_fence_before();
             __syncwarp();

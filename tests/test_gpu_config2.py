@@ -60,7 +60,7 @@ def test_config2_teacher_forced_decode(lm, B, rows):
         # about 2e-2 of the largest logit apart (summation order decides each rounding); the fp32 states agree more closely
         e = rel_err(lg[rows].float().cpu(), ref_lg)
         es0, es11 = rel_err(dec.states[0][0][rows].cpu(), ref_S0), rel_err(dec.states[11][0][rows].cpu(), ref_S11)
-        assert e <= 3e-2 and es0 <= 2e-3 and es11 <= 1e-2, (B, use_graph, e, es0, es11)
+        assert e <= 3e-2 and es0 <= 2e-3 and es11 <= 2e-2, (B, use_graph, e, es0, es11)
         # the decode steps alone, relative to the prompt's own error: a step adds no visible error of its own
         step_err = [rel_err(lg[rows, i].float().cpu(), ref_lg[:, i]) for i in range(STEPS + 1)]
         assert max(step_err[1:]) <= 2.5 * max(step_err[0], 2e-3), step_err
