@@ -302,6 +302,36 @@ int pgb_decode_sample_ex(const void *logits, int dtype, float temp, float min_p,
                          int B, int V, int ctx, void *stream);
 
 /* ---------------------------------------------------------------------------------------------------------
+ * One decode step of the whole language model -- embedding, every layer (norm + fused projection, recurrent state step,
+ * output projection, norm + MLP), final norm, tied head -- as ONE cooperative launch of one CTA per SM, for 1..4 sequences
+ * in bf16 with fp32 states updated in place. Replaces, for one token, the layer loop of src/model.py:859-884 over
+ * src/assoc.py:384-512 (T = 1) and src/model.py:552-560 that the reference replays as a CUDA graph of about a thousand
+ * launches (src/bench.py:242-317). Arithmetic and roundings are those of pgb_decode_embed, pgb_skinny_linear and
+ * pgb_aspin_decode_step chained five launches a layer.
+ *
+ *   layer_table  [L][18] 64-bit words on the device, per layer: pointers Wc [NP][d] (rows q | k | v | decay | gate, padded),
+ *                bc [NP], ln weight, ln bias (0 for RMS), Wo' [d][d] (output weight times sigmoid(gate)), MLP norm weight,
+ *                MLP norm bias (0 for RMS), Wa [dff][d], ba [dff], Wb [d][dff], bb [d] (all bf16), theta [H][D/2], A [H],
+ *                per-head RMS weight [D] (fp32), S [B][H][D][D] (fp32, in place); then word 15 = the two norm kinds as
+ *                int32 (low: layer norm in front of the mixer, high: in front of the MLP; 1 = RMS, 2 = layer norm), word 16 =
+ *                their epsilons as fp32 (same order), word 17 = the per-head RMS norm's epsilon as fp32 in its low half.
+ *   E [V][d], P [ctx][d] bf16 (E is also the head); tok [B], pos [1] int64 and shift [1] fp32 on the device as for
+ *   pgb_decode_embed / pgb_aspin_decode_step (shift_dev); logits [B][V] fp32 out (bf16-rounded values).
+ *   work: pgb_decode_token_work_bytes(B, d, NP, dff) bytes of scratch, 16-byte aligned.
+ *   sync: two 64-bit words, zero before the first launch and then left to the kernel (the grid barrier's counters); one
+ *         pair per stream of launches, never shared by two launches in flight.
+ *   B <= 4, D in {64, 128}, d = H * D, NP >= 3d + 2H, NP and dff multiples of 8; delta: 0 plain rule, 1 delta rule.
+ * Every barrier wait is bounded; a wait that runs out makes the whole grid return and pgb_tc_error_flag reads 81 (zero the
+ * sync words before the next launch).
+ * ------------------------------------------------------------------------------------------------------- */
+long long pgb_decode_token_work_bytes(int B, int d, int NP, int dff);
+int pgb_decode_token_fwd(const void *layer_table, int L, const void *E, const void *P, const void *final_norm_weight,
+                         const void *final_norm_bias, int final_norm_kind, float final_norm_eps, const long long *tok,
+                         const long long *pos, const float *shift, void *work, long long work_bytes, float *logits,
+                         unsigned long long *sync, int B, int d, int H, int D, int NP, int dff, int V, int ctx, int delta,
+                         void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
  * y = act(x W^T + bias) as one tcgen05 GEMM with the bias and the activation applied on the accumulator in the epilogue.
  * Replaces the Linear(d, 4d) + GELU pair of the MLP block (src/model.py:552-560) in the prefill pass, where the separate
  * activation is a second pass over the hidden tensor. bf16, fp32 accumulate; the pre-activation is rounded to bf16 first,

@@ -56,6 +56,11 @@ int skinny_linear_launch(const void *, const void *, const void *, const void *,
 int add_norm_launch(const void *, const void *, const void *, const void *, float, int, void *, void *, long long, int, int,
                     cudaStream_t);
 int rotate_launch(const void *, int, const float *, const float *, void *, int, int, int, int, cudaStream_t);
+int decode_token_launch(const void *, int, const void *, const void *, const void *, const void *, int, float, const long long *,
+                        const long long *, const float *, void *, float *, unsigned long long *, int, int, int, int, int, int, int, int,
+                        int, cudaStream_t);
+size_t decode_token_work_bytes(int B, int d, int NP, int dff);
+int decode_token_error_flag(int *);
 
 // PGB_PREFILL_AUTO sends bf16 plain-rule work to the tensor-core kernel only once this is on
 static const bool kAutoUsesTensor = true;
@@ -323,6 +328,33 @@ int pgb_decode_embed(const long long *tok, const long long *pos, const void *E, 
     return decode_embed_launch(tok, pos, E, P, x, B, d, vocab, ctx, (cudaStream_t)stream);
 }
 
+long long pgb_decode_token_work_bytes(int B, int d, int NP, int dff) {
+    if (B < 1 || d < 1 || NP < 1 || dff < 1) return 0;
+    return (long long)decode_token_work_bytes(B, d, NP, dff);
+}
+
+int pgb_decode_token_fwd(const void *layer_table, int L, const void *E, const void *P, const void *final_norm_weight,
+                         const void *final_norm_bias, int final_norm_kind, float final_norm_eps, const long long *tok,
+                         const long long *pos, const float *shift, void *work, long long work_bytes, float *logits,
+                         unsigned long long *sync, int B, int d, int H, int D, int NP, int dff, int V, int ctx, int delta,
+                         void *stream) {
+    if (!layer_table || !E || !P || !final_norm_weight || !tok || !pos || !shift || !work || !logits || !sync) return PGB_ERR_NULL_POINTER;
+    if (final_norm_kind != 1 && final_norm_kind != 2) return PGB_ERR_BAD_SHAPE;
+    if (final_norm_kind == 2 && !final_norm_bias) return PGB_ERR_NULL_POINTER;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    if (L < 1 || B < 1 || H < 1 || d != H * D || (dff % 8) != 0 || dff < 8 || (NP % 8) != 0 || NP < 3 * d + 2 * H || V < 1 || ctx < 1)
+        return PGB_ERR_BAD_SHAPE;
+    if (B > 4 || (long long)4 * (dff > d ? dff : d) * 2 + (long long)L * 144 > 120 * 1024) return PGB_ERR_TOO_LARGE;   // shared memory
+    if (work_bytes < pgb_decode_token_work_bytes(B, d, NP, dff)) return PGB_ERR_BAD_SHAPE;
+    if (!aligned(layer_table, 8) || !aligned(E, 16) || !aligned(P, 16) || !aligned(final_norm_weight, 16) ||
+        (final_norm_bias && !aligned(final_norm_bias, 16)) || !aligned(tok, 8) || !aligned(pos, 8) || !aligned(work, 16) ||
+        !aligned(logits, 4) || !aligned(sync, 16))
+        return PGB_ERR_MISALIGNED;
+    return decode_token_launch(layer_table, L, E, P, final_norm_weight, final_norm_bias, final_norm_kind, final_norm_eps, tok, pos,
+                               shift, work, logits, sync, B, d, H, D, NP, dff, V, ctx, delta ? 1 : 0,
+                               (cudaStream_t)stream);
+}
+
 int pgb_decode_sample(const void *logits, int dtype, float temp, unsigned long long seed, long long *tok, long long *hist,
                       int hist_cols, long long *count, long long *pos, float *shift, unsigned int *ticket, int B, int V, int ctx,
                       void *stream) {
@@ -403,8 +435,11 @@ int pgb_tc_error_flag(int *out_host) {
     if (rc == PGB_OK) rc = tc_ws_error_flag(&c);
     int d = 0;
     if (rc == PGB_OK) rc = linear_gelu_error_flag(&d);
+    int e = 0;
+    if (rc == PGB_OK) rc = decode_token_error_flag(&e);
     b = b > c ? b : c;
     b = b > d ? b : d;
+    b = b > e ? b : e;
     *out_host = a > b ? a : b;
     return rc;
 }

@@ -11,7 +11,10 @@
 //
 // The draw is the Gumbel-max form of categorical sampling, tok = argmax_v (logit_v / temp - log(-log u_v)), with u_v a
 // counter-based uniform (a 64-bit mix of seed, step count, sequence and vocabulary index): reproducible from the seed,
-// independent of launch geometry, and it needs no state.
+// independent of launch geometry, and it needs no state. With few rows a row is shared by a thread-block cluster of up
+// to eight CTAs (a single CTA walking 50k logits costs more than the rest of a small-batch step's kernels together).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace pgb {
@@ -48,8 +51,15 @@ __device__ __forceinline__ unsigned long long mix64(unsigned long long z) {     
     return z ^ (z >> 31);
 }
 
-constexpr int SAMPLE_NT = 256;
+constexpr int SAMPLE_NT = 512;
+constexpr int SAMPLE_MAX_SPLIT = 8;                                   // CTAs that share a row: one thread-block cluster
 
+__device__ __forceinline__ bool sample_better(float s, int v, float best, int arg) { return s > best || (s == best && v < arg); }
+
+// One row of logits per thread-block cluster: with few rows (decode at small batch) a row is split over the cluster's
+// CTAs, which combine their candidates through the first CTA's shared memory (distributed shared memory: no scratch in
+// global memory, no second launch). The draw does not depend on the split: the uniform of (row, id) is a function of the
+// seed, the step and the two indices only, and ties go to the smallest id.
 template <typename T_>
 __global__ void __launch_bounds__(SAMPLE_NT) decode_sample_kernel(const T_ *__restrict__ logits, float temp, float min_p, unsigned long long seed,
                                                                   long long *__restrict__ tok, long long *__restrict__ hist, int hist_cols,
@@ -58,38 +68,51 @@ __global__ void __launch_bounds__(SAMPLE_NT) decode_sample_kernel(const T_ *__re
                                                                   int V, int ctx) {
     pdl_wait();
     pdl_launch_dependents();
+    namespace cg = cooperative_groups;
+    cg::cluster_group cl = cg::this_cluster();
+    const int S = (int)cl.num_blocks(), rank = (int)cl.block_rank();
     __shared__ float sval[SAMPLE_NT / 32];
     __shared__ int sidx[SAMPLE_NT / 32];
-    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ float cmax[SAMPLE_MAX_SPLIT], cval[SAMPLE_MAX_SPLIT];   // the cluster's per-CTA results, gathered in CTA 0
+    __shared__ int cidx[SAMPLE_MAX_SPLIT];
+    const int b = blockIdx.x / S, rows = gridDim.x / S, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const long long step = count[0];
-    if (b == 0 && tid == 0 && step > 0) {                             // nobody in this kernel reads these two
+    if (blockIdx.x == 0 && tid == 0 && step > 0) {                    // nobody in this kernel reads these two
         if (pos != nullptr) pos[0] = (pos[0] + 1) % ctx;
         if (shift != nullptr) shift[0] = 1.0f;
     }
     const T_ *row = logits + (size_t)b * V;
     const float inv_t = temp > 0.f ? 1.0f / temp : 1.0f;
     const unsigned long long key = mix64(seed ^ mix64((unsigned long long)step * 0x100000001b3ull + (unsigned long long)b));
+    const int v0 = rank * SAMPLE_NT + tid, dv = S * SAMPLE_NT;
+    float *cmax0 = cl.map_shared_rank(cmax, 0), *cval0 = cl.map_shared_rank(cval, 0);
+    int *cidx0 = cl.map_shared_rank(cidx, 0);
     // min-p: p_v >= min_p * p_max  <=>  logit_v / temp >= max_w logit_w / temp + log(min_p); one extra pass for the maximum
     float floor_s = -INFINITY;
     if (temp > 0.f && min_p > 0.f) {
-        __shared__ float smax[SAMPLE_NT / 32];
         float m = -INFINITY;
-        for (int v = tid; v < V; v += SAMPLE_NT) {
+        for (int v = v0; v < V; v += dv) {
             float s;
             if constexpr (sizeof(T_) == 2) s = __bfloat162float(row[v]); else s = row[v];
             m = fmaxf(m, s * inv_t);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        if (lane == 0) smax[warp] = m;
+        if (lane == 0) sval[warp] = m;
         __syncthreads();
-        m = smax[0];
-        for (int w = 1; w < SAMPLE_NT / 32; ++w) m = fmaxf(m, smax[w]);
+        if (tid == 0) {
+            for (int w = 1; w < SAMPLE_NT / 32; ++w) m = fmaxf(m, sval[w]);
+            cmax0[rank] = m;
+        }
+        cl.sync();
+        m = cmax0[0];
+        for (int r = 1; r < S; ++r) m = fmaxf(m, cmax0[r]);
         floor_s = m + logf(min_p);
+        __syncthreads();                                              // sval is reused below
     }
     float best = -INFINITY;
     int arg = V;                                                      // ties go to the smallest index
-    for (int v = tid; v < V; v += SAMPLE_NT) {
+    for (int v = v0; v < V; v += dv) {
         float s;
         if constexpr (sizeof(T_) == 2) s = __bfloat162float(row[v]); else s = row[v];
         s *= inv_t;
@@ -99,28 +122,57 @@ __global__ void __launch_bounds__(SAMPLE_NT) decode_sample_kernel(const T_ *__re
             const float u = ((float)(r >> 40) + 0.5f) * (1.0f / 16777216.0f);          // (0, 1), 24 bits
             s -= logf(-logf(u));
         }
-        if (s > best || (s == best && v < arg)) { best = s; arg = v; }
+        if (sample_better(s, v, best, arg)) { best = s; arg = v; }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ob = __shfl_xor_sync(0xffffffffu, best, o);
         const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
-        if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        if (sample_better(ob, oa, best, arg)) { best = ob; arg = oa; }
     }
     if (lane == 0) { sval[warp] = best; sidx[warp] = arg; }
     __syncthreads();
     if (tid == 0) {
         for (int w = 1; w < SAMPLE_NT / 32; ++w)
-            if (sval[w] > best || (sval[w] == best && sidx[w] < arg)) { best = sval[w]; arg = sidx[w]; }
+            if (sample_better(sval[w], sidx[w], best, arg)) { best = sval[w]; arg = sidx[w]; }
+        cval0[rank] = best; cidx0[rank] = arg;
+    }
+    cl.sync();                                                        // every CTA's candidate is in CTA 0; nobody leaves before it is read
+    if (rank == 0 && tid == 0) {
+        best = cval[0]; arg = cidx[0];
+        for (int r = 1; r < S; ++r)
+            if (sample_better(cval[r], cidx[r], best, arg)) { best = cval[r]; arg = cidx[r]; }
         if (arg >= V) arg = 0;                                        // a row of NaNs: still a valid id
         tok[b] = arg;
         if (hist != nullptr && step >= 0 && step < hist_cols) hist[(size_t)b * hist_cols + step] = arg;
         __threadfence();
-        if (atomicAdd(ticket, 1u) == gridDim.x - 1) {                 // every row has read the count: advance it
+        if (atomicAdd(ticket, 1u) == (unsigned)rows - 1u) {           // every row has read the count: advance it
             count[0] = step + 1;
             *ticket = 0u;
         }
     }
+}
+
+// CTAs per row: as many as keep the whole launch within about two CTAs per SM, at most one portable cluster
+static int sample_split(int B, int V) {
+    int s = 1;
+    while (s < SAMPLE_MAX_SPLIT && B * s * 2 <= 256 && V >= s * 2 * SAMPLE_NT * 4) s *= 2;
+    return s;
+}
+
+template <typename T_>
+static cudaError_t sample_go(const T_ *logits, float temp, float min_p, unsigned long long seed, long long *tok, long long *hist, int hist_cols,
+                             long long *count, long long *pos, float *shift, unsigned int *ticket, int B, int V, int ctx, cudaStream_t stream) {
+    const int S = sample_split(B, V);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(B * S)); cfg.blockDim = dim3(SAMPLE_NT); cfg.dynamicSmemBytes = 0; cfg.stream = stream;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    at[1].id = cudaLaunchAttributeClusterDimension;
+    at[1].val.clusterDim.x = (unsigned)S; at[1].val.clusterDim.y = 1; at[1].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, decode_sample_kernel<T_>, logits, temp, min_p, seed, tok, hist, hist_cols, count, pos, shift, ticket, V, ctx);
 }
 
 int decode_embed_launch(const long long *tok, const long long *pos, const void *E, const void *P, void *x, int B, int d, int vocab,
@@ -136,11 +188,9 @@ int decode_sample_launch(const void *logits, int dtype, float temp, float min_p,
                          cudaStream_t stream) {
     cudaError_t e;
     if (dtype == PGB_BF16)
-        e = pdl_launch(decode_sample_kernel<__nv_bfloat16>, dim3((unsigned)B), dim3(SAMPLE_NT), 0, stream, (const __nv_bfloat16 *)logits,
-                       temp, min_p, seed, tok, hist, hist_cols, count, pos, shift, ticket, V, ctx);
+        e = sample_go((const __nv_bfloat16 *)logits, temp, min_p, seed, tok, hist, hist_cols, count, pos, shift, ticket, B, V, ctx, stream);
     else
-        e = pdl_launch(decode_sample_kernel<float>, dim3((unsigned)B), dim3(SAMPLE_NT), 0, stream, (const float *)logits, temp, min_p, seed,
-                       tok, hist, hist_cols, count, pos, shift, ticket, V, ctx);
+        e = sample_go((const float *)logits, temp, min_p, seed, tok, hist, hist_cols, count, pos, shift, ticket, B, V, ctx, stream);
     if (e != cudaSuccess) { set_cuda_error(e, "decode_sample launch"); return PGB_ERR_CUDA; }
     return check_launch("decode_sample_kernel");
 }

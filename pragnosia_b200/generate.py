@@ -9,6 +9,7 @@ from __future__ import annotations
 
 from typing import Optional
 
+import numpy as np
 import torch
 import torch.nn.functional as F
 
@@ -17,12 +18,15 @@ from .assoc import AssocCarrier
 
 
 class Decoder:
-    def __init__(self, model, batch: int, use_graph: bool = True, fused: bool = True, min_p: float = 0.0):
+    def __init__(self, model, batch: int, use_graph: bool = True, fused: bool = True, min_p: float = 0.0,
+                 token_kernel: bool = True):
         self.m = model.eval()
         self.min_p = float(min_p)                            # drop ids below min_p x the most likely one's probability (src/bench.py:38)
         self.B = batch
         self.use_graph = use_graph
         self.fused = fused                                   # small-batch bf16 step through the fused linear kernel
+        self.token_kernel = token_kernel                     # ... and, where it applies, the whole step as one launch
+        self._plan = None
         self.dev = next(model.parameters()).device
         self.w = model.ctx
         self.states = None
@@ -58,6 +62,8 @@ class Decoder:
             for old, cur in zip(self.states, new):
                 for a, b in zip(old, cur):
                     if torch.is_tensor(a): a.copy_(b)
+        if self._plan is not None:
+            self._plan["sync"].zero_()                       # a fresh pair of barrier counters (a step that gave up leaves them uneven)
         self.pos.fill_(pw)
         self.shift.fill_(float(n))                           # the last window's length (src/assoc.py:512 returns p0 + T)
         return F.linear(h[:, -1:], m.e.weight)[:, -1].float()
@@ -71,11 +77,65 @@ class Decoder:
         return (self.fused and self.B <= 4 and m.e.weight.dtype == torch.bfloat16 and m.d % 8 == 0 and
                 all(isinstance(mx, AssocCarrier) and mx.plain_step for mx in m.mix))
 
+    def _token_ok(self):
+        """The whole step as ONE cooperative launch (ops.decode_token): the fused path's conditions, one kind of mixer
+        throughout, an MLP width the 128-bit loads divide."""
+        m = self.m
+        if not (self.token_kernel and self._fused_ok()):
+            return False
+        mx0 = m.mix[0]
+        return (all(mx.delta == mx0.delta and mx.dk == mx0.dk and mx.h == mx0.h for mx in m.mix) and mx0.dk in (64, 128) and
+                all(mp.a.weight.shape[0] % 8 == 0 and mp.a.weight.shape == m.mlp[0].a.weight.shape for mp in m.mlp))
+
+    def _token_plan(self):
+        """The device-side table of per-layer pointers and norm settings the one-launch step reads, its scratch, barrier
+        counters and logits; rebuilt when the weights' stamp or a state's address changes."""
+        m = self.m
+        key = (self._stamp, tuple(st[0].data_ptr() for st in self.states))
+        if self._plan is not None and self._plan["key"] == key:
+            return self._plan
+        rows = np.zeros((m.layers, 18), dtype=np.int64)
+        i32, f32 = rows.view(np.int32), rows.view(np.float32)
+        keep = []                                            # every tensor whose address the table holds
+
+        def at(t):
+            if t is None:
+                return 0
+            c = t.detach().to(torch.bfloat16).contiguous(); keep.append(c)
+            return c.data_ptr()
+
+        for i, (mx, mp) in enumerate(zip(m.mix, m.mlp)):
+            c = mx._consts(); keep.append(c)
+            k1, w1, b1, e1 = ops._norm_args(mx.ln)
+            k2, w2, b2, e2 = ops._norm_args(mp.n)
+            rows[i, :15] = [c["W"].data_ptr(), c["b"].data_ptr(), at(w1), at(b1), c["ow"].data_ptr(), at(w2), at(b2),
+                            at(mp.a.weight), at(mp.a.bias), at(mp.b.weight), at(mp.b.bias), c["theta"].data_ptr(),
+                            c["A"].data_ptr(), c["onw"].data_ptr(), self.states[i][0].data_ptr()]
+            i32[i, 30], i32[i, 31] = k1, k2
+            f32[i, 32], f32[i, 33], f32[i, 34] = e1, e2, mx._rms_eps()
+        mx0, NP, dff = m.mix[0], m.mix[0]._consts()["W"].shape[0], m.mlp[0].a.weight.shape[0]
+        work = torch.empty(ops.decode_token_work_bytes(self.B, m.d, NP, dff) // 2, dtype=torch.bfloat16, device=self.dev)
+        self._plan = dict(key=key, keep=keep, table=torch.from_numpy(rows).to(self.dev), work=work, NP=NP, dff=dff,
+                          sync=torch.zeros(2, dtype=torch.int64, device=self.dev), H=mx0.h, D=mx0.dk, delta=bool(mx0.delta),
+                          logits=torch.empty(self.B, m.e.weight.shape[0], dtype=torch.float32, device=self.dev))
+        return self._plan
+
+    def _step_token(self, advance: bool = True, out: Optional[torch.Tensor] = None):
+        m, p = self.m, self._token_plan()
+        lg = ops.decode_token(p["table"], m.e.weight, m.p.weight, m.n, self.tok, self.pos, self.shift, p["work"],
+                              p["logits"] if out is None else out, p["sync"], p["H"], p["D"], p["NP"], p["dff"], p["delta"])
+        if advance:
+            self.shift.fill_(1.0)
+            self.pos.copy_((self.pos + 1) % self.w)
+        return lg
+
     @property
     def launches_per_token(self):
-        """Kernels in one token's graph: this library's on the fused path (draw, embedding, five per layer, head); on the
-        library-GEMM path the count includes the GEMMs and the copies around them."""
+        """Kernels in one token's graph: this library's on the one-launch path (draw, step) and on the fused path (draw,
+        embedding, five per layer, head); on the library-GEMM path the count includes the GEMMs and the copies around them."""
         L = self.m.layers
+        if self._token_ok():
+            return 2
         if self._fused_ok():
             return 1 + 1 + 5 * L + 1
         per_layer = 2 + 1 + 1 + 1 + 1 + 1 + 1            # two add+norm, projection, state step, output projection, MLP up (+GELU) and down
@@ -101,6 +161,8 @@ class Decoder:
         return ops.skinny_linear(x, m.e.weight, delta=delta, norm=m.n).float()
 
     def _step(self, advance: bool = True):
+        if self._token_ok():
+            return self._step_token(advance)
         if self._fused_ok():
             return self._step_fused(advance)
         m = self.m
@@ -176,7 +238,10 @@ class Decoder:
         being fed, so the draw kernel advances them for the PREVIOUS token (from the second token on) before the step."""
         ops.decode_sample(self._lg_in, temp, seed, self.tok, self._cnt, self._ticket, hist=self._hist, pos=self.pos,
                           shift=self.shift, ctx=self.w, min_p=self.min_p)
-        self._lg_in.copy_(self._step(advance=False))
+        if self._token_ok():
+            self._step_token(advance=False, out=self._lg_in)  # the step writes the waiting logits itself
+        else:
+            self._lg_in.copy_(self._step(advance=False))
 
     def _generate_graphed(self, lg, n: int, temp: float, seed: int):
         key = (n, float(temp), int(seed), self.min_p)

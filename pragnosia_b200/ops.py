@@ -472,6 +472,33 @@ def decode_embed(tok, pos, E, P):
 
 
 @on_device_of
+def decode_token(table, E, P, final_norm, tok, pos, shift, work, logits, sync, H, D, NP, dff, delta: bool):
+    """One decode step of the whole model in ONE cooperative launch (decode_token.cu): embedding, every layer, final norm
+    and tied head for 1..4 sequences. table (L,18) int64 on the device: the per-layer pointers and norm settings the C
+    header documents (generate.Decoder builds it); work / sync: scratch from decode_token_work_bytes and two zeroed
+    64-bit words; logits (B,V) fp32 out. The states the table points at are updated in place."""
+    need_cuda(table, E, P, tok, pos, shift, work, logits, sync)
+    if E.dtype != torch.bfloat16 or P.dtype != torch.bfloat16 or tok.dtype != torch.long or pos.dtype != torch.long:
+        raise ValueError("decode_token: bf16 tables, int64 ids")
+    if table.dtype != torch.int64 or table.dim() != 2 or table.shape[1] != 18 or not table.is_contiguous():
+        raise ValueError("decode_token: table must be a contiguous (L,18) int64 tensor")
+    if logits.dtype != torch.float32 or not logits.is_contiguous() or shift.dtype != torch.float32:
+        raise ValueError("decode_token: fp32 logits and shift")
+    kind, nw, nb, eps = _norm_args(final_norm)
+    if nw.dtype != torch.bfloat16 or (nb is not None and nb.dtype != torch.bfloat16):
+        raise ValueError("decode_token: bf16 norm parameters")
+    B, V, d = logits.shape[0], E.shape[0], E.shape[1]
+    check(lib().pgb_decode_token_fwd(ptr(table), table.shape[0], ptr(E), ptr(P), ptr(nw), ptr(nb), kind, float(eps), ptr(tok), ptr(pos),
+                                     ptr(shift), ptr(work), work.numel() * work.element_size(), ptr(logits), ptr(sync), B, d, H, D, NP,
+                                     dff, V, P.shape[0], 1 if delta else 0, stream_of(E)), "pgb_decode_token_fwd")
+    return logits
+
+
+def decode_token_work_bytes(B: int, d: int, NP: int, dff: int) -> int:
+    return int(lib().pgb_decode_token_work_bytes(B, d, NP, dff))
+
+
+@on_device_of
 def decode_sample(logits, temp, seed, tok, count, ticket, hist=None, pos=None, shift=None, ctx: int = 1, min_p: float = 0.0):
     """Draw one id per row of logits (B,V) into tok (B,) / (B,1) int64, record it in hist[:, count] and advance the step
     counters (count, pos modulo ctx, shift) -- all on the device, one launch. ticket: a zeroed uint32/int32 scalar.

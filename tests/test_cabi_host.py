@@ -132,3 +132,8 @@ def test_new_entry_points_reject_bad_calls(L):
     assert L.pgb_decode_sample_ex(one, 0, 1.0, 1.5, 0, one, None, 0, one, None, None, one, 1, 8, 1, None) == 2
     assert L.pgb_skinny_linear_ex(one, None, None, None, 0, 1e-5, one, None, 0, one, None, 1, 768, 16, 4, None) == 2
     assert L.pgb_aspin_prep_bwd_tiles(17) == 3
+    # the one-launch decode step: scratch size, then the rejects (bias missing for a layer norm, short scratch, batch, head dim)
+    assert L.pgb_decode_token_work_bytes(1, 768, 2328, 3072) == 2 * (4 * 768 + 2328 + 3072)
+    tok = lambda **kw: L.pgb_decode_token_fwd(one, 12, one, one, one, kw.get("nb", one), 2, 1e-5, one, one, one, one, kw.get("wb", 10 ** 6),
+                                              one, one, kw.get("B", 1), 768, 12, kw.get("D", 64), 2328, 3072, 50257, 512, 0, None)
+    assert tok(nb=None) == 1 and tok(wb=10) == 2 and tok(B=5) == 7 and tok(D=96) == 3
