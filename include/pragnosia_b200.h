@@ -325,6 +325,10 @@ int pgb_decode_sample_ex(const void *logits, int dtype, float temp, float min_p,
  * sync words before the next launch).
  * ------------------------------------------------------------------------------------------------------- */
 long long pgb_decode_token_work_bytes(int B, int d, int NP, int dff);
+/* Self-test of that kernel's failure path: one CTA arrives at a grid barrier nobody else will reach; after `limit_polls`
+ * polls (1 .. 2^20) its wait gives up, pgb_tc_error_flag reads 81 and the kernel returns normally -- nothing faults, traps
+ * or hangs. sync: two 64-bit words holding zero (zero them again afterwards). No counterpart in the reference. */
+int pgb_decode_token_wait_selftest(unsigned long long *sync, long long limit_polls, void *stream);
 int pgb_decode_token_fwd(const void *layer_table, int L, const void *E, const void *P, const void *final_norm_weight,
                          const void *final_norm_bias, int final_norm_kind, float final_norm_eps, const long long *tok,
                          const long long *pos, const float *shift, void *work, long long work_bytes, float *logits,

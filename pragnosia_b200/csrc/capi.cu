@@ -61,6 +61,7 @@ int decode_token_launch(const void *, int, const void *, const void *, const voi
                         int, cudaStream_t);
 size_t decode_token_work_bytes(int B, int d, int NP, int dff);
 int decode_token_error_flag(int *);
+int decode_token_wait_selftest_launch(unsigned long long *, unsigned, cudaStream_t);
 
 // PGB_PREFILL_AUTO sends bf16 plain-rule work to the tensor-core kernel only once this is on
 static const bool kAutoUsesTensor = true;
@@ -328,6 +329,13 @@ int pgb_decode_embed(const long long *tok, const long long *pos, const void *E, 
     return decode_embed_launch(tok, pos, E, P, x, B, d, vocab, ctx, (cudaStream_t)stream);
 }
 
+int pgb_decode_token_wait_selftest(unsigned long long *sync, long long limit_polls, void *stream) {
+    if (!sync) return PGB_ERR_NULL_POINTER;
+    if (limit_polls < 1 || limit_polls > (1ll << 20)) return PGB_ERR_BAD_SHAPE;          // at most about a second
+    if (!aligned(sync, 16)) return PGB_ERR_MISALIGNED;
+    return decode_token_wait_selftest_launch(sync, (unsigned)limit_polls, (cudaStream_t)stream);
+}
+
 long long pgb_decode_token_work_bytes(int B, int d, int NP, int dff) {
     if (B < 1 || d < 1 || NP < 1 || dff < 1) return 0;
     return (long long)decode_token_work_bytes(B, d, NP, dff);
@@ -344,7 +352,7 @@ int pgb_decode_token_fwd(const void *layer_table, int L, const void *E, const vo
     if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
     if (L < 1 || B < 1 || H < 1 || d != H * D || (dff % 8) != 0 || dff < 8 || (NP % 8) != 0 || NP < 3 * d + 2 * H || V < 1 || ctx < 1)
         return PGB_ERR_BAD_SHAPE;
-    if (B > 4 || (long long)4 * (dff > d ? dff : d) * 2 + (long long)L * 144 > 120 * 1024) return PGB_ERR_TOO_LARGE;   // shared memory
+    if (B > 4 || (long long)4 * (dff > d ? dff : d) * 2 + (long long)L * 144 > 72 * 1024) return PGB_ERR_TOO_LARGE;   // shared memory
     if (work_bytes < pgb_decode_token_work_bytes(B, d, NP, dff)) return PGB_ERR_BAD_SHAPE;
     if (!aligned(layer_table, 8) || !aligned(E, 16) || !aligned(P, 16) || !aligned(final_norm_weight, 16) ||
         (final_norm_bias && !aligned(final_norm_bias, 16)) || !aligned(tok, 8) || !aligned(pos, 8) || !aligned(work, 16) ||

@@ -83,7 +83,7 @@ __device__ __forceinline__ void dt_arrive(unsigned long long *sync) {
     // release: this CTA's writes (ordered before this by the CTA barrier above) are visible to whoever sees the count
     if (threadIdx.x == 0) asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(sync), "l"(1ull) : "memory");
 }
-__device__ __forceinline__ bool dt_wait(unsigned long long *sync, unsigned long long &gen) {
+__device__ __forceinline__ bool dt_wait(unsigned long long *sync, unsigned long long &gen, unsigned limit = DT_SPIN_LIMIT) {
     __shared__ int s_alive;
     if (threadIdx.x == 0) {
         int alive = 1;
@@ -94,7 +94,7 @@ __device__ __forceinline__ bool dt_wait(unsigned long long *sync, unsigned long 
             asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(sync) : "memory");
             if (c >= target) break;
             ++spins;
-            if (spins > DT_SPIN_LIMIT || ((spins & 63u) == 0u && *reinterpret_cast<volatile int *>(&g_dt_error) != 0)) {
+            if (spins > limit || ((spins & 63u) == 0u && *reinterpret_cast<volatile int *>(&g_dt_error) != 0)) {
                 atomicExch(&g_dt_error, 81);
                 alive = 0;
                 break;
@@ -255,17 +255,18 @@ template <int PENDING>
 __device__ __forceinline__ void dt_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
 
 constexpr int DT_PIECES = 12;                                         // 128-bit pieces of weights a lane has in flight per item
-constexpr int DT_STAGE_U4 = 2 * DT_PIECES * 32;                       // a warp's two staging buffers, in uint4
+constexpr int DT_DEPTH = 3;                                           // items a warp has in flight or in use
+constexpr int DT_STAGE_U4 = DT_DEPTH * DT_PIECES * 32;                // a warp's staging buffers, in uint4
 
 // One linear phase: out[b][n] = act(sum_k W[n][k] z[b][k] + bias[n]) with z the rows rw describes.
 //
 // Output rows go in groups of R consecutive rows, groups dealt round-robin to the grid's warps; a warp's work is a list of
 // items (group, chunk of 32 * U pieces of K), U = 12 / R, so a lane moves twelve 128-bit pieces per item. Weights travel
 // global -> shared memory by asynchronous copies into the warp's own two staging buffers (no registers held while they
-// fly; a lane reads back only what it copied itself). The first two items -- constants, nothing another CTA writes -- are
+// fly; a lane reads back only what it copied itself). The first three items -- constants, nothing another CTA writes -- are
 // requested between the two halves of the barrier that ends the previous phase (wait_first), so they travel from HBM
-// while the barrier completes; after it the rows are built from the previous phase's output, and a warp with more items (the head) keeps
-// two of them in flight while it multiplies a third. OUT: bf16, or fp32 holding the bf16-rounded value (the logits).
+// while the barrier completes; after it the rows are built from the previous phase's output, and a warp with more items
+// (the head) keeps two of them in flight while it multiplies a third. OUT: bf16, or fp32 holding the bf16-rounded value (the logits).
 // NB: rows of z the instantiation multiplies (>= the batch; the surplus is computed on whatever shared memory holds and
 // never written). False: the barrier gave up.
 template <typename OUT, int R, int NB>
@@ -277,12 +278,19 @@ __device__ __noinline__ bool dt_phase_rb(const DtArgs &a, const DtRows &rw, bool
     const int K = rw.K, K8 = K >> 3, nwarps = gridDim.x * DT_WARPS, groups = (N + R - 1) / R;
     const int nchunks = (K8 + 32 * U - 1) / (32 * U);
     const int first = blockIdx.x * DT_WARPS + warp;
-    const int items = first < groups ? ((groups - first + nwarps - 1) / nwarps) * nchunks : 0;
     uint4 *wb = wstage + warp * DT_STAGE_U4 + lane;
-    float bias_q[2] = {0.f, 0.f};                                     // of the output this lane will finish, requested with the weights
-    auto issue = [&](int item, int buf) {
-        const int n0 = (first + (item / nchunks) * nwarps) * R, k0 = (item % nchunks) * 32 * U;
-        if (bias != nullptr && lane < R * NB && n0 + lane / NB < N) bias_q[buf] = __bfloat162float(bias[n0 + lane / NB]);
+    float bias_q[DT_DEPTH] = {0.f, 0.f, 0.f};                                     // of the output this lane will finish, requested with the weights
+    // the items in order, walked by two cursors (requests ahead, multiplications behind) with no division in sight
+    int ig = first, ic = 0, issued = 0;                               // next item to request: group, chunk; items requested so far
+    auto issue = [&](int buf) {
+        const int n0 = ig * R, k0 = ic * 32 * U;
+        if (++ic == nchunks) { ic = 0; ig += nwarps; }
+        ++issued;
+        if (bias != nullptr && lane < R * NB && n0 + lane / NB < N) {
+            const float bv = __bfloat162float(bias[n0 + lane / NB]);
+#pragma unroll
+            for (int i = 0; i < DT_DEPTH; ++i) if (i == buf) bias_q[i] = bv;
+        }
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const uint4 *wr = reinterpret_cast<const uint4 *>(W + (size_t)(n0 + r < N ? n0 + r : N - 1) * K);
@@ -295,8 +303,9 @@ __device__ __noinline__ bool dt_phase_rb(const DtArgs &a, const DtRows &rw, bool
         dt_cp_async_commit();
     };
     if (wait_first) dt_arrive(a.sync);                                // the previous phase's results are out: tell the grid, then ...
-    if (items > 0) issue(0, 0);                                       // ... request weights while the other CTAs arrive
-    if (items > 1) issue(1, 1);
+#pragma unroll
+    for (int i = 0; i < DT_DEPTH; ++i)
+        if (ig < groups) issue(i);                                    // ... request weights while the other CTAs arrive
     if (wait_first && !dt_wait(a.sync, gen)) return false;
     dt_build_rows(a, rw, zs);
 
@@ -305,11 +314,13 @@ __device__ __noinline__ bool dt_phase_rb(const DtArgs &a, const DtRows &rw, bool
     for (int r = 0; r < R; ++r)
 #pragma unroll
         for (int b = 0; b < NB; ++b) acc[r][b] = 0.f;
-    for (int it = 0; it < items; ++it) {
-        const int buf = it & 1;
-        if (it + 1 < items) dt_cp_async_wait<1>(); else dt_cp_async_wait<0>();
-        const int n0 = (first + (it / nchunks) * nwarps) * R, ck = it % nchunks, k0 = ck * 32 * U;
-        const float my_bias = bias_q[buf];
+    int ck = 0, buf = 0;
+    for (int it = 0, cgp = first; cgp < groups; ++it, buf = (buf + 1 == DT_DEPTH ? 0 : buf + 1)) {
+        if (it + 2 < issued) dt_cp_async_wait<2>(); else if (it + 1 < issued) dt_cp_async_wait<1>(); else dt_cp_async_wait<0>();
+        const int n0 = cgp * R, k0 = ck * 32 * U;
+        float my_bias = 0.f;
+#pragma unroll
+        for (int i = 0; i < DT_DEPTH; ++i) if (i == buf) my_bias = bias_q[i];
         auto piece = [&](int u, int k8) {
             float w[R][8];
 #pragma unroll
@@ -337,8 +348,9 @@ __device__ __noinline__ bool dt_phase_rb(const DtArgs &a, const DtRows &rw, bool
                 piece(u, k0 + lane + 32 * u);
             }
         }
-        if (it + 2 < items) issue(it + 2, buf);                       // this lane's slots of the buffer are free again
-        if (ck == nchunks - 1) {
+        if (ig < groups) issue(buf);                                  // this lane's slots of the buffer are free again
+        if (++ck == nchunks) {
+            ck = 0; cgp += nwarps;
 #pragma unroll
             for (int r = 0; r < R; ++r)
 #pragma unroll
@@ -443,6 +455,20 @@ __global__ void __launch_bounds__(DT_THREADS, 1) decode_token_kernel(DtArgs a) {
     // ---- final norm and the tied head
     const DtRows rw{1, xcur, a.dl, nullptr, a.fn_kind, a.fn_eps, a.fn_w, a.fn_b, d};
     dt_phase<float, NB>(a, rw, true, gen, a.E, nullptr, a.V, false, a.logits, zs, wstage);
+}
+
+// The barrier's failure path on its own: one CTA arrives at a barrier of a "grid" that it alone will never complete
+// (the counter would have to reach twice the arrivals), so its wait runs out after `limit` polls, raises the flag and the
+// kernel returns normally.
+__global__ void __launch_bounds__(DT_THREADS) decode_token_wait_selftest_kernel(unsigned long long *sync, unsigned limit) {
+    unsigned long long gen = 1;                                       // as if one barrier had completed: the target is 2 arrivals, one comes
+    dt_arrive(sync);
+    dt_wait(sync, gen, limit);
+}
+
+int decode_token_wait_selftest_launch(unsigned long long *sync, unsigned limit, cudaStream_t stream) {
+    decode_token_wait_selftest_kernel<<<1, DT_THREADS, 0, stream>>>(sync, limit);
+    return check_launch("decode_token_wait_selftest_kernel");
 }
 
 int decode_token_error_flag(int *out) {

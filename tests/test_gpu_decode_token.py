@@ -73,3 +73,17 @@ def test_changed_weights_retire_the_table():
     ref = Decoder(m, batch=1, token_kernel=False); ref.prefill(prompt)
     close(lg1, ref.step(prompt[:, -1]), 2e-2, "after the update")
     assert not torch.equal(lg0, lg1)
+
+
+def test_a_barrier_wait_that_runs_out_raises_the_flag_and_returns():
+    """The grid barrier's failure path without a fault: one CTA waits, with a short limit, for arrivals that never come."""
+    import ctypes
+    assert healthy() == 0
+    sync = torch.zeros(2, dtype=torch.int64, device=DEV)
+    rc = _lib.lib().pgb_decode_token_wait_selftest(ctypes.c_void_p(sync.data_ptr()), 2000, None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert sync[0].item() == 1                                        # it did arrive
+    assert healthy() == 81 and healthy() == 0                         # reported once, then clear
+    x = torch.ones(8, device=DEV)                                     # the context is still usable
+    assert (x + 1).sum().item() == 16
