@@ -302,6 +302,31 @@ int pgb_decode_sample_ex(const void *logits, int dtype, float temp, float min_p,
                          int B, int V, int ctx, void *stream);
 
 /* ---------------------------------------------------------------------------------------------------------
+ * y = act(x W^T + bias) for a batch of decode rows (one token per sequence, up to 128 sequences) as one tcgen05 launch: the
+ * rows of x are one 128-row tile, a CTA owns 16 / 32 / 64 rows of W and streams them once by TMA (requested before the wait
+ * on the kernel that produces x), bias and erf-GELU on the accumulator. Replaces, for T = 1 and batches too large for
+ * pgb_skinny_linear, the F.linear (+ GELU) calls of src/assoc.py:384-512 and src/model.py:552-560. bf16, fp32 accumulate;
+ * the pre-activation is rounded to bf16 first, as the separate Linear would.
+ *   x [B][K], W [N][K] (torch.nn.Linear layout), bias [N] or NULL, y [B][N]; act 0: none, 1: GELU (erf).
+ *   B <= 128; N and K multiples of 8; x, W, y, bias 16-byte aligned. Bounded waits (pgb_tc_error_flag).
+ * ------------------------------------------------------------------------------------------------------- */
+int pgb_batch_linear(const void *x, const void *W, const void *bias, void *y, int B, int N, int K, int act, void *stream);
+/* The same launch taking over the add + norm kernels on either side of the layer (every extra argument optional):
+ *   folded norm (norm_kind 1 RMS / 2 layer norm): x is the raw residual stream and W already carries the norm's weight,
+ *     W'[n][k] = W[n][k] w[k]; with c1[n] = sum_k W'[n][k] and c2[n] = sum_k beta[k] W[n][k] + b[n] (fp32 [N], bias must be
+ *     NULL) the epilogue forms r (acc - mu c1) + c2 from the row's mean mu and r = 1 / sqrt(var + eps), both taken from the
+ *     partial row sums (sum, sum of squares) row_sums_in [parts_in][B][2] that the kernel producing x left behind;
+ *   residual (resid [B][N] bf16): y = resid + act(x W^T + b) with the separate ops' roundings, i.e. the new residual
+ *     stream, and row_sums_out [pgb_batch_linear_parts(N)][B][2] receives each CTA's partial row sums of y.
+ * pgb_decode_embed_ex writes the row sums of the embedding (one part) for the first layer's folded norm. */
+int pgb_batch_linear_ex(const void *x, const void *W, const void *bias, void *y, int B, int N, int K, int act, const float *row_sums_in,
+                        int parts_in, const float *c1, const float *c2, int norm_kind, float eps, const void *resid, float *row_sums_out,
+                        void *stream);
+int pgb_batch_linear_parts(int N);
+int pgb_decode_embed_ex(const long long *tok, const long long *pos, const void *E, const void *P, void *x, float *row_sums, int B, int d,
+                        int vocab, int ctx, void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
  * One decode step of the whole language model -- embedding, every layer (norm + fused projection, recurrent state step,
  * output projection, norm + MLP), final norm, tied head -- as ONE cooperative launch of one CTA per SM, for 1..4 sequences
  * in bf16 with fp32 states updated in place. Replaces, for one token, the layer loop of src/model.py:859-884 over

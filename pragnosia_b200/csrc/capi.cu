@@ -46,7 +46,7 @@ int prefill_tc_delta_launch(const PrefillArgs &, int, int, void *, cudaStream_t)
 int prefill_tc_delta_static_launch(const PrefillArgs &, int, int, cudaStream_t);
 long long prefill_tc_delta_static_capacity();
 int rot_table_launch(const float *, float *, int, int, int, cudaStream_t);
-int decode_embed_launch(const long long *, const long long *, const void *, const void *, void *, int, int, int, int, cudaStream_t);
+int decode_embed_launch(const long long *, const long long *, const void *, const void *, void *, int, int, int, int, float *, cudaStream_t);
 int decode_sample_launch(const void *, int, float, float, unsigned long long, long long *, long long *, int, long long *, long long *, float *,
                          unsigned int *, int, int, int, cudaStream_t);
 int linear_gelu_launch(const void *, const void *, const void *, void *, long long, int, int, int, cudaStream_t);
@@ -61,6 +61,10 @@ int decode_token_launch(const void *, int, const void *, const void *, const voi
                         int, cudaStream_t);
 size_t decode_token_work_bytes(int B, int d, int NP, int dff);
 int decode_token_error_flag(int *);
+int batch_linear_launch(const void *, const void *, const void *, void *, int, int, int, int, const float *, int, const float *, const float *,
+                        int, float, const void *, float *, cudaStream_t);
+int batch_linear_parts(int N);
+int batch_linear_error_flag(int *);
 int decode_token_wait_selftest_launch(unsigned long long *, unsigned, cudaStream_t);
 
 // PGB_PREFILL_AUTO sends bf16 plain-rule work to the tensor-core kernel only once this is on
@@ -321,12 +325,18 @@ int pgb_aspin_delta_prefill_noscratch_fwd(const void *q, const void *k, const vo
     return prefill_tc_delta_static_launch(a, o_dtype, D, (cudaStream_t)stream);
 }
 
-int pgb_decode_embed(const long long *tok, const long long *pos, const void *E, const void *P, void *x, int B, int d, int vocab,
-                     int ctx, void *stream) {
+int pgb_decode_embed_ex(const long long *tok, const long long *pos, const void *E, const void *P, void *x, float *row_sums, int B, int d,
+                        int vocab, int ctx, void *stream) {
     if (!tok || !pos || !E || !P || !x) return PGB_ERR_NULL_POINTER;
     if (B < 1 || d < 8 || (d % 8) != 0 || vocab < 1 || ctx < 1) return PGB_ERR_BAD_SHAPE;
-    if (!aligned(E, 16) || !aligned(P, 16) || !aligned(x, 16) || !aligned(tok, 8) || !aligned(pos, 8)) return PGB_ERR_MISALIGNED;
-    return decode_embed_launch(tok, pos, E, P, x, B, d, vocab, ctx, (cudaStream_t)stream);
+    if (!aligned(E, 16) || !aligned(P, 16) || !aligned(x, 16) || !aligned(tok, 8) || !aligned(pos, 8) || (row_sums && !aligned(row_sums, 8)))
+        return PGB_ERR_MISALIGNED;
+    return decode_embed_launch(tok, pos, E, P, x, B, d, vocab, ctx, row_sums, (cudaStream_t)stream);
+}
+
+int pgb_decode_embed(const long long *tok, const long long *pos, const void *E, const void *P, void *x, int B, int d, int vocab,
+                     int ctx, void *stream) {
+    return pgb_decode_embed_ex(tok, pos, E, P, x, nullptr, B, d, vocab, ctx, stream);
 }
 
 int pgb_decode_token_wait_selftest(unsigned long long *sync, long long limit_polls, void *stream) {
@@ -389,6 +399,28 @@ int pgb_linear_act(const void *x, const void *W, const void *bias, void *y, long
     return linear_gelu_launch(x, W, bias, y, M, N, K, act, (cudaStream_t)stream);
 }
 
+int pgb_batch_linear_ex(const void *x, const void *W, const void *bias, void *y, int B, int N, int K, int act, const float *row_sums_in,
+                        int parts_in, const float *c1, const float *c2, int norm_kind, float eps, const void *resid, float *row_sums_out,
+                        void *stream) {
+    if (!x || !W || !y) return PGB_ERR_NULL_POINTER;
+    if (act < 0 || act > 1 || B < 1 || N < 8 || K < 8 || (N % 8) != 0 || (K % 8) != 0) return PGB_ERR_BAD_SHAPE;
+    if (norm_kind < 0 || norm_kind > 2 || parts_in < 0) return PGB_ERR_BAD_SHAPE;
+    if (norm_kind != 0 && (!row_sums_in || !c1 || !c2 || parts_in < 1 || bias)) return PGB_ERR_NULL_POINTER;   // the folded norm's c2 carries the bias
+    if (B > 128) return PGB_ERR_TOO_LARGE;                            // the batch is one 128-row tensor-core tile
+    if (!aligned(x, 16) || !aligned(W, 16) || !aligned(y, 16) || (bias && !aligned(bias, 16)) || (resid && !aligned(resid, 16)) ||
+        (c1 && !aligned(c1, 16)) || (c2 && !aligned(c2, 16)) || (row_sums_in && !aligned(row_sums_in, 8)) ||
+        (row_sums_out && !aligned(row_sums_out, 8)))
+        return PGB_ERR_MISALIGNED;
+    return batch_linear_launch(x, W, bias, y, B, N, K, act, row_sums_in, parts_in, c1, c2, norm_kind, eps, resid, row_sums_out,
+                               (cudaStream_t)stream);
+}
+
+int pgb_batch_linear(const void *x, const void *W, const void *bias, void *y, int B, int N, int K, int act, void *stream) {
+    return pgb_batch_linear_ex(x, W, bias, y, B, N, K, act, nullptr, 0, nullptr, nullptr, 0, 0.f, nullptr, nullptr, stream);
+}
+
+int pgb_batch_linear_parts(int N) { return N < 1 ? 0 : batch_linear_parts(N); }
+
 int pgb_skinny_linear_ex(const void *x, const void *delta, const void *norm_weight, const void *norm_bias, int norm_kind, float eps,
                          const void *W, const void *bias, int act, void *y, void *x_out, int B, int K, int N, int flags, void *stream) {
     if (!x || !W || !y) return PGB_ERR_NULL_POINTER;
@@ -443,8 +475,10 @@ int pgb_tc_error_flag(int *out_host) {
     if (rc == PGB_OK) rc = tc_ws_error_flag(&c);
     int d = 0;
     if (rc == PGB_OK) rc = linear_gelu_error_flag(&d);
-    int e = 0;
+    int e = 0, f = 0;
     if (rc == PGB_OK) rc = decode_token_error_flag(&e);
+    if (rc == PGB_OK) rc = batch_linear_error_flag(&f);
+    e = e > f ? e : f;
     b = b > c ? b : c;
     b = b > d ? b : d;
     b = b > e ? b : e;

@@ -21,9 +21,12 @@ namespace pgb {
 
 __global__ void __launch_bounds__(128) decode_embed_kernel(const long long *__restrict__ tok, const long long *__restrict__ pos,
                                                            const __nv_bfloat16 *__restrict__ E, const __nv_bfloat16 *__restrict__ P,
-                                                           __nv_bfloat16 *__restrict__ x, int d, int vocab, int ctx) {
+                                                           __nv_bfloat16 *__restrict__ x, int d, int vocab, int ctx,
+                                                           float *__restrict__ stats) {
     pdl_wait();
     pdl_launch_dependents();
+    __shared__ float red[2][4];
+    float s1 = 0.f, s2 = 0.f;                                         // sum and sum of squares of the row (for a norm folded into the next GEMM)
     const int b = blockIdx.x;
     long long t = tok[b], p = pos[0];
     t = t < 0 ? 0 : (t >= vocab ? vocab - 1 : t);                     // ids outside the table are clamped, never dereferenced
@@ -39,8 +42,18 @@ __global__ void __launch_bounds__(128) decode_embed_kernel(const long long *__re
         for (int j = 0; j < 4; ++j) {
             const float2 fa = __bfloat1622float2(a2[j]), fc = __bfloat1622float2(c2[j]);
             o2[j] = __floats2bfloat162_rn(fa.x + fc.x, fa.y + fc.y);
+            const float2 r = __bfloat1622float2(o2[j]);
+            s1 += r.x + r.y; s2 = fmaf(r.x, r.x, fmaf(r.y, r.y, s2));
         }
         xr[i] = o;
+    }
+    if (stats != nullptr) {                                           // blockDim.x = 128: four warps
+        s1 = warp_sum(s1); s2 = warp_sum(s2);
+        if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = s1; red[1][threadIdx.x >> 5] = s2; }
+        __syncthreads();
+        if (threadIdx.x == 0)
+            *reinterpret_cast<float2 *>(stats + 2 * b) = make_float2(red[0][0] + red[0][1] + red[0][2] + red[0][3],
+                                                                     red[1][0] + red[1][1] + red[1][2] + red[1][3]);
     }
 }
 
@@ -176,9 +189,9 @@ static cudaError_t sample_go(const T_ *logits, float temp, float min_p, unsigned
 }
 
 int decode_embed_launch(const long long *tok, const long long *pos, const void *E, const void *P, void *x, int B, int d, int vocab,
-                        int ctx, cudaStream_t stream) {
+                        int ctx, float *stats, cudaStream_t stream) {
     cudaError_t e = pdl_launch(decode_embed_kernel, dim3((unsigned)B), dim3(128), 0, stream, tok, pos, (const __nv_bfloat16 *)E,
-                               (const __nv_bfloat16 *)P, (__nv_bfloat16 *)x, d, vocab, ctx);
+                               (const __nv_bfloat16 *)P, (__nv_bfloat16 *)x, d, vocab, ctx, stats);
     if (e != cudaSuccess) { set_cuda_error(e, "decode_embed launch"); return PGB_ERR_CUDA; }
     return check_launch("decode_embed_kernel");
 }

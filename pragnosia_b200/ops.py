@@ -459,16 +459,63 @@ def skinny_linear(x, W, bias=None, delta=None, norm: Optional[torch.nn.Module] =
 
 
 @on_device_of
-def decode_embed(tok, pos, E, P):
-    """x (B,d) = E[tok] + P[pos] in one launch; tok (B,) / (B,1) int64 and pos (1,) int64 on the device, bf16 tables."""
+def batch_linear(x, W, bias=None, act: Optional[str] = None, folded=None, resid=None, want_sums: bool = False):
+    """y = act(x W^T + bias) for up to 128 decode rows in ONE tensor-core launch (bf16); x (B,K), W (N,K), act None or
+    "gelu" (erf). N and K multiples of 8.
+    folded = (row_sums (P,B,2) fp32, c1 (N,) fp32, c2 (N,) fp32, kind, eps): x is the raw residual stream and W carries the
+    norm's weight (fold_norm); the norm is applied on the accumulator. resid (B,N): returns resid + y, the new residual
+    stream, and with want_sums also its partial row sums (parts,B,2) for the next folded norm."""
+    need_cuda(x, W)
+    if x.dtype != torch.bfloat16 or W.dtype != torch.bfloat16 or x.dim() != 2:
+        raise ValueError("batch_linear: bf16, x (B,K)")
+    B, K = x.shape
+    N = W.shape[0]
+    x, W = x.contiguous(), W.contiguous()
+    b = None if bias is None else bias.to(x.dtype).contiguous()
+    y = torch.empty(B, N, device=x.device, dtype=x.dtype)
+    sums_in, parts_in, c1, c2, kind, eps = None, 0, None, None, 0, 0.0
+    if folded is not None:
+        sums_in, c1, c2, kind, eps = folded
+        parts_in = sums_in.shape[0]
+        if sums_in.dtype != torch.float32 or tuple(sums_in.shape[1:]) != (B, 2) or not sums_in.is_contiguous() or b is not None:
+            raise ValueError("batch_linear: row sums (parts,B,2) fp32, and no separate bias with a folded norm")
+    sums_out = None
+    if resid is not None:
+        resid = resid.contiguous()
+        if want_sums:
+            sums_out = torch.empty(int(lib().pgb_batch_linear_parts(N)), B, 2, device=x.device, dtype=torch.float32)
+    check(lib().pgb_batch_linear_ex(ptr(x), ptr(W), ptr(b), ptr(y), B, N, K, 1 if act == "gelu" else 0, ptr(sums_in), parts_in, ptr(c1),
+                                    ptr(c2), int(kind), float(eps), ptr(resid), ptr(sums_out), stream_of(x)), "pgb_batch_linear")
+    return (y, sums_out) if want_sums else y
+
+
+def fold_norm(norm: torch.nn.Module, W, bias=None):
+    """The constants that let a linear layer take the norm in front of it (batch_linear's folded form): W' = W diag(w) in
+    W's dtype, c1 = row sums of W' and c2 = W beta + bias in fp32. Returns (W', c1, c2, kind, eps)."""
+    kind, w, beta, eps = _norm_args(norm)
+    Wf = (W.float() * w.float()).to(W.dtype).contiguous()
+    c1 = Wf.float().sum(1).contiguous()
+    c2 = torch.zeros(W.shape[0], device=W.device, dtype=torch.float32)
+    if beta is not None:
+        c2 = c2 + W.float() @ beta.float()
+    if bias is not None:
+        c2 = c2 + bias.float()
+    return Wf, c1, c2.contiguous(), kind, eps
+
+
+@on_device_of
+def decode_embed(tok, pos, E, P, want_sums: bool = False):
+    """x (B,d) = E[tok] + P[pos] in one launch; tok (B,) / (B,1) int64 and pos (1,) int64 on the device, bf16 tables.
+    want_sums: also the rows' (sum, sum of squares) as (1,B,2) fp32, for a norm folded into the next linear layer."""
     need_cuda(tok, pos, E, P)
     if E.dtype != torch.bfloat16 or P.dtype != torch.bfloat16 or tok.dtype != torch.long or pos.dtype != torch.long:
         raise ValueError("decode_embed: bf16 tables, int64 ids")
     B, d = tok.numel(), E.shape[1]
     x = torch.empty(B, d, device=E.device, dtype=E.dtype)
-    check(lib().pgb_decode_embed(ptr(tok.contiguous()), ptr(pos), ptr(E.contiguous()), ptr(P.contiguous()), ptr(x), B, d,
-                                 E.shape[0], P.shape[0], stream_of(E)), "pgb_decode_embed")
-    return x
+    sums = torch.empty(1, B, 2, device=E.device, dtype=torch.float32) if want_sums else None
+    check(lib().pgb_decode_embed_ex(ptr(tok.contiguous()), ptr(pos), ptr(E.contiguous()), ptr(P.contiguous()), ptr(x), ptr(sums), B, d,
+                                    E.shape[0], P.shape[0], stream_of(E)), "pgb_decode_embed")
+    return (x, sums) if want_sums else x
 
 
 @on_device_of

@@ -41,15 +41,17 @@ def oracle_run(Pb, cfg, ids):
     return torch.stack(out, 1), states[0][0], states[11][0]
 
 
-@pytest.mark.parametrize("B,rows", [(1, [0]), (64, [3, 41])])
-def test_config2_teacher_forced_decode(lm, B, rows):
+@pytest.mark.parametrize("B,rows,folded", [(1, [0], False), (64, [3, 41], False), (64, [3, 41], True)])
+def test_config2_teacher_forced_decode(lm, B, rows, folded):
+    """folded: the batch-64 step through this library's tensor-core linear with the norms folded in (Decoder(folded=True)),
+    held to the same tolerances as the step built from the library's GEMMs."""
     m, Pb, cfg = lm
     ids = synth.token_ids(B, 512 + STEPS + 1, 8192, seed=70 + B)
     ref_lg, ref_S0, ref_S11 = oracle_run(Pb, cfg, ids[rows])
     got = {}
     for use_graph in (False, True):
-        dec = Decoder(m, batch=B, use_graph=use_graph)
-        assert dec._fused_ok() == (B <= 4)
+        dec = Decoder(m, batch=B, use_graph=use_graph, folded=folded)
+        assert dec._fused_ok() == (B <= 4) and dec._wide_ok() == folded
         lg = [dec.prefill(ids[:, :512].to(DEV))]
         for t in range(512, 512 + STEPS):
             lg.append(dec.step(ids[:, t].to(DEV)).clone())

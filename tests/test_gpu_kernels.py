@@ -484,3 +484,66 @@ def test_windowed_walks_equal_single_calls():
     assert rel_err(hw[0].cpu(), hf[0].cpu()) <= 1e-5 and rel_err(hw[1].cpu(), hf[1].cpu()) <= 1e-5
     got = sharded.run_windows(lambda w: u[:, w * 100:(w + 1) * 100].contiguous(), 3)
     assert torch.equal(torch.cat(got, 1), u)
+
+
+@pytest.mark.parametrize("B,K,N,bias,act", [(64, 768, 2328, True, None), (9, 768, 768, False, None), (128, 3072, 768, True, None),
+                                            (33, 768, 3072, True, "gelu"), (64, 768, 8192, False, None), (5, 128, 392, True, None),
+                                            (16, 200, 24, True, "gelu")])
+def test_batch_linear_tensor_core(B, K, N, bias, act):
+    """The decode step's linear layer for 5..128 rows as one tcgen05 launch, against the fp32 product of the same bf16
+    operands with the separate ops' roundings (bf16 pre-activation, erf-GELU, bf16)."""
+    g = torch.Generator().manual_seed(B * 7 + N)
+    x = torch.randn(B, K, generator=g).to(DEV).to(torch.bfloat16)
+    W = (torch.randn(N, K, generator=g) / K ** 0.5).to(DEV).to(torch.bfloat16)
+    b = (torch.randn(N, generator=g) * 0.3).to(DEV).to(torch.bfloat16) if bias else None
+    y = ops.batch_linear(x, W, b, act=act)
+    ref = x.float() @ W.float().t()
+    if bias:
+        ref = ref + b.float()
+    ref = ref.to(torch.bfloat16).float()
+    if act == "gelu":
+        ref = torch.nn.functional.gelu(ref).to(torch.bfloat16).float()
+    assert y.shape == (B, N) and y.dtype == torch.bfloat16
+    assert rel_err(y.float().cpu(), ref.cpu()) <= 4e-3
+    assert torch.equal(y, ops.batch_linear(x, W, b, act=act))           # run twice: bit-identical
+
+
+@pytest.mark.parametrize("norm_cls", [torch.nn.LayerNorm, torch.nn.RMSNorm])
+def test_batch_linear_folded_norm_and_residual(norm_cls):
+    """The linear layer that takes over the add + norm launches around it: the norm folded into the weight and applied on
+    the accumulator from row sums, the residual add and the next norm's row sums in the epilogue."""
+    g = torch.Generator().manual_seed(31)
+    B, K, N = 48, 768, 2328
+    stream = (torch.randn(B, K, generator=g) * 1.5 + 0.3).to(DEV).to(torch.bfloat16)
+    norm = norm_cls(K).to(DEV)
+    with torch.no_grad():
+        norm.weight.copy_(1.0 + 0.2 * torch.randn(K, generator=g).to(DEV))
+        if getattr(norm, "bias", None) is not None:
+            norm.bias.copy_(0.2 * torch.randn(K, generator=g).to(DEV))
+    norm = norm.to(torch.bfloat16)
+    W = (torch.randn(N, K, generator=g) / K ** 0.5).to(DEV).to(torch.bfloat16)
+    b = (torch.randn(N, generator=g) * 0.3).to(DEV).to(torch.bfloat16)
+    sums = torch.stack([stream.float().sum(1), (stream.float() ** 2).sum(1)], 1)[None].contiguous()
+    Wf, c1, c2, kind, eps = ops.fold_norm(norm, W, b)
+    out = ops.batch_linear(stream, Wf, act="gelu", folded=(sums, c1, c2, kind, eps))
+    ref = F.gelu(F.linear(norm.float()(stream.float()), W.float(), b.float()))
+    assert rel_err(out.float().cpu(), ref.cpu()) <= 8e-3                      # bf16 roundings of the weight and the output
+    # the sums may arrive in parts
+    parts = torch.stack([torch.stack([stream[:, i::3].float().sum(1), (stream[:, i::3].float() ** 2).sum(1)], 1) for i in range(3)]).contiguous()
+    out3 = ops.batch_linear(stream, Wf, act="gelu", folded=(parts, c1, c2, kind, eps))
+    assert rel_err(out3.float().cpu(), out.float().cpu()) <= 4e-3
+    # residual add and the row sums of the new stream
+    o = torch.randn(B, K, generator=g).to(DEV).to(torch.bfloat16)
+    Wo = (torch.randn(K, K, generator=g) / K ** 0.5).to(DEV).to(torch.bfloat16)
+    bo = (torch.randn(K, generator=g) * 0.1).to(DEV).to(torch.bfloat16)
+    new, psums = ops.batch_linear(o, Wo, bo, resid=stream, want_sums=True)
+    lin = F.linear(o.float(), Wo.float(), bo.float()).to(torch.bfloat16)
+    want = (stream.float() + lin.float()).to(torch.bfloat16)
+    assert rel_err(new.float().cpu(), want.float().cpu()) <= 4e-3
+    assert tuple(psums.shape) == (K // 16, B, 2)
+    tot = psums.sum(0)
+    assert torch.allclose(tot[:, 0].cpu(), new.float().sum(1).cpu(), rtol=1e-4, atol=1e-2)
+    assert torch.allclose(tot[:, 1].cpu(), (new.float() ** 2).sum(1).cpu(), rtol=1e-4, atol=1e-2)
+    xe, se = ops.decode_embed(torch.arange(B, device=DEV), torch.tensor([3], device=DEV), W[:64].contiguous(), W[100:120].contiguous(), want_sums=True)
+    assert torch.allclose(se[0, :, 0].cpu(), xe.float().sum(1).cpu(), rtol=1e-4, atol=1e-3)
+    assert torch.allclose(se[0, :, 1].cpu(), (xe.float() ** 2).sum(1).cpu(), rtol=1e-4, atol=1e-3)

@@ -175,3 +175,38 @@ def test_fused_small_batch_decode_matches_the_separate_ops(mixer, norm):
         close(lg, ref_lg, 3e-2, f"logits fused={key[0]} graph={key[1]}")
         close(S, ref_S, 3e-2, f"state fused={key[0]} graph={key[1]}")
     close(outs[(True, True)][0], outs[(True, False)][0], 1e-6, "fused: graph replay equals eager")
+
+
+@pytest.mark.parametrize("mixer,norm,B", [("aspin", "rms", 6), ("dspin", "ln", 16), ("hspin", "rms", 33)])
+def test_mid_batch_decode_through_the_tensor_core_linear(mixer, norm, B):
+    """Batches past the few-row kernels run every linear layer of the step as one tcgen05 launch with the norm in front
+    folded into the weight (ops.batch_linear). The folded form rounds at other places than the separate ops, so the two
+    runs are not compared with each other but each with the CPU oracle in fp32 arithmetic on the same bf16-rounded
+    weights (what both approximate): the folded step must be as close to it as the step built from the library's GEMMs,
+    eagerly and under the captured graph."""
+    m, P, cfg = small_lm(mixer, norm, torch.bfloat16)
+    Pb = {k: v.to(torch.bfloat16).float() for k, v in P.items()}
+    ids = synth.token_ids(B, 44, 256, seed=19)
+    lg0, states = oracle.lm_prefill(Pb, cfg, ids[:, :32])
+    ref = [lg0[:, -1]]
+    for t in range(32, 42):
+        ref.append(oracle.lm_decode_step(Pb, cfg, ids[:, t], t % 32, states))
+    ref = torch.stack(ref, 1)
+    err, outs = {}, {}
+    for fused in (False, True):
+        for use_graph in (False, True):
+            dec = Decoder(m, batch=B, use_graph=use_graph, folded=fused)
+            assert dec._wide_ok() == fused and not dec._fused_ok()
+            assert dec.launches_per_token == (1 + 1 + 5 * m.layers + 2 if fused else 1 + 3 + 8 * m.layers + 2 + 1)
+            lg = [dec.prefill(ids[:, :32].to(DEV))]
+            for t in range(32, 42):
+                lg.append(dec.step(ids[:, t].to(DEV)).clone())
+            outs[(fused, use_graph)] = torch.stack(lg, 1)
+            err[(fused, use_graph)] = (rel_err(outs[(fused, use_graph)].float().cpu(), ref),
+                                       rel_err(dec.states[1][0].cpu(), states[1][0]))
+    assert rel_err(outs[(True, True)], outs[(True, False)]) <= 1e-6                   # a graph replay is the eager step
+    for k in ((True, False), (True, True)):
+        # small random models amplify a rounding difference over ten steps; the full-size model is held to the oracle's own
+        # tolerances in test_gpu_config2
+        assert err[k][0] <= max(3e-2, 2.0 * err[(False, False)][0]), err
+        assert err[k][1] <= max(1e-2, 1.25 * err[(False, False)][1]), err
