@@ -106,6 +106,9 @@ CASES = {
     "add_norm": (lambda: _add_norm(8192, 768), "residual add + RMS norm: 8192 rows of 768 bf16"),
     "mlp_up": (lambda: _linear_act(8192, 768, 3072), "MLP up-projection + bias + erf-GELU as one tensor-core GEMM: M8192 K768 N3072 bf16"),
     "skinny": (lambda: _skinny(1, 768, 3072), "decode-step linear (add + RMS norm + linear + GELU) at batch 1: K768 N3072 bf16"),
+    "batch_linear": (lambda: _batch_linear(64, 768, 2328), "decode-step linear for 64 rows on the tensor cores (bias): K768 N2328 bf16"),
+    "decode_token": (lambda: _decode_token(1), "the whole decode step of the configuration-2 model as one launch, batch 1 (12 layers, d768, vocabulary 8192)"),
+    "decode_token_b4": (lambda: _decode_token(4), "the same at batch 4"),
 }
 
 # floating-point operations per launch of the cases that are bound by the tensor pipe rather than by HBM
@@ -127,6 +130,32 @@ def _skinny(B, K, N):
     b = torch.randn(N, device=dev).to(torch.bfloat16)
     norm = torch.nn.RMSNorm(K).to(dev).to(torch.bfloat16)
     return (lambda: ops.skinny_linear(x, W, b, delta=dl, norm=norm, act="gelu")), (N * K + N + 3 * B * K + B * N) * 2
+
+
+def _batch_linear(B, K, N):
+    dev = "cuda"
+    x = torch.randn(B, K, device=dev).to(torch.bfloat16)
+    W = (torch.randn(N, K, device=dev) * K ** -0.5).to(torch.bfloat16)
+    b = torch.randn(N, device=dev).to(torch.bfloat16)
+    return (lambda: ops.batch_linear(x, W, b)), (N * K + N + B * K + B * N) * 2
+
+
+def _decode_token(B):
+    """One token through Decoder._step_token: the launch reads every weight once (the embedding table as the head) and
+    reads and writes every layer's state."""
+    from .generate import Decoder
+    from .model import LM
+    dev = "cuda"
+    torch.manual_seed(0)
+    m = LM(vocab=8192, d=768, layers=12, mlp_mult=4, ctx=512, mixer="aspin", norm="rms").to(dev).to(torch.bfloat16).eval()
+    dec = Decoder(m, batch=B, use_graph=False)
+    with torch.no_grad():
+        dec.prefill(synth.token_ids(B, 64, 8192, seed=7).to(dev))
+    tok = torch.zeros(B, dtype=torch.long, device=dev)
+    assert dec._token_ok()
+    weights = sum(p.numel() for n, p in m.named_parameters() if not n.startswith("p.")) * 2
+    dec.tok.copy_(tok.view(B, 1))
+    return (lambda: dec._step_token(advance=False)), weights + 2 * B * 12 * 12 * 64 * 64 * 4
 
 
 def time_case(name: str, iters: int = 20, flush_mb: int = 256):
