@@ -47,6 +47,8 @@ class LM(nn.Module):
         if mixer not in _MIXERS:
             raise NotImplementedError(f"mixer {mixer!r}: only the pure-carrier mixers {sorted(_MIXERS)} are built here")
         self.vocab, self.d, self.layers, self.ctx, self.mixer, self.norm = vocab, d, layers, ctx, mixer, norm
+        self.wavefront = True                                # graphed forward_carried: consecutive windows a layer apart on separate streams
+        self.wavefront_streams = 4
         self.e = nn.Embedding(vocab, d)
         self.p = nn.Embedding(ctx, d)
         self.mix = nn.ModuleList([_MIXERS[mixer](d) for _ in range(layers)])
@@ -125,13 +127,22 @@ class LM(nn.Module):
             if stamp != self._graphs_stamp:
                 self._graphs.clear()
                 self._graphs_stamp = stamp
-            key = (B, window, x.device, self.e.weight.dtype)
-            run = self._graphs.get(key)
-            if run is None:
-                run = self._graphs[key] = _WindowGraphs(self, B, window, x.device)
-            last = None
-            for s in range(0, T, window):
-                last = run(x[:, s:s + window], first=(s == 0))
+            nw = T // window
+            if self.wavefront and nw >= 2 and all(isinstance(mx, AssocCarrier) for mx in self.mix):
+                # every window of the call in ONE graph, consecutive windows on two streams a layer apart
+                key = (B, window, nw, x.device, self.e.weight.dtype)
+                run = self._graphs.get(key)
+                if run is None:
+                    run = self._graphs[key] = _StepGraph(self, B, window, nw, x.device)
+                last = run(x)
+            else:
+                key = (B, window, x.device, self.e.weight.dtype)
+                run = self._graphs.get(key)
+                if run is None:
+                    run = self._graphs[key] = _WindowGraphs(self, B, window, x.device)
+                last = None
+                for s in range(0, T, window):
+                    last = run(x[:, s:s + window], first=(s == 0))
             states = run.states
         else:
             states = [None] * self.layers
@@ -140,6 +151,71 @@ class LM(nn.Module):
                 last = self._layers(self._embed(x[:, s:s + window]), states)
         logits = F.linear(self._add_norm(*last, self.n)[1], self.e.weight)
         return (logits, states) if return_states else logits
+
+
+class _StepGraph:
+    """ONE CUDA graph of a whole multi-window pass, with consecutive windows on separate streams. Window w + 1 needs from
+    window w only each layer's carried state, so it can run one layer behind it instead of after it: layer l of window
+    w + 1 waits for the event recorded after layer l of window w. The two windows' kernels then share the GPU -- the
+    half-empty second wave of one window's prefill kernel (192 one-per-SM CTAs on 148 SMs) is filled by the other
+    window's GEMM tiles. Same kernels in the same order along every dependency chain: results are those of the
+    window-by-window pass to the bit. The reference runs the windows one after the other, eagerly (src/model.py:857-863)."""
+
+    def __init__(self, model, B, Tw, NW, device):
+        self.m, self.B, self.Tw, self.NW = model, B, Tw, NW
+        self.ids = torch.zeros(B, Tw * NW, dtype=torch.long, device=device)
+        self.sides = [torch.cuda.Stream(device=device) for _ in range(min(NW, model.wavefront_streams) - 1)]
+        self.graph = None
+        self.states = None
+        self.out = None
+
+    def _pass(self):
+        m, main = self.m, torch.cuda.current_stream()
+        streams = [main] + self.sides
+        states = [None] * m.layers
+        fork = torch.cuda.Event(); fork.record(main)
+        for sd in self.sides:
+            sd.wait_event(fork)
+        prev, out = None, None
+        try:
+            for w in range(self.NW):
+                st = streams[w % len(streams)]
+                evs = [torch.cuda.Event() for _ in range(m.layers)]
+                for mx in m.mix:
+                    mx.inplace_state = w > 0                           # later windows update the first window's state tensors
+                with torch.cuda.stream(st):
+                    x, delta = m._embed(self.ids[:, w * self.Tw:(w + 1) * self.Tw]), None
+                    for i, (mx, mp) in enumerate(zip(m.mix, m.mlp)):
+                        x, z = m._add_norm(x, delta, mx.ln)
+                        if prev is not None:
+                            st.wait_event(prev[i])                     # the state this layer enters with
+                        delta, states[i] = mx.mix(z, states[i])
+                        evs[i].record(st)
+                        x, z = m._add_norm(x, delta, mp.n)
+                        delta = mp.ff(z)
+                    out = (x, delta)
+                prev = evs
+            for sd in self.sides:
+                join = torch.cuda.Event(); join.record(sd); main.wait_event(join)
+        finally:
+            for mx in m.mix:
+                mx.inplace_state = False
+        return out, states
+
+    def __call__(self, ids):
+        if self.graph is None:
+            warm = torch.cuda.Stream()
+            warm.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(warm):                              # warm-up: library workspaces, cached constants
+                self._pass()
+            torch.cuda.current_stream().wait_stream(warm)
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self.out, self.states = self._pass()
+        self.ids.copy_(ids)
+        self.graph.replay()
+        return self.out
 
 
 class _WindowGraphs:
