@@ -127,6 +127,16 @@ int pgb_assoc_out_fwd(const void *q, const void *k, const void *v, int io_dtype,
                       int H, int T, int D, void *stream);
 int pgb_prefix_scan_fwd(const void *k, const void *v, int io_dtype, const float *w, const float *a_log, const float *S0, void *sent,
                         float *sfin, int B, int H, int NC, int D, void *stream);
+/* Backward of the two plain-rule operators above (src/assoc_kernel.py:75-126 _bwd_chunk, :206-228 _prefix_bwd, wired with
+ * register_autograd at :179 and :299). Every gradient is fp32; sums are taken in a fixed order.
+ *   pgb_assoc_out_bwd:   dout [B][H][T][D] (io dtype) -> dq, dk, dv [B][H][T][D], dla [B][H][T], dsent [B][H][NC][D][D].
+ *   pgb_prefix_scan_bwd: dsent [B][H][NC][D][D] and dsfin [B][H][D][D] (either may be NULL = zero), sent = the forward's
+ *                        output -> dk, dv [B][H][NC*64][D], dw [B][H][NC][64], da_log [B][H][NC], dS0 [B][H][D][D] (or NULL). */
+int pgb_assoc_out_bwd(const void *q, const void *k, const void *v, int io_dtype, const float *la, const void *sent, const void *dout,
+                      float *dq, float *dk, float *dv, float *dla, float *dsent, int B, int H, int T, int D, void *stream);
+int pgb_prefix_scan_bwd(const void *k, const void *v, int io_dtype, const float *w, const float *a_log, const void *sent,
+                        const float *dsent, const float *dsfin, float *dk, float *dv, float *dw, float *da_log, float *dS0, int B, int H,
+                        int NC, int D, void *stream);
 int pgb_delta_inv_fwd(const void *k, const float *la, const float *beta, void *X, int B, int H, int T, int D, void *stream);
 int pgb_delta_loop_fwd(const void *k, const void *v, int io_dtype, const float *la, const float *beta, const void *X, const float *S0,
                        void *W, void *sent, float *sfin, int B, int H, int T, int D, void *stream);

@@ -27,6 +27,10 @@ int prefix_scan_launch(const void *, const void *, int, const float *, const flo
 int delta_loop_launch(const void *, const void *, int, const float *, const float *, const void *, const float *, void *, void *, float *,
                       int, int, int, cudaStream_t);
 int delta_inv_launch(const void *, const float *, const float *, void *, int, int, int, cudaStream_t);
+int assoc_out_bwd_launch(const void *, const void *, const void *, int, const float *, const void *, const void *, float *, float *, float *,
+                         float *, float *, int, int, int, cudaStream_t);
+int prefix_scan_bwd_launch(const void *, const void *, int, const float *, const float *, const void *, const float *, const float *, float *,
+                           float *, float *, float *, float *, int, int, int, cudaStream_t);
 int key_topk_launch(void *, int, long long, long long, long long, int, int, int, int, int, cudaStream_t);
 int short_conv_launch(const void *, int, long long, long long, const void *, const void *, void *, void *, int, int, int, int, cudaStream_t);
 int lambda_scan_pick_ts(int B, int T, int D, int vec, int sms, int force_ts);
@@ -180,6 +184,25 @@ int pgb_prefix_scan_fwd(const void *k, const void *v, int io_dtype, const float 
     if (B <= 0 || H <= 0 || NC <= 0 || (long long)B * H > 65535) return PGB_ERR_BAD_SHAPE;
     if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
     return prefix_scan_launch(k, v, io_dtype, w, a_log, S0, sent, sfin, B * H, NC, D, (cudaStream_t)stream);
+}
+
+int pgb_assoc_out_bwd(const void *q, const void *k, const void *v, int io_dtype, const float *la, const void *sent, const void *dout,
+                      float *dq, float *dk, float *dv, float *dla, float *dsent, int B, int H, int T, int D, void *stream) {
+    if (!q || !k || !v || !la || !sent || !dout || !dq || !dk || !dv || !dla || !dsent) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(io_dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || H <= 0 || T <= 0 || (long long)B * H > 65535) return PGB_ERR_BAD_SHAPE;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    return assoc_out_bwd_launch(q, k, v, io_dtype, la, sent, dout, dq, dk, dv, dla, dsent, B * H, T, D, (cudaStream_t)stream);
+}
+
+int pgb_prefix_scan_bwd(const void *k, const void *v, int io_dtype, const float *w, const float *a_log, const void *sent,
+                        const float *dsent, const float *dsfin, float *dk, float *dv, float *dw, float *da_log, float *dS0, int B, int H,
+                        int NC, int D, void *stream) {
+    if (!k || !v || !w || !a_log || !sent || !dk || !dv || !dw || !da_log) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(io_dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || H <= 0 || NC <= 0) return PGB_ERR_BAD_SHAPE;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    return prefix_scan_bwd_launch(k, v, io_dtype, w, a_log, sent, dsent, dsfin, dk, dv, dw, da_log, dS0, B * H, NC, D, (cudaStream_t)stream);
 }
 
 int pgb_delta_inv_fwd(const void *k, const float *la, const float *beta, void *X, int B, int H, int T, int D, void *stream) {

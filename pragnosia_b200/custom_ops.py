@@ -8,7 +8,8 @@ Two groups:
   * the fused operators this library adds -- aspin_prefill (one walk instead of three launches), aspin_prefill_fused,
     aspin_layer_prefill, aspin_decode_step, lambda_scan, rot_table, rotate, add_norm, linear_act.
 Every operator is functional (mutates_args=()): outputs are new tensors; an absent optional output is an empty tensor.
-Backward formulas are registered for lambda_scan (the adjoint scan) and assoc_prep.
+Backward formulas are registered for lambda_scan (the adjoint scan), assoc_prep, assoc_out and prefix_scan (the plain
+rule trains through the split operators).
 
 The operator bodies run eagerly and call pragnosia_b200.ops, which makes the one library call.
 """
@@ -168,6 +169,33 @@ def _(q, k, v, la, sent, bc):
     return torch.empty(q.shape, device=q.device, dtype=q.dtype if q.dtype in (_F32, _BF16) else _F32)
 
 
+@torch.library.custom_op(f"{NS}::assoc_out_bwd", mutates_args=())
+def assoc_out_bwd(q: Tensor, k: Tensor, v: Tensor, la: Tensor, sent: Tensor, dout: Tensor) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+    return ops.assoc_out_bwd(q, k, v, la, sent, dout)
+
+
+@assoc_out_bwd.register_fake
+def _(q, k, v, la, sent, dout):
+    B, H, T, D = q.shape
+    return (_e(q, B, H, T, D, dtype=_F32), _e(q, B, H, T, D, dtype=_F32), _e(q, B, H, T, D, dtype=_F32), _e(q, B, H, T, dtype=_F32),
+            _e(q, B, H, _nc(T), D, D, dtype=_F32))
+
+
+def _out_setup(ctx, inputs, output):
+    q, k, v, la, sent, bc = inputs
+    ctx.save_for_backward(q, k, v, la, sent)
+
+
+def _out_backward(ctx, dout):
+    """The reference's _bwd_chunk (src/assoc_kernel.py:75-126, wired at :179)."""
+    q, k, v, la, sent = ctx.saved_tensors
+    dq, dk, dv, dla, dsent = assoc_out_bwd(q, k, v, la, sent, dout.contiguous())
+    return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dla.to(la.dtype), dsent.to(sent.dtype), None
+
+
+assoc_out.register_autograd(_out_backward, setup_context=_out_setup)
+
+
 @torch.library.custom_op(f"{NS}::prefix_scan", mutates_args=())
 def prefix_scan(k: Tensor, v: Tensor, w: Tensor, a_log: Tensor, S0: Optional[Tensor], has_s0: bool, bv: int) -> Tuple[Tensor, Tensor]:
     return ops.prefix_scan(k, v, w, a_log, S0, has_s0, bv)
@@ -178,6 +206,40 @@ def _(k, v, w, a_log, S0, has_s0, bv):
     B, H, NC = w.shape[:3]
     D = k.shape[-1]
     return _e(k, B, H, NC, D, D, dtype=_BF16), _e(k, B, H, D, D, dtype=_F32)
+
+
+@torch.library.custom_op(f"{NS}::prefix_scan_bwd", mutates_args=())
+def prefix_scan_bwd(k: Tensor, v: Tensor, w: Tensor, a_log: Tensor, sent: Tensor, dsent: Optional[Tensor], dsfin: Optional[Tensor],
+                    want_ds0: bool) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+    dk, dv, dw, da, ds0 = ops.prefix_scan_bwd(k, v, w, a_log, sent, dsent, dsfin, want_ds0)
+    return dk, dv, dw, da, (ds0 if want_ds0 else _none(dk))
+
+
+@prefix_scan_bwd.register_fake
+def _(k, v, w, a_log, sent, dsent, dsfin, want_ds0):
+    B, H, NC = a_log.shape
+    D = k.shape[-1]
+    return (_e(k, B, H, NC * ops.CHUNK, D, dtype=_F32), _e(k, B, H, NC * ops.CHUNK, D, dtype=_F32), _e(k, B, H, NC, ops.CHUNK, dtype=_F32),
+            _e(k, B, H, NC, dtype=_F32), _e(k, *((B, H, D, D) if want_ds0 else (0,)), dtype=_F32))
+
+
+def _prefix_setup(ctx, inputs, output):
+    k, v, w, a_log, S0, has_s0, bv = inputs
+    ctx.has_s0 = bool(has_s0 and S0 is not None)
+    ctx.w_shape = w.shape
+    ctx.save_for_backward(k, v, w, a_log, output[0], *([S0] if ctx.has_s0 else []))
+
+
+def _prefix_backward(ctx, dsent, dsfin):
+    """The reference's _prefix_bwd (src/assoc_kernel.py:206-228, wired at :299)."""
+    k, v, w, a_log, sent = ctx.saved_tensors[:5]
+    dk, dv, dw, da, ds0 = prefix_scan_bwd(k, v, w, a_log, sent, None if dsent is None else dsent.contiguous(),
+                                          None if dsfin is None else dsfin.contiguous(), ctx.has_s0)
+    return (dk.to(k.dtype), dv.to(v.dtype), dw.view(ctx.w_shape).to(w.dtype), da.to(a_log.dtype),
+            (ds0.to(ctx.saved_tensors[5].dtype) if ctx.has_s0 else None), None, None)
+
+
+prefix_scan.register_autograd(_prefix_backward, setup_context=_prefix_setup)
 
 
 @torch.library.custom_op(f"{NS}::delta_inv", mutates_args=())

@@ -581,6 +581,10 @@ def linear_act(x, W, bias=None, act: Optional[str] = "gelu"):
 
 
 # ---------------------------------------------------------------------------------------------------------- split operators
+def _needs_grad(*ts):
+    return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in ts)
+
+
 def _io(t):
     return t if t.dtype in (torch.float32, torch.bfloat16) else t.float()
 
@@ -598,8 +602,8 @@ def assoc_out(q, k, v, la, sent, bc: int = CHUNK):
     la, sent = _f32c(la), sent.to(torch.bfloat16).contiguous()
     if tuple(sent.shape) != (B, H, (T + CHUNK - 1) // CHUNK, D, D):
         raise ValueError("assoc_out: sent must be (B,H,ceil(T/64),D,D)")
-    if _compiling():
-        return _cops().assoc_out(q, k, v, la, sent, int(bc))
+    if _compiling() or _needs_grad(q, k, v, la, sent):
+        return _cops().assoc_out(q, k, v, la, sent, int(bc))     # the operator carries the backward (assoc_out_bwd)
     o = torch.empty_like(q)
     check(lib().pgb_assoc_out_fwd(ptr(q), ptr(k), ptr(v), dtype_code(q), ptr(la), ptr(sent), ptr(o), B, H, T, D, stream_of(q)),
           "pgb_assoc_out_fwd")
@@ -619,13 +623,51 @@ def prefix_scan(k, v, w, a_log, S0=None, has_s0: bool = True, bv: int = 16):
         raise ValueError("prefix_scan: k and v must hold whole 64-token chunks")
     w, a_log = _f32c(w), _f32c(a_log)
     S0 = _f32c(S0) if (has_s0 and S0 is not None) else None
-    if _compiling():
-        return tuple(_cops().prefix_scan(k, v, w, a_log, S0, S0 is not None, int(bv)))
+    if _compiling() or _needs_grad(k, v, w, a_log, S0):
+        return tuple(_cops().prefix_scan(k, v, w, a_log, S0, S0 is not None, int(bv)))   # carries the backward (prefix_scan_bwd)
     sent = torch.empty(B, H, NC, D, D, device=k.device, dtype=torch.bfloat16)
     sfin = torch.empty(B, H, D, D, device=k.device, dtype=torch.float32)
     check(lib().pgb_prefix_scan_fwd(ptr(k), ptr(v), dtype_code(k), ptr(w), ptr(a_log), ptr(S0), ptr(sent), ptr(sfin), B, H, NC, D,
                                     stream_of(k)), "pgb_prefix_scan_fwd")
     return sent, sfin
+
+
+@on_device_of
+def assoc_out_bwd(q, k, v, la, sent, dout):
+    """Gradients of assoc_out (the reference's _bwd_chunk): (dq, dk, dv (B,H,T,D), dla (B,H,T), dsent (B,H,NC,D,D)), fp32."""
+    need_cuda(q, k, v, la, sent, dout)
+    B, H, T, D = q.shape
+    q = _io(q).contiguous()
+    k, v, dout = k.to(q.dtype).contiguous(), v.to(q.dtype).contiguous(), dout.to(q.dtype).contiguous()
+    la, sent = _f32c(la), sent.to(torch.bfloat16).contiguous()
+    NC = (T + CHUNK - 1) // CHUNK
+    f = dict(device=q.device, dtype=torch.float32)
+    dq, dk, dv = (torch.empty(B, H, T, D, **f) for _ in range(3))
+    dla, dsent = torch.empty(B, H, T, **f), torch.empty(B, H, NC, D, D, **f)
+    check(lib().pgb_assoc_out_bwd(ptr(q), ptr(k), ptr(v), dtype_code(q), ptr(la), ptr(sent), ptr(dout), ptr(dq), ptr(dk), ptr(dv),
+                                  ptr(dla), ptr(dsent), B, H, T, D, stream_of(q)), "pgb_assoc_out_bwd")
+    return dq, dk, dv, dla, dsent
+
+
+@on_device_of
+def prefix_scan_bwd(k, v, w, a_log, sent, dsent, dsfin, want_ds0: bool = True):
+    """Gradients of prefix_scan (the reference's _prefix_bwd): (dk, dv (B,H,NC*64,D), dw (B,H,NC,64), da_log (B,H,NC),
+    dS0 (B,H,D,D) or None), fp32. dsent / dsfin may be None (no gradient arrived)."""
+    need_cuda(k, v, w, a_log, sent)
+    B, H, NC = a_log.shape
+    D = k.shape[-1]
+    k = _io(k).contiguous()
+    v = v.to(k.dtype).contiguous()
+    w, a_log, sent = _f32c(w), _f32c(a_log), sent.to(torch.bfloat16).contiguous()
+    dsent = None if dsent is None else _f32c(dsent)
+    dsfin = None if dsfin is None else _f32c(dsfin)
+    f = dict(device=k.device, dtype=torch.float32)
+    dk, dv = torch.empty(B, H, NC * CHUNK, D, **f), torch.empty(B, H, NC * CHUNK, D, **f)
+    dw, da = torch.empty(B, H, NC, CHUNK, **f), torch.empty(B, H, NC, **f)
+    ds0 = torch.empty(B, H, D, D, **f) if want_ds0 else None
+    check(lib().pgb_prefix_scan_bwd(ptr(k), ptr(v), dtype_code(k), ptr(w), ptr(a_log), ptr(sent), ptr(dsent), ptr(dsfin), ptr(dk), ptr(dv),
+                                    ptr(dw), ptr(da), ptr(ds0), B, H, NC, D, stream_of(k)), "pgb_prefix_scan_bwd")
+    return dk, dv, dw, da, ds0
 
 
 @on_device_of

@@ -132,6 +132,13 @@ def test_new_entry_points_reject_bad_calls(L):
     assert L.pgb_decode_sample_ex(one, 0, 1.0, 1.5, 0, one, None, 0, one, None, None, one, 1, 8, 1, None) == 2
     assert L.pgb_skinny_linear_ex(one, None, None, None, 0, 1e-5, one, None, 0, one, None, 1, 768, 16, 4, None) == 2
     assert L.pgb_aspin_prep_bwd_tiles(17) == 3
+    # the plain rule's two backward kernels, the batch linear layer
+    assert L.pgb_assoc_out_bwd(one, one, one, 0, one, one, one, one, one, one, one, None, 1, 1, 8, 64, None) == 1
+    assert L.pgb_assoc_out_bwd(one, one, one, 0, one, one, one, one, one, one, one, one, 1, 1, 8, 96, None) == 3
+    assert L.pgb_prefix_scan_bwd(one, one, 7, one, one, one, None, None, one, one, one, one, None, 1, 1, 1, 64, None) == 5
+    assert L.pgb_batch_linear(one, one, None, one, 129, 16, 64, 0, None) == 7 and L.pgb_batch_linear(one, one, None, one, 4, 12, 64, 0, None) == 2
+    assert L.pgb_batch_linear_ex(one, one, one, one, 4, 16, 64, 0, one, 1, one, one, 1, 1e-5, None, None, None) == 1   # folded norm + bias
+    assert L.pgb_batch_linear_parts(768) == 48
     # the one-launch decode step: scratch size, then the rejects (bias missing for a layer norm, short scratch, batch, head dim)
     assert L.pgb_decode_token_work_bytes(1, 768, 2328, 3072) == 2 * (4 * 768 + 2328 + 3072)
     tok = lambda **kw: L.pgb_decode_token_fwd(one, 12, one, one, one, kw.get("nb", one), 2, 1e-5, one, one, one, one, kw.get("wb", 10 ** 6),

@@ -153,3 +153,41 @@ def test_min_p_sampling():
     prompt = synth.token_ids(2, 40, 256, seed=2).to(DEV)
     out = Decoder(m, batch=2, min_p=0.3).generate(prompt, 10, temp=1.0, seed=1)
     assert tuple(out.shape) == (2, 10) and torch.equal(out, Decoder(m, batch=2, min_p=0.3, use_graph=False).generate(prompt, 10, temp=1.0, seed=1))
+
+
+@pytest.mark.parametrize("D,T,io", [(64, 200, torch.float32), (128, 130, torch.float32), (64, 333, torch.bfloat16)])
+def test_plain_rule_trains_through_the_split_operators(D, T, io):
+    """assoc_out and prefix_scan carry the reference's backward kernels (src/assoc_kernel.py:75-126, 206-228): the
+    gradients of the plain-rule scan composed from them, against autograd through the CPU oracle's chunked scan."""
+    with torch.enable_grad():
+        _split_operator_gradients(D, T, io)
+
+
+def _split_operator_gradients(D, T, io):
+    B, H = 2, 3
+    x = synth.assoc_op_inputs(B, H, T, D, seed=5, with_state=True)
+    w_o = torch.randn(B, H, T, D, generator=torch.Generator().manual_seed(1))
+    w_s = torch.randn(B, H, D, D, generator=torch.Generator().manual_seed(2)) * 0.1
+    names = ("q", "k", "v", "la", "S0")
+    ref_in = {n: x[n].double().requires_grad_(True) for n in names}
+    if io == torch.bfloat16:                                          # the kernels see bf16-rounded q, k, v
+        ref_in = {n: (x[n].to(io).double() if n in "qkv" else x[n].double()).requires_grad_(True) for n in names}
+    o_ref, s_ref = oracle.assoc_scan(ref_in["q"], ref_in["k"], ref_in["v"], ref_in["la"], ref_in["S0"])
+    ((o_ref * w_o).sum() + (s_ref * w_s).sum()).backward()
+
+    dev_in = {n: (x[n].to(io) if n in "qkv" else x[n]).to(DEV).requires_grad_(True) for n in names}
+    q, k, v, la, S0 = (dev_in[n] for n in names)
+    NC = (T + 63) // 64
+    pad = NC * 64 - T
+    kp, vp = (torch.nn.functional.pad(t, (0, 0, 0, pad)) for t in (k, v))
+    Lc = torch.nn.functional.pad(la, (0, pad)).view(B, H, NC, 64).cumsum(-1)
+    a_log = Lc[..., -1]
+    w = torch.exp(a_log[..., None] - Lc)
+    sent, sfin = ops.prefix_scan(kp, vp, w, a_log, S0)
+    o = ops.assoc_out(q, k, v, la, sent)
+    ((o.float() * w_o.to(DEV)).sum() + (sfin * w_s.to(DEV)).sum()).backward()
+    tol = 2e-2 if io == torch.bfloat16 else 1e-2                      # the states between the two operators travel as bf16
+    assert rel_err(o.detach().float().cpu(), o_ref.detach().float()) <= tol
+    for n in names:
+        e = rel_err(dev_in[n].grad.float().cpu(), ref_in[n].grad.float())
+        assert e <= tol, (n, e)
