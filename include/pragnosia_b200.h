@@ -137,6 +137,18 @@ int pgb_assoc_out_bwd(const void *q, const void *k, const void *v, int io_dtype,
 int pgb_prefix_scan_bwd(const void *k, const void *v, int io_dtype, const float *w, const float *a_log, const void *sent,
                         const float *dsent, const float *dsfin, float *dk, float *dv, float *dw, float *da_log, float *dS0, int B, int H,
                         int NC, int D, void *stream);
+/* Backward of the two delta-rule operators below (src/assoc_kernel.py:390-507 _delta_loop_bwd, :626-656 _inv_bwd, wired with
+ * register_autograd at :509 and :704). fp32 gradients, fixed summation order.
+ *   pgb_delta_inv_bwd:  dX [B][H][NC][64][64] -> dk [B][H][T][D], dla, dbeta [B][H][T].
+ *   pgb_delta_loop_bwd: dW [B][H][T][D], dsent [B][H][NC][D][D], dsfin [B][H][D][D] (each may be NULL = zero); sent = the
+ *     forward's output. Sums over value columns leave as one part per 64-column slab, P = D / 64, for the caller to add:
+ *     dk_part [P][B][H][T][D], dla_part, dbeta_part [P][B][H][T], dX_part [P][B][H][NC][64][64]; dv [B][H][T][D] and
+ *     dS0 [B][H][D][D] (or NULL) are complete. */
+int pgb_delta_inv_bwd(const void *k, int io_dtype, const float *la, const float *beta, const void *X, const float *dX, float *dk, float *dla,
+                      float *dbeta, int B, int H, int T, int D, void *stream);
+int pgb_delta_loop_bwd(const void *k, const void *v, int io_dtype, const float *la, const float *beta, const void *X, const void *sent,
+                       const float *dW, const float *dsent, const float *dsfin, float *dk_part, float *dv, float *dla_part,
+                       float *dbeta_part, float *dX_part, float *dS0, int B, int H, int T, int D, void *stream);
 int pgb_delta_inv_fwd(const void *k, const float *la, const float *beta, void *X, int B, int H, int T, int D, void *stream);
 int pgb_delta_loop_fwd(const void *k, const void *v, int io_dtype, const float *la, const float *beta, const void *X, const float *S0,
                        void *W, void *sent, float *sfin, int B, int H, int T, int D, void *stream);

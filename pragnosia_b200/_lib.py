@@ -61,6 +61,8 @@ SIGNATURES = {
     "pgb_prefix_scan_fwd": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "pgb_assoc_out_bwd": [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "pgb_prefix_scan_bwd": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "pgb_delta_inv_bwd": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "pgb_delta_loop_bwd": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "pgb_delta_inv_fwd": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "pgb_delta_loop_fwd": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "pgb_key_topk_mask": [_vp, _i, _ll, _ll, _ll, _i, _i, _i, _i, _i, _vp],

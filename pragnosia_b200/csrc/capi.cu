@@ -29,6 +29,10 @@ int delta_loop_launch(const void *, const void *, int, const float *, const floa
 int delta_inv_launch(const void *, const float *, const float *, void *, int, int, int, cudaStream_t);
 int assoc_out_bwd_launch(const void *, const void *, const void *, int, const float *, const void *, const void *, float *, float *, float *,
                          float *, float *, int, int, int, cudaStream_t);
+int delta_inv_bwd_launch(const void *, int, const float *, const float *, const void *, const float *, float *, float *, float *, int, int, int,
+                         cudaStream_t);
+int delta_loop_bwd_launch(const void *, const void *, int, const float *, const float *, const void *, const void *, const float *, const float *,
+                          const float *, float *, float *, float *, float *, float *, float *, int, int, int, cudaStream_t);
 int prefix_scan_bwd_launch(const void *, const void *, int, const float *, const float *, const void *, const float *, const float *, float *,
                            float *, float *, float *, float *, int, int, int, cudaStream_t);
 int key_topk_launch(void *, int, long long, long long, long long, int, int, int, int, int, cudaStream_t);
@@ -203,6 +207,26 @@ int pgb_prefix_scan_bwd(const void *k, const void *v, int io_dtype, const float 
     if (B <= 0 || H <= 0 || NC <= 0) return PGB_ERR_BAD_SHAPE;
     if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
     return prefix_scan_bwd_launch(k, v, io_dtype, w, a_log, sent, dsent, dsfin, dk, dv, dw, da_log, dS0, B * H, NC, D, (cudaStream_t)stream);
+}
+
+int pgb_delta_inv_bwd(const void *k, int io_dtype, const float *la, const float *beta, const void *X, const float *dX, float *dk, float *dla,
+                      float *dbeta, int B, int H, int T, int D, void *stream) {
+    if (!k || !la || !beta || !X || !dX || !dk || !dla || !dbeta) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(io_dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || H <= 0 || T <= 0 || (long long)B * H > 65535) return PGB_ERR_BAD_SHAPE;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    return delta_inv_bwd_launch(k, io_dtype, la, beta, X, dX, dk, dla, dbeta, B * H, T, D, (cudaStream_t)stream);
+}
+
+int pgb_delta_loop_bwd(const void *k, const void *v, int io_dtype, const float *la, const float *beta, const void *X, const void *sent,
+                       const float *dW, const float *dsent, const float *dsfin, float *dk_part, float *dv, float *dla_part,
+                       float *dbeta_part, float *dX_part, float *dS0, int B, int H, int T, int D, void *stream) {
+    if (!k || !v || !la || !beta || !X || !sent || !dk_part || !dv || !dla_part || !dbeta_part || !dX_part) return PGB_ERR_NULL_POINTER;
+    if (!dtype_ok(io_dtype)) return PGB_ERR_BAD_DTYPE;
+    if (B <= 0 || H <= 0 || T <= 0 || (long long)B * H > 65535) return PGB_ERR_BAD_SHAPE;
+    if (D != 64 && D != 128) return PGB_ERR_UNSUPPORTED_DIM;
+    return delta_loop_bwd_launch(k, v, io_dtype, la, beta, X, sent, dW, dsent, dsfin, dk_part, dv, dla_part, dbeta_part, dX_part, dS0, B * H, T,
+                                 D, (cudaStream_t)stream);
 }
 
 int pgb_delta_inv_fwd(const void *k, const float *la, const float *beta, void *X, int B, int H, int T, int D, void *stream) {

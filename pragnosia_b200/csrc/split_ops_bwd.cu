@@ -1,6 +1,6 @@
-// Backward of the plain rule's two split operators (the reference's _bwd_chunk, src/assoc_kernel.py:75-126, and
-// _prefix_bwd, :206-228, with their register_autograd wiring at :179 and :299), so that code written against
-// membrae::assoc_out / membrae::prefix_scan can train through this library. Like the forward kernels in split_ops.cu
+// Backward of the split operators (the reference's _bwd_chunk, src/assoc_kernel.py:75-126, _prefix_bwd, :206-228,
+// _delta_loop_bwd, :390-507, and _inv_bwd, :626-656, with their register_autograd wiring at :179, :299, :509, :704), so that
+// code written against membrae::assoc_out / prefix_scan / delta_loop_fwd / delta_inv can train through this library. Like the forward kernels in split_ops.cu
 // these are plain fp32 FFMA kernels built for exactness, not speed; every gradient leaves in fp32 and every sum is taken
 // in a fixed order (no atomics).
 //
@@ -210,6 +210,248 @@ __global__ void __launch_bounds__(SB_NT) prefix_scan_bwd_kernel(const TIO *__res
         for (int idx = tid; idx < D * D; idx += SB_NT) dS0[(size_t)bh * D * D + idx] = G[(idx / D) * P + idx % D];
 }
 
+// ---------------------------------------------------------------------------------------------------- delta_inv backward
+// X = (I + N)^-1,  N[t][s] = beta_t (k_t.k_s) e^{L_t-L_s} for s < t.   dN = -X^T dX X^T restricted to s < t, then
+//   dbeta_t = sum_s dN (k_t.k_s) dec;   dk_t = sum_s c[t][s] k_s + sum_t' c[t'][t] k_t'  with c = dN beta dec;
+//   dL_t = sum_s dN N [t,s] - sum_t' dN N [t',t];   dla = reverse cumulative sum of dL.
+// (the reference's _inv_bwd, src/assoc_kernel.py:626-656, wired at :704)
+template <typename TIO, int D>
+__global__ void __launch_bounds__(SB_NT) delta_inv_bwd_kernel(const TIO *__restrict__ k, const float *__restrict__ la, const float *__restrict__ be,
+                                                              const __nv_bfloat16 *__restrict__ X, const float *__restrict__ dX,
+                                                              float *__restrict__ dk, float *__restrict__ dla, float *__restrict__ dbe,
+                                                              int T, int NC) {
+    constexpr int P = D + 1, MP = SB_C + 1;
+    extern __shared__ float sb_smem[];
+    float *ks = sb_smem, *Xs = ks + SB_C * P, *M1 = Xs + SB_C * MP, *M2 = M1 + SB_C * MP, *M3 = M2 + SB_C * MP, *las = M3 + SB_C * MP,
+          *L = las + SB_C, *bes = L + SB_C, *dL = bes + SB_C;
+    const int tid = threadIdx.x, c = blockIdx.x, bh = blockIdx.y, t0 = c * SB_C;
+    const size_t base = ((size_t)bh * T + t0) * D, xb = ((size_t)bh * NC + c) * SB_C * SB_C;
+    for (int idx = tid; idx < SB_C * D; idx += SB_NT) ks[(idx / D) * P + idx % D] = t0 + idx / D < T ? sb_ld(k + base + idx) : 0.f;
+    for (int idx = tid; idx < SB_C * SB_C; idx += SB_NT) {
+        Xs[(idx / SB_C) * MP + idx % SB_C] = __bfloat162float(X[xb + idx]);
+        M1[(idx / SB_C) * MP + idx % SB_C] = dX[xb + idx];                       // M1 = dX
+    }
+    if (tid < SB_C) {
+        las[tid] = t0 + tid < T ? la[(size_t)bh * T + t0 + tid] : 0.f;
+        bes[tid] = t0 + tid < T ? be[(size_t)bh * T + t0 + tid] : 0.f;
+    }
+    __syncthreads();
+    if (tid < SB_C) {
+        float s = 0.f;
+        for (int i = 0; i <= tid; ++i) s += las[i];
+        L[tid] = s;
+    }
+    const int r = tid >> 2, c0 = (tid & 3) * 16;                      // thread (row, 16 consecutive columns) of a 64 x 64 matrix
+    for (int b = c0; b < c0 + 16; ++b) {                              // M2 = X^T dX
+        float acc = 0.f;
+        for (int t = 0; t < SB_C; ++t) acc = fmaf(Xs[t * MP + r], M1[t * MP + b], acc);
+        M2[r * MP + b] = acc;
+    }
+    __syncthreads();
+    for (int b = c0; b < c0 + 16; ++b) {                              // M3 = dN = -(X^T dX) X^T, strictly lower
+        float acc = 0.f;
+        if (b < r)
+            for (int u = 0; u < SB_C; ++u) acc = fmaf(M2[r * MP + u], Xs[b * MP + u], acc);
+        M3[r * MP + b] = -acc;
+    }
+    __syncthreads();
+    for (int b = c0; b < c0 + 16; ++b) {                              // M1 = c (dk coefficient), M2 = dN N, Xs = dN (k.k) dec
+        float cc = 0.f, g = 0.f, nb = 0.f;
+        if (b < r) {
+            float kk = 0.f;
+            for (int i = 0; i < D; ++i) kk = fmaf(ks[r * P + i], ks[b * P + i], kk);
+            const float dec = expf(fminf(L[r] - L[b], 0.f)), dn = M3[r * MP + b];
+            nb = dn * kk * dec; cc = dn * bes[r] * dec; g = nb * bes[r];
+        }
+        M1[r * MP + b] = cc; M2[r * MP + b] = g; Xs[r * MP + b] = nb;
+    }
+    __syncthreads();
+    {   // dk[t][i] = sum_s c[t][s] k[s][i] + sum_t' c[t'][t] k[t'][i]
+        constexpr int NG = SB_NT / D, NT = SB_C / NG;
+        const int col = tid % D, grp = tid / D;
+        float acc[NT];
+#pragma unroll
+        for (int tt = 0; tt < NT; ++tt) acc[tt] = 0.f;
+        for (int u = 0; u < SB_C; ++u) {
+            const float ku = ks[u * P + col];
+#pragma unroll
+            for (int tt = 0; tt < NT; ++tt) {
+                const int t = grp * NT + tt;
+                acc[tt] = fmaf(M1[t * MP + u] + M1[u * MP + t], ku, acc[tt]);
+            }
+        }
+#pragma unroll
+        for (int tt = 0; tt < NT; ++tt)
+            if (t0 + grp * NT + tt < T) dk[base + (size_t)(grp * NT + tt) * D + col] = acc[tt];
+    }
+    if (tid < SB_C) {
+        float s = 0.f, b = 0.f;
+        for (int u = 0; u < SB_C; ++u) { s += M2[tid * MP + u] - M2[u * MP + tid]; b += Xs[tid * MP + u]; }
+        dL[tid] = s;
+        if (t0 + tid < T) dbe[(size_t)bh * T + t0 + tid] = b;
+    }
+    __syncthreads();
+    if (tid < SB_C && t0 + tid < T) {
+        float s = 0.f;
+        for (int u = SB_C - 1; u >= tid; --u) s += dL[u];
+        dla[(size_t)bh * T + t0 + tid] = s;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------- delta_loop backward
+// Forward per chunk:  rhs = beta (v - e^L (k S));  W = X rhs;  S' = e^{L_C} S + (k w)^T W,  w_s = e^{L_C - L_s}.
+// One CTA per (sequence-head, 64 value columns) walks the chunks backwards with G = dLoss/dS' (its columns) in shared
+// memory. Sums over value columns (dk, dla, dbeta, dX) leave as one partial per column slab; the caller adds the slabs.
+// (the reference's _delta_loop_bwd, src/assoc_kernel.py:390-507, wired at :509)
+template <typename TIO, int D>
+__global__ void __launch_bounds__(SB_NT) delta_loop_bwd_kernel(const TIO *__restrict__ k, const TIO *__restrict__ v, const float *__restrict__ la,
+                                                               const float *__restrict__ be, const __nv_bfloat16 *__restrict__ X,
+                                                               const __nv_bfloat16 *__restrict__ sent, const float *__restrict__ dW,
+                                                               const float *__restrict__ dsent, const float *__restrict__ dsfin,
+                                                               float *__restrict__ dk_part, float *__restrict__ dv, float *__restrict__ dla_part,
+                                                               float *__restrict__ dbe_part, float *__restrict__ dX_part, float *__restrict__ dS0,
+                                                               int BH, int T, int NC) {
+    constexpr int P = D + 1, MP = SB_C + 1, SL = 64;                  // SL: value columns of this CTA
+    extern __shared__ float sb_smem[];
+    float *G = sb_smem, *S = G + D * MP, *ks = S + D * MP, *Xs = ks + SB_C * P, *RH = Xs + SB_C * MP, *Wm = RH + SB_C * MP,
+          *KS = Wm + SB_C * MP, *KG = KS + SB_C * MP, *DW = KG + SB_C * MP, *DR = DW + SB_C * MP, *las = DR + SB_C * MP, *L = las + SB_C,
+          *eL = L + SB_C, *wt = eL + SB_C, *bes = wt + SB_C, *dwv = bes + SB_C, *dLa = dwv + SB_C, *red = dLa + SB_C;
+    const int tid = threadIdx.x, slab = blockIdx.x, bh = blockIdx.y, j0 = slab * SL, lane = tid & 31, warp = tid >> 5;
+    const int r = tid >> 2, c0 = (tid & 3) * 16;                      // (token row, 16 slab columns)
+    constexpr int NG = SB_NT / D, NT = SB_C / NG;                     // (state row / k column i, group of token rows)
+    const int col = tid % D, grp = tid / D;
+    const size_t part = (size_t)slab * BH + bh;
+    for (int idx = tid; idx < D * SL; idx += SB_NT) {
+        const int i = idx / SL, j = idx % SL;
+        G[i * MP + j] = dsfin != nullptr ? dsfin[((size_t)bh * D + i) * D + j0 + j] : 0.f;
+    }
+    for (int c = NC - 1; c >= 0; --c) {
+        const int t0 = c * SB_C;
+        const size_t base = ((size_t)bh * T + t0) * D, xb = ((size_t)bh * NC + c) * SB_C * SB_C, sb = ((size_t)bh * NC + c) * D * D;
+        __syncthreads();
+        for (int idx = tid; idx < SB_C * D; idx += SB_NT) ks[(idx / D) * P + idx % D] = t0 + idx / D < T ? sb_ld(k + base + idx) : 0.f;
+        for (int idx = tid; idx < SB_C * SB_C; idx += SB_NT) Xs[(idx / SB_C) * MP + idx % SB_C] = __bfloat162float(X[xb + idx]);
+        for (int idx = tid; idx < D * SL; idx += SB_NT) S[(idx / SL) * MP + idx % SL] = __bfloat162float(sent[sb + (size_t)(idx / SL) * D + j0 + idx % SL]);
+        for (int idx = tid; idx < SB_C * SL; idx += SB_NT) {
+            const int t = idx / SL, j = idx % SL;
+            const bool live = t0 + t < T;
+            RH[t * MP + j] = live ? sb_ld(v + base + (size_t)t * D + j0 + j) : 0.f;                 // v for now
+            DW[t * MP + j] = (live && dW != nullptr) ? dW[base + (size_t)t * D + j0 + j] : 0.f;
+        }
+        if (tid < SB_C) {
+            las[tid] = t0 + tid < T ? la[(size_t)bh * T + t0 + tid] : 0.f;
+            bes[tid] = t0 + tid < T ? be[(size_t)bh * T + t0 + tid] : 0.f;
+        }
+        __syncthreads();
+        if (tid < SB_C) {
+            float s = 0.f, tot = 0.f;
+            for (int i = 0; i < SB_C; ++i) { tot += las[i]; if (i <= tid) s += las[i]; }
+            L[tid] = s; eL[tid] = expf(s);
+            wt[tid] = t0 + tid < T ? expf(fminf(tot - s, 0.f)) : 0.f;
+        }
+        __syncthreads();
+        // 1. KS = k S;  KG = k G;  rhs = beta (v - e^L KS)
+        for (int j = c0; j < c0 + 16; ++j) {
+            float a = 0.f, g = 0.f;
+            for (int i = 0; i < D; ++i) { a = fmaf(ks[r * P + i], S[i * MP + j], a); g = fmaf(ks[r * P + i], G[i * MP + j], g); }
+            KS[r * MP + j] = a; KG[r * MP + j] = g;
+            RH[r * MP + j] = bes[r] * (RH[r * MP + j] - eL[r] * a);
+        }
+        __syncthreads();
+        // 2. W = X rhs;  dWtot = dW + w (k G)
+        for (int j = c0; j < c0 + 16; ++j) {
+            float a = 0.f;
+            for (int s = 0; s <= r; ++s) a = fmaf(Xs[r * MP + s], RH[s * MP + j], a);
+            Wm[r * MP + j] = a;
+            DW[r * MP + j] = fmaf(wt[r], KG[r * MP + j], DW[r * MP + j]);
+        }
+        __syncthreads();
+        // 3. drhs = X^T dWtot;  dX[t][s] = sum_j dWtot[t][j] rhs[s][j] (s <= t);  dw_s = sum_j W[s][j] KG[s][j]
+        for (int j = c0; j < c0 + 16; ++j) {
+            float a = 0.f;
+            for (int t = r; t < SB_C; ++t) a = fmaf(Xs[t * MP + r], DW[t * MP + j], a);
+            DR[r * MP + j] = a;
+        }
+        for (int s = c0; s < c0 + 16; ++s) {
+            float a = 0.f;
+            if (s <= r)
+                for (int j = 0; j < SL; ++j) a = fmaf(DW[r * MP + j], RH[s * MP + j], a);
+            dX_part[(part * NC + c) * SB_C * SB_C + (size_t)r * SB_C + s] = a;
+        }
+        if (tid < SB_C) {
+            float a = 0.f;
+            for (int j = 0; j < SL; ++j) a = fmaf(Wm[tid * MP + j], KG[tid * MP + j], a);
+            dwv[tid] = a;
+        }
+        __syncthreads();
+        // 4. dv = beta drhs;  dbeta_t = sum_j drhs (v - e^L KS);  dL_t (first part) = sum_j dKS KS with dKS = -beta e^L drhs
+        if (tid < SB_C) {
+            const int t = tid;
+            const bool live = t0 + t < T;
+            float db = 0.f, dl = 0.f;
+            for (int j = 0; j < SL; ++j) {
+                const float dr = DR[t * MP + j], ksv = KS[t * MP + j];
+                dl = fmaf(-bes[t] * eL[t] * dr, ksv, dl);
+                if (live) db = fmaf(dr, sb_ld(v + base + (size_t)t * D + j0 + j) - eL[t] * ksv, db);   // v again: its tile now holds rhs
+            }
+            dLa[t] = dl;
+            if (live) dbe_part[part * T + t0 + t] = db;
+        }
+        for (int j = c0; j < c0 + 16; ++j)
+            if (t0 + r < T) dv[base + (size_t)r * D + j0 + j] = bes[r] * DR[r * MP + j];
+        __syncthreads();
+        for (int j = c0; j < c0 + 16; ++j) DR[r * MP + j] *= -bes[r] * eL[r];                      // DR = dKS
+        __syncthreads();
+        // 5. dk[t][i] = w_t sum_j G[i][j] W[t][j] + sum_j dKS[t][j] S[i][j]   (this slab's part)
+        {
+            float acc[NT];
+#pragma unroll
+            for (int tt = 0; tt < NT; ++tt) acc[tt] = 0.f;
+            for (int j = 0; j < SL; ++j) {
+                const float gj = G[col * MP + j], sj = S[col * MP + j];
+#pragma unroll
+                for (int tt = 0; tt < NT; ++tt) {
+                    const int t = grp * NT + tt;
+                    acc[tt] = fmaf(wt[t] * gj, Wm[t * MP + j], acc[tt]);
+                    acc[tt] = fmaf(DR[t * MP + j], sj, acc[tt]);
+                }
+            }
+#pragma unroll
+            for (int tt = 0; tt < NT; ++tt)
+                if (t0 + grp * NT + tt < T) dk_part[(part * T + t0 + grp * NT + tt) * D + col] = acc[tt];
+        }
+        // 6. <G, S> for dL_C, summed in a fixed order
+        const float LC = L[SB_C - 1], aC = expf(LC);
+        float pr = 0.f;
+        for (int idx = tid; idx < D * SL; idx += SB_NT) pr = fmaf(G[(idx / SL) * MP + idx % SL], S[(idx / SL) * MP + idx % SL], pr);
+        pr = warp_sum(pr);
+        if (lane == 0) red[warp] = pr;
+        __syncthreads();
+        // 7. dL and dla (this slab's part): dL_t = dL_t(a) - dw_t w_t, plus dL_C on the chunk's last step
+        if (tid == 0) {
+            float gs = 0.f;
+            for (int i = 0; i < SB_NT / 32; ++i) gs += red[i];
+            float dLC = aC * gs;
+            for (int s = 0; s < SB_C; ++s) dLC = fmaf(dwv[s], wt[s], dLC);
+            float run = 0.f;
+            for (int t = SB_C - 1; t >= 0; --t) {
+                run += dLa[t] - dwv[t] * wt[t] + (t == SB_C - 1 ? dLC : 0.f);
+                if (t0 + t < T) dla_part[part * T + t0 + t] = run;
+            }
+        }
+        // 8. G <- e^{L_C} G + k^T dKS + dsent[c]
+        for (int idx = tid; idx < D * SL; idx += SB_NT) {
+            const int i = idx / SL, j = idx % SL;
+            float a = dsent != nullptr ? dsent[sb + (size_t)i * D + j0 + j] : 0.f;
+            for (int t = 0; t < SB_C; ++t) a = fmaf(ks[t * P + i], DR[t * MP + j], a);
+            G[i * MP + j] = fmaf(aC, G[i * MP + j], a);
+        }
+    }
+    __syncthreads();
+    if (dS0 != nullptr)
+        for (int idx = tid; idx < D * SL; idx += SB_NT) dS0[((size_t)bh * D + idx / SL) * D + j0 + idx % SL] = G[(idx / SL) * MP + idx % SL];
+}
+
 // ---------------------------------------------------------------------------------------------------- host side
 template <typename K>
 static int sb_attr(K kern, size_t smem, const char *what) {
@@ -259,6 +501,50 @@ int prefix_scan_bwd_launch(const void *k, const void *v, int io_dtype, const flo
                        : prefix_scan_bwd_go<__nv_bfloat16, 128>(k, v, w, a_log, sent, dsent, dsfin, dk, dv, dw, da_log, dS0, BH, NC, st);
     return D == 64 ? prefix_scan_bwd_go<float, 64>(k, v, w, a_log, sent, dsent, dsfin, dk, dv, dw, da_log, dS0, BH, NC, st)
                    : prefix_scan_bwd_go<float, 128>(k, v, w, a_log, sent, dsent, dsfin, dk, dv, dw, da_log, dS0, BH, NC, st);
+}
+
+template <typename TIO, int D>
+static int delta_inv_bwd_go(const void *k, const float *la, const float *be, const void *X, const float *dX, float *dk, float *dla, float *dbe,
+                            int BH, int T, cudaStream_t st) {
+    const int NC = (T + SB_C - 1) / SB_C;
+    const size_t smem = (size_t)(SB_C * (D + 1) + 4 * SB_C * (SB_C + 1) + 4 * SB_C) * sizeof(float);
+    int rc = sb_attr(delta_inv_bwd_kernel<TIO, D>, smem, "delta_inv_bwd smem attribute");
+    if (rc != PGB_OK) return rc;
+    delta_inv_bwd_kernel<TIO, D><<<dim3(NC, BH), SB_NT, smem, st>>>((const TIO *)k, la, be, (const __nv_bfloat16 *)X, dX, dk, dla, dbe, T, NC);
+    return check_launch("delta_inv_bwd_kernel");
+}
+
+int delta_inv_bwd_launch(const void *k, int io_dtype, const float *la, const float *be, const void *X, const float *dX, float *dk, float *dla,
+                         float *dbe, int BH, int T, int D, cudaStream_t st) {
+    if (io_dtype == PGB_BF16)
+        return D == 64 ? delta_inv_bwd_go<__nv_bfloat16, 64>(k, la, be, X, dX, dk, dla, dbe, BH, T, st)
+                       : delta_inv_bwd_go<__nv_bfloat16, 128>(k, la, be, X, dX, dk, dla, dbe, BH, T, st);
+    return D == 64 ? delta_inv_bwd_go<float, 64>(k, la, be, X, dX, dk, dla, dbe, BH, T, st)
+                   : delta_inv_bwd_go<float, 128>(k, la, be, X, dX, dk, dla, dbe, BH, T, st);
+}
+
+template <typename TIO, int D>
+static int delta_loop_bwd_go(const void *k, const void *v, const float *la, const float *be, const void *X, const void *sent, const float *dW,
+                             const float *dsent, const float *dsfin, float *dk_part, float *dv, float *dla_part, float *dbe_part,
+                             float *dX_part, float *dS0, int BH, int T, cudaStream_t st) {
+    const int NC = (T + SB_C - 1) / SB_C;
+    const size_t smem = (size_t)(2 * D * (SB_C + 1) + SB_C * (D + 1) + 7 * SB_C * (SB_C + 1) + 7 * SB_C + 8) * sizeof(float);
+    int rc = sb_attr(delta_loop_bwd_kernel<TIO, D>, smem, "delta_loop_bwd smem attribute");
+    if (rc != PGB_OK) return rc;
+    delta_loop_bwd_kernel<TIO, D><<<dim3(D / 64, BH), SB_NT, smem, st>>>((const TIO *)k, (const TIO *)v, la, be, (const __nv_bfloat16 *)X,
+                                                                       (const __nv_bfloat16 *)sent, dW, dsent, dsfin, dk_part, dv, dla_part,
+                                                                       dbe_part, dX_part, dS0, BH, T, NC);
+    return check_launch("delta_loop_bwd_kernel");
+}
+
+int delta_loop_bwd_launch(const void *k, const void *v, int io_dtype, const float *la, const float *be, const void *X, const void *sent,
+                          const float *dW, const float *dsent, const float *dsfin, float *dk_part, float *dv, float *dla_part,
+                          float *dbe_part, float *dX_part, float *dS0, int BH, int T, int D, cudaStream_t st) {
+    if (io_dtype == PGB_BF16)
+        return D == 64 ? delta_loop_bwd_go<__nv_bfloat16, 64>(k, v, la, be, X, sent, dW, dsent, dsfin, dk_part, dv, dla_part, dbe_part, dX_part, dS0, BH, T, st)
+                       : delta_loop_bwd_go<__nv_bfloat16, 128>(k, v, la, be, X, sent, dW, dsent, dsfin, dk_part, dv, dla_part, dbe_part, dX_part, dS0, BH, T, st);
+    return D == 64 ? delta_loop_bwd_go<float, 64>(k, v, la, be, X, sent, dW, dsent, dsfin, dk_part, dv, dla_part, dbe_part, dX_part, dS0, BH, T, st)
+                   : delta_loop_bwd_go<float, 128>(k, v, la, be, X, sent, dW, dsent, dsfin, dk_part, dv, dla_part, dbe_part, dX_part, dS0, BH, T, st);
 }
 
 }  // namespace pgb

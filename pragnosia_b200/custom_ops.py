@@ -9,7 +9,7 @@ Two groups:
     aspin_layer_prefill, aspin_decode_step, lambda_scan, rot_table, rotate, add_norm, linear_act.
 Every operator is functional (mutates_args=()): outputs are new tensors; an absent optional output is an empty tensor.
 Backward formulas are registered for lambda_scan (the adjoint scan), assoc_prep, assoc_out and prefix_scan (the plain
-rule trains through the split operators).
+rule and the delta rule train through the split operators).
 
 The operator bodies run eagerly and call pragnosia_b200.ops, which makes the one library call.
 """
@@ -253,6 +253,32 @@ def _(k, la, be, nc):
     return _e(k, B, H, nc, ops.CHUNK, ops.CHUNK, dtype=_BF16)
 
 
+@torch.library.custom_op(f"{NS}::delta_inv_bwd", mutates_args=())
+def delta_inv_bwd(k: Tensor, la: Tensor, be: Tensor, X: Tensor, dX: Tensor) -> Tuple[Tensor, Tensor, Tensor]:
+    return ops.delta_inv_bwd(k, la, be, X, dX)
+
+
+@delta_inv_bwd.register_fake
+def _(k, la, be, X, dX):
+    B, H, T, D = k.shape
+    return _e(k, B, H, T, D, dtype=_F32), _e(k, B, H, T, dtype=_F32), _e(k, B, H, T, dtype=_F32)
+
+
+def _inv_setup(ctx, inputs, output):
+    k, la, be, nc = inputs
+    ctx.save_for_backward(k, la, be, output)
+
+
+def _inv_backward(ctx, dX):
+    """The reference's _inv_bwd (src/assoc_kernel.py:626-656, wired at :704)."""
+    k, la, be, X = ctx.saved_tensors
+    dk, dla, dbe = delta_inv_bwd(k, la, be, X, dX.contiguous())
+    return dk.to(k.dtype), dla.to(la.dtype), dbe.to(be.dtype), None
+
+
+delta_inv.register_autograd(_inv_backward, setup_context=_inv_setup)
+
+
 @torch.library.custom_op(f"{NS}::delta_loop_fwd", mutates_args=())
 def delta_loop_fwd(k: Tensor, v: Tensor, la: Tensor, be: Tensor, X: Tensor, S0: Optional[Tensor], has_s0: bool, bc: int, bv: int,
                    bvb: int) -> Tuple[Tensor, Tensor, Tensor]:
@@ -264,6 +290,38 @@ def _(k, v, la, be, X, S0, has_s0, bc, bv, bvb):
     B, H, T, D = k.shape
     NC = X.shape[2]
     return _e(k, B, H, T, D, dtype=_BF16), _e(k, B, H, NC, D, D, dtype=_BF16), _e(k, B, H, D, D, dtype=_F32)
+
+
+@torch.library.custom_op(f"{NS}::delta_loop_bwd", mutates_args=())
+def delta_loop_bwd(k: Tensor, v: Tensor, la: Tensor, be: Tensor, X: Tensor, sent: Tensor, dW: Optional[Tensor], dsent: Optional[Tensor],
+                   dsfin: Optional[Tensor], want_ds0: bool) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    dk, dv, dla, dbe, dX, ds0 = ops.delta_loop_bwd(k, v, la, be, X, sent, dW, dsent, dsfin, want_ds0)
+    return dk, dv, dla, dbe, dX, (ds0 if want_ds0 else _none(dk))
+
+
+@delta_loop_bwd.register_fake
+def _(k, v, la, be, X, sent, dW, dsent, dsfin, want_ds0):
+    B, H, T, D = k.shape
+    return (_e(k, B, H, T, D, dtype=_F32), _e(k, B, H, T, D, dtype=_F32), _e(k, B, H, T, dtype=_F32), _e(k, B, H, T, dtype=_F32),
+            _e(k, *X.shape, dtype=_F32), _e(k, *((B, H, D, D) if want_ds0 else (0,)), dtype=_F32))
+
+
+def _loop_setup(ctx, inputs, output):
+    k, v, la, be, X, S0, has_s0, bc, bv, bvb = inputs
+    ctx.has_s0 = bool(has_s0 and S0 is not None)
+    ctx.save_for_backward(k, v, la, be, X, output[1], *([S0] if ctx.has_s0 else []))
+
+
+def _loop_backward(ctx, dW, dsent, dsfin):
+    """The reference's _delta_loop_bwd (src/assoc_kernel.py:390-507, wired at :509)."""
+    k, v, la, be, X, sent = ctx.saved_tensors[:6]
+    c = lambda t: None if t is None else t.contiguous()
+    dk, dv, dla, dbe, dX, ds0 = delta_loop_bwd(k, v, la, be, X, sent, c(dW), c(dsent), c(dsfin), ctx.has_s0)
+    return (dk.to(k.dtype), dv.to(v.dtype), dla.to(la.dtype), dbe.to(be.dtype), dX.to(X.dtype),
+            (ds0.to(ctx.saved_tensors[6].dtype) if ctx.has_s0 else None), None, None, None, None)
+
+
+delta_loop_fwd.register_autograd(_loop_backward, setup_context=_loop_setup)
 
 
 # ------------------------------------------------------------------------------------------------ the fused operators

@@ -678,8 +678,8 @@ def delta_inv(k, la, be, nc: int):
     if nc != (T + CHUNK - 1) // CHUNK:
         raise ValueError("delta_inv: nc must be ceil(T/64)")
     k, la, be = k.to(torch.bfloat16).contiguous(), _f32c(la), _f32c(be)
-    if _compiling():
-        return _cops().delta_inv(k, la, be, int(nc))
+    if _compiling() or _needs_grad(k, la, be):
+        return _cops().delta_inv(k, la, be, int(nc))                 # the operator carries the backward (delta_inv_bwd)
     X = torch.empty(B, H, nc, CHUNK, CHUNK, device=k.device, dtype=torch.bfloat16)
     check(lib().pgb_delta_inv_fwd(ptr(k), ptr(la), ptr(be), ptr(X), B, H, T, D, stream_of(k)), "pgb_delta_inv_fwd")
     return X
@@ -698,14 +698,52 @@ def delta_loop_fwd(k, v, la, be, X, S0=None, has_s0: bool = True, bc: int = CHUN
     v = v.to(k.dtype).contiguous()
     la, be, X = _f32c(la), _f32c(be), X.to(torch.bfloat16).contiguous()
     S0 = _f32c(S0) if (has_s0 and S0 is not None) else None
-    if _compiling():
-        return tuple(_cops().delta_loop_fwd(k, v, la, be, X, S0, S0 is not None, int(bc), int(bv), int(bvb)))
+    if _compiling() or _needs_grad(k, v, la, be, X, S0):
+        return tuple(_cops().delta_loop_fwd(k, v, la, be, X, S0, S0 is not None, int(bc), int(bv), int(bvb)))   # carries delta_loop_bwd
     W = torch.empty(B, H, T, D, device=k.device, dtype=torch.bfloat16)
     sent = torch.empty(B, H, NC, D, D, device=k.device, dtype=torch.bfloat16)
     sfin = torch.empty(B, H, D, D, device=k.device, dtype=torch.float32)
     check(lib().pgb_delta_loop_fwd(ptr(k), ptr(v), dtype_code(k), ptr(la), ptr(be), ptr(X), ptr(S0), ptr(W), ptr(sent), ptr(sfin),
                                    B, H, T, D, stream_of(k)), "pgb_delta_loop_fwd")
     return W, sent, sfin
+
+
+@on_device_of
+def delta_inv_bwd(k, la, be, X, dX):
+    """Gradients of delta_inv (the reference's _inv_bwd): (dk (B,H,T,D), dla, dbeta (B,H,T)), fp32."""
+    need_cuda(k, la, be, X, dX)
+    B, H, T, D = k.shape
+    k = _io(k).contiguous()
+    la, be, X, dX = _f32c(la), _f32c(be), X.to(torch.bfloat16).contiguous(), _f32c(dX)
+    f = dict(device=k.device, dtype=torch.float32)
+    dk, dla, dbe = torch.empty(B, H, T, D, **f), torch.empty(B, H, T, **f), torch.empty(B, H, T, **f)
+    check(lib().pgb_delta_inv_bwd(ptr(k), dtype_code(k), ptr(la), ptr(be), ptr(X), ptr(dX), ptr(dk), ptr(dla), ptr(dbe), B, H, T, D,
+                                  stream_of(k)), "pgb_delta_inv_bwd")
+    return dk, dla, dbe
+
+
+@on_device_of
+def delta_loop_bwd(k, v, la, be, X, sent, dW, dsent, dsfin, want_ds0: bool = True):
+    """Gradients of delta_loop_fwd (the reference's _delta_loop_bwd): (dk, dv (B,H,T,D), dla, dbeta (B,H,T),
+    dX (B,H,NC,64,64), dS0 (B,H,D,D) or None), fp32. dW / dsent / dsfin may be None (no gradient arrived)."""
+    need_cuda(k, v, la, be, X, sent)
+    B, H, T, D = k.shape
+    NC = X.shape[2]
+    k = _io(k).contiguous()
+    v = v.to(k.dtype).contiguous()
+    la, be = _f32c(la), _f32c(be)
+    X, sent = X.to(torch.bfloat16).contiguous(), sent.to(torch.bfloat16).contiguous()
+    dW, dsent, dsfin = (None if t is None else _f32c(t) for t in (dW, dsent, dsfin))
+    Pn = D // 64
+    f = dict(device=k.device, dtype=torch.float32)
+    dkp, dv = torch.empty(Pn, B, H, T, D, **f), torch.empty(B, H, T, D, **f)
+    dlap, dbep = torch.empty(Pn, B, H, T, **f), torch.empty(Pn, B, H, T, **f)
+    dXp = torch.empty(Pn, B, H, NC, CHUNK, CHUNK, **f)
+    ds0 = torch.empty(B, H, D, D, **f) if want_ds0 else None
+    check(lib().pgb_delta_loop_bwd(ptr(k), ptr(v), dtype_code(k), ptr(la), ptr(be), ptr(X), ptr(sent), ptr(dW), ptr(dsent), ptr(dsfin),
+                                   ptr(dkp), ptr(dv), ptr(dlap), ptr(dbep), ptr(dXp), ptr(ds0), B, H, T, D, stream_of(k)),
+          "pgb_delta_loop_bwd")
+    return dkp.sum(0), dv, dlap.sum(0), dbep.sum(0), dXp.sum(0), ds0
 
 
 # ---------------------------------------------------------------------------------------------------------- layer options

@@ -245,3 +245,28 @@ def test_compiled_layer_has_no_graph_break_and_matches_eager(delta):
         c = torch.compile(layer, fullgraph=True)(h)
         for a, b in zip(e, c):
             assert torch.equal(a, b) if not delta else rel_err(a.float(), b.float()) <= 4e-3
+
+
+@pytest.mark.parametrize("delta", [False, True])
+def test_scan_kernels_are_differentiable_by_their_drop_in_names(delta):
+    """assoc_scan_kernel / delta_scan_kernel with requires_grad inputs compose the differentiable operators (the reference's
+    own composition, src/assoc_kernel.py:302-323, 512-546) and give the gradients of the CPU oracle's chunked scan
+    (tests/test_assoc.py:158-163, 174-185 check the same five / six gradients)."""
+    from pragnosia_b200.assoc_kernel import assoc_scan_kernel, delta_scan_kernel
+    B, H, T, D = 2, 2, 150, 64
+    x = synth.assoc_op_inputs(B, H, T, D, seed=8, delta=delta, with_state=True)
+    names = ("q", "k", "v", "la", "S0") + (("beta",) if delta else ())
+    with torch.enable_grad():
+        ref = {n: (x[n].to(torch.bfloat16).double() if n in "qkv" else x[n].double()).requires_grad_(True) for n in names}
+        o_r, s_r = oracle.assoc_scan(ref["q"], ref["k"], ref["v"], ref["la"], ref["S0"], beta=ref.get("beta"))
+        (o_r.square().sum() + s_r.square().sum()).backward()
+        dev = {n: (x[n].to(torch.bfloat16) if n in "qkv" else x[n]).to(DEV).requires_grad_(True) for n in names}
+        if delta:
+            o, S, sent = delta_scan_kernel(dev["q"], dev["k"], dev["v"], dev["la"], dev["beta"], dev["S0"])
+        else:
+            o, S, sent = assoc_scan_kernel(dev["q"], dev["k"], dev["v"], dev["la"], dev["S0"])
+        assert o.dtype == torch.bfloat16 and tuple(sent.shape) == (B, H, 3, D, D)
+        (o.float().square().sum() + S.square().sum()).backward()
+    for n in names:
+        e = rel_err(dev[n].grad.float().cpu(), ref[n].grad.float())
+        assert e <= 4e-2, (n, e)

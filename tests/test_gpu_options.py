@@ -191,3 +191,32 @@ def _split_operator_gradients(D, T, io):
     for n in names:
         e = rel_err(dev_in[n].grad.float().cpu(), ref_in[n].grad.float())
         assert e <= tol, (n, e)
+
+
+@pytest.mark.parametrize("D,T,io", [(64, 200, torch.float32), (128, 130, torch.float32), (64, 333, torch.bfloat16)])
+def test_delta_rule_trains_through_the_split_operators(D, T, io):
+    """delta_inv and delta_loop_fwd carry the reference's backward kernels (src/assoc_kernel.py:390-507, 626-656): the
+    gradients of the delta-rule scan composed as the reference composes it (inverse, walk, assoc_out on the residuals),
+    against autograd through the CPU oracle's chunked scan."""
+    with torch.enable_grad():
+        B, H = 2, 2
+        x = synth.assoc_op_inputs(B, H, T, D, seed=6, delta=True, with_state=True)
+        w_o = torch.randn(B, H, T, D, generator=torch.Generator().manual_seed(1))
+        w_s = torch.randn(B, H, D, D, generator=torch.Generator().manual_seed(2)) * 0.1
+        names = ("q", "k", "v", "la", "beta", "S0")
+        ref_in = {n: (x[n].to(torch.bfloat16).double() if n in "qkv" else x[n].double()).requires_grad_(True) for n in names}
+        o_ref, s_ref = oracle.assoc_scan(ref_in["q"], ref_in["k"], ref_in["v"], ref_in["la"], ref_in["S0"], beta=ref_in["beta"])
+        ((o_ref * w_o).sum() + (s_ref * w_s).sum()).backward()
+
+        # q, k, v on the bf16 grid in both runs (delta_inv takes k in bf16); the op I/O dtype is io
+        dev_in = {n: (x[n].to(torch.bfloat16).to(io) if n in "qkv" else x[n]).to(DEV).requires_grad_(True) for n in names}
+        q, k, v, la, be, S0 = (dev_in[n] for n in names)
+        NC = (T + 63) // 64
+        X = ops.delta_inv(k, la, be, NC)
+        W, sent, sfin = ops.delta_loop_fwd(k, v, la, be, X, S0)
+        o = ops.assoc_out(q, k, W, la, sent)
+        ((o.float() * w_o.to(DEV)).sum() + (sfin * w_s.to(DEV)).sum()).backward()
+        assert rel_err(o.detach().float().cpu(), o_ref.detach().float()) <= 2e-2
+        for n in names:                                               # X, W and the states between the operators travel as bf16
+            e = rel_err(dev_in[n].grad.float().cpu(), ref_in[n].grad.float())
+            assert e <= 3e-2, (n, e)
