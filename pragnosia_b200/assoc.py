@@ -135,6 +135,8 @@ class AssocCarrier(nn.Module):
         B, T, D = z.shape
         H, dk, d = self.h, self.dk, self.d
         sconv = getattr(self, "sconv", None)
+        if T > 1 and torch.is_grad_enabled() and (z.requires_grad or any(p.requires_grad for p in self.parameters())):
+            return self._mix_train(z, h0)
         S0, p0, cc = None, 0, None
         if h0 is not None:
             S0, p0 = h0[0], h0[1]
@@ -180,6 +182,34 @@ class AssocCarrier(nn.Module):
         else:
             p_new = T
         return delta, ((S, p_new, cc) if sconv is not None else (S, p_new))
+
+    def _mix_train(self, z, h0):
+        """The layer with a gradient wanted (the reference's training path, src/assoc.py:384-512 with its kernels on):
+        separate projections of the live parameters, the differentiable prep / scan operators (their backward kernels are
+        the reference's six), torch for the rest. Plain rule and delta rule with hl_floor / write_all / beta_scale /
+        pos_wrap; a carried state must come with position 0."""
+        from .assoc_kernel import assoc_scan_kernel, delta_scan_kernel, prep_kernel
+        if getattr(self, "sconv", None) is not None or self.key_topk:
+            raise NotImplementedError("training path: short convolution and key_topk are inference-only here")
+        B, T, D = z.shape
+        H, dk = self.h, self.dk
+        S0 = None
+        if h0 is not None:
+            S0, p0 = h0[0], h0[1]
+            if torch.is_tensor(p0) or p0 != 0:
+                raise NotImplementedError("training path: the carried state must be at position 0")
+        qp, kp, vp = (lin(z).view(B, T, H, dk) for lin in (self.q, self.k, self.v))
+        gl = None if (self.delta or self.write_all) else self.wi(z)
+        q, k, v = prep_kernel(qp, kp, vp, gl, self.theta, self._positions(T, z.device))
+        la = self.logalpha(z).float().transpose(1, 2)
+        if self.delta:
+            beta = self._beta(self.wb(z)).transpose(1, 2)
+            o, S, sent = delta_scan_kernel(q, k, v, la, beta, S0)
+        else:
+            o, S, sent = assoc_scan_kernel(q, k, v, la, S0)
+        self.sent = sent if self.need_sent else None
+        o = self.on(o.to(z.dtype)).transpose(1, 2).reshape(B, T, D)
+        return F.linear(o, (self.o.weight.float() * torch.sigmoid(self.gate.float())).to(z.dtype)), (S, T)
 
     def _la(self, a_logit, c):
         """log alpha (B,T,H) fp32 from the decay gate's logits, floored per head when hl_floor is set."""
