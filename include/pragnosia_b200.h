@@ -340,10 +340,12 @@ int pgb_batch_linear(const void *x, const void *W, const void *bias, void *y, in
  *     partial row sums (sum, sum of squares) row_sums_in [parts_in][B][2] that the kernel producing x left behind;
  *   residual (resid [B][N] bf16): y = resid + act(x W^T + b) with the separate ops' roundings, i.e. the new residual
  *     stream, and row_sums_out [pgb_batch_linear_parts(N)][B][2] receives each CTA's partial row sums of y.
- * pgb_decode_embed_ex writes the row sums of the embedding (one part) for the first layer's folded norm. */
+ * pgb_decode_embed_ex writes the row sums of the embedding (one part) for the first layer's folded norm.
+ * The kernel requests W, bias, c1 and c2 before it waits for the kernel ahead of it on the stream: they must be complete
+ * before that kernel was launched, or flags must carry PGB_SKINNY_FRESH_CONSTANTS (then nothing is read before the wait). */
 int pgb_batch_linear_ex(const void *x, const void *W, const void *bias, void *y, int B, int N, int K, int act, const float *row_sums_in,
                         int parts_in, const float *c1, const float *c2, int norm_kind, float eps, const void *resid, float *row_sums_out,
-                        void *stream);
+                        int flags, void *stream);
 int pgb_batch_linear_parts(int N);
 int pgb_decode_embed_ex(const long long *tok, const long long *pos, const void *E, const void *P, void *x, float *row_sums, int B, int d,
                         int vocab, int ctx, void *stream);

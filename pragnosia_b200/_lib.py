@@ -37,7 +37,7 @@ SIGNATURES = {
     "pgb_decode_sample": [_vp, _i, _f, C.c_ulonglong, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "pgb_decode_sample_ex": [_vp, _i, _f, _f, C.c_ulonglong, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     "pgb_batch_linear": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
-    "pgb_batch_linear_ex": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp, _i, _f, _vp, _vp, _vp],
+    "pgb_batch_linear_ex": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp, _vp, _i, _f, _vp, _vp, _i, _vp],
     "pgb_batch_linear_parts": [_i],
     "pgb_decode_embed_ex": [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "pgb_decode_token_work_bytes": [_i, _i, _i, _i],

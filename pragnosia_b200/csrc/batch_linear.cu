@@ -35,6 +35,7 @@ constexpr int BL_NT = 6 * 32;                                         // produce
 struct BlFused {
     const float *stats_in; int parts_in; const float *c1, *c2; int norm_kind; float eps;
     const __nv_bfloat16 *resid; float *stats_out;
+    int late_consts;                 // W, bias, c1, c2 may be the output of the kernel just ahead: read nothing before the wait
 };
 
 // One ring of stages in shared memory, a stage = one x tile (64 K-columns of every row) and one slab of W, up to 16 stages
@@ -93,15 +94,20 @@ __global__ void __launch_bounds__(BL_NT, 1) batch_linear_kernel(const __grid_con
         // ------------------------------------------------------------------------------------------ producer
         const bool leader = bl_elect_one();
         const int pre = KB < STAGES ? KB : STAGES;
-        if (leader) {
-            for (int kb = 0; kb < pre; ++kb) {                        // the weight slabs do not depend on the kernel ahead
+        // The weight slabs do not depend on the kernel ahead -- unless the caller says that kernel produced them (a cast, a
+        // copy made contiguous just now): then they are requested after the wait like x.
+        auto request_w = [&]() {
+            for (int kb = 0; kb < pre; ++kb) {
                 mbar_expect_tx(bar_full(kb), STAGE);
                 bl_tma_2d(base + kb * STAGE + A_BYTES, &mw, bar_full(kb), kb * BL_BK, n0);
             }
-        }
+        };
+        if (leader && !f.late_consts) request_w();
         pdl_wait();                                                   // x is the kernel ahead's output
-        if (leader)
+        if (leader) {
+            if (f.late_consts) request_w();
             for (int kb = 0; kb < pre; ++kb) bl_tma_2d(base + kb * STAGE, &mx, bar_full(kb), kb * BL_BK, 0);
+        }
         __syncwarp();
         bool ok = true;
         for (int kb = pre; kb < KB && ok; ++kb) {
@@ -140,7 +146,8 @@ __global__ void __launch_bounds__(BL_NT, 1) batch_linear_kernel(const __grid_con
         const int row = BM == 128 ? 32 * sub + lane : (lane < 16 ? 16 * sub + lane : BM);
         const uint32_t lane_base = (uint32_t)(32 * sub) << 16;
         // the CTA's bias values (the same for every row), requested before the accumulator is waited for; the folded norm's
-        // two vectors only as far as the L1
+        // two vectors only as far as the L1 (after the wait on the kernel ahead if it may have produced them)
+        if (f.late_consts) pdl_wait();
         uint4 braw[BN / 8];
 #pragma unroll
         for (int g = 0; g < BN / 8; ++g) {
@@ -260,8 +267,8 @@ int batch_linear_parts(int N) { return (N + 15) / 16; }
 
 int batch_linear_launch(const void *x, const void *W, const void *bias, void *y, int B, int N, int K, int act, const float *stats_in,
                         int parts_in, const float *c1, const float *c2, int norm_kind, float eps, const void *resid, float *stats_out,
-                        cudaStream_t stream) {
-    const BlFused f{stats_in, parts_in, c1, c2, norm_kind, eps, (const __nv_bfloat16 *)resid, stats_out};
+                        int late_consts, cudaStream_t stream) {
+    const BlFused f{stats_in, parts_in, c1, c2, norm_kind, eps, (const __nv_bfloat16 *)resid, stats_out, late_consts};
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     // the narrowest slab that still gives about one CTA per SM: every CTA re-reads x from the L2, so fewer, wider CTAs

@@ -70,7 +70,7 @@ int decode_token_launch(const void *, int, const void *, const void *, const voi
 size_t decode_token_work_bytes(int B, int d, int NP, int dff);
 int decode_token_error_flag(int *);
 int batch_linear_launch(const void *, const void *, const void *, void *, int, int, int, int, const float *, int, const float *, const float *,
-                        int, float, const void *, float *, cudaStream_t);
+                        int, float, const void *, float *, int, cudaStream_t);
 int batch_linear_parts(int N);
 int batch_linear_error_flag(int *);
 int decode_token_wait_selftest_launch(unsigned long long *, unsigned, cudaStream_t);
@@ -448,10 +448,10 @@ int pgb_linear_act(const void *x, const void *W, const void *bias, void *y, long
 
 int pgb_batch_linear_ex(const void *x, const void *W, const void *bias, void *y, int B, int N, int K, int act, const float *row_sums_in,
                         int parts_in, const float *c1, const float *c2, int norm_kind, float eps, const void *resid, float *row_sums_out,
-                        void *stream) {
+                        int flags, void *stream) {
     if (!x || !W || !y) return PGB_ERR_NULL_POINTER;
     if (act < 0 || act > 1 || B < 1 || N < 8 || K < 8 || (N % 8) != 0 || (K % 8) != 0) return PGB_ERR_BAD_SHAPE;
-    if (norm_kind < 0 || norm_kind > 2 || parts_in < 0) return PGB_ERR_BAD_SHAPE;
+    if (norm_kind < 0 || norm_kind > 2 || parts_in < 0 || (flags & ~PGB_SKINNY_FRESH_CONSTANTS)) return PGB_ERR_BAD_SHAPE;
     if (norm_kind != 0 && (!row_sums_in || !c1 || !c2 || parts_in < 1 || bias)) return PGB_ERR_NULL_POINTER;   // the folded norm's c2 carries the bias
     if (B > 128) return PGB_ERR_TOO_LARGE;                            // the batch is one 128-row tensor-core tile
     if (!aligned(x, 16) || !aligned(W, 16) || !aligned(y, 16) || (bias && !aligned(bias, 16)) || (resid && !aligned(resid, 16)) ||
@@ -459,11 +459,11 @@ int pgb_batch_linear_ex(const void *x, const void *W, const void *bias, void *y,
         (row_sums_out && !aligned(row_sums_out, 8)))
         return PGB_ERR_MISALIGNED;
     return batch_linear_launch(x, W, bias, y, B, N, K, act, row_sums_in, parts_in, c1, c2, norm_kind, eps, resid, row_sums_out,
-                               (cudaStream_t)stream);
+                               (flags & PGB_SKINNY_FRESH_CONSTANTS) ? 1 : 0, (cudaStream_t)stream);
 }
 
 int pgb_batch_linear(const void *x, const void *W, const void *bias, void *y, int B, int N, int K, int act, void *stream) {
-    return pgb_batch_linear_ex(x, W, bias, y, B, N, K, act, nullptr, 0, nullptr, nullptr, 0, 0.f, nullptr, nullptr, stream);
+    return pgb_batch_linear_ex(x, W, bias, y, B, N, K, act, nullptr, 0, nullptr, nullptr, 0, 0.f, nullptr, nullptr, 0, stream);
 }
 
 int pgb_batch_linear_parts(int N) { return N < 1 ? 0 : batch_linear_parts(N); }

@@ -470,8 +470,10 @@ def batch_linear(x, W, bias=None, act: Optional[str] = None, folded=None, resid=
         raise ValueError("batch_linear: bf16, x (B,K)")
     B, K = x.shape
     N = W.shape[0]
-    x, W = x.contiguous(), W.contiguous()
-    b = None if bias is None else bias.to(x.dtype).contiguous()
+    x = x.contiguous()
+    W, fresh = _cast_once(W, x.dtype)
+    b, f2 = _cast_once(bias, x.dtype)
+    fresh = fresh or f2                                              # a constant made by a kernel just now: tell the launch
     y = torch.empty(B, N, device=x.device, dtype=x.dtype)
     sums_in, parts_in, c1, c2, kind, eps = None, 0, None, None, 0, 0.0
     if folded is not None:
@@ -485,7 +487,8 @@ def batch_linear(x, W, bias=None, act: Optional[str] = None, folded=None, resid=
         if want_sums:
             sums_out = torch.empty(int(lib().pgb_batch_linear_parts(N)), B, 2, device=x.device, dtype=torch.float32)
     check(lib().pgb_batch_linear_ex(ptr(x), ptr(W), ptr(b), ptr(y), B, N, K, 1 if act == "gelu" else 0, ptr(sums_in), parts_in, ptr(c1),
-                                    ptr(c2), int(kind), float(eps), ptr(resid), ptr(sums_out), stream_of(x)), "pgb_batch_linear")
+                                    ptr(c2), int(kind), float(eps), ptr(resid), ptr(sums_out), 1 if fresh else 0, stream_of(x)),
+          "pgb_batch_linear")
     return (y, sums_out) if want_sums else y
 
 

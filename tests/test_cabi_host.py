@@ -137,7 +137,8 @@ def test_new_entry_points_reject_bad_calls(L):
     assert L.pgb_assoc_out_bwd(one, one, one, 0, one, one, one, one, one, one, one, one, 1, 1, 8, 96, None) == 3
     assert L.pgb_prefix_scan_bwd(one, one, 7, one, one, one, None, None, one, one, one, one, None, 1, 1, 1, 64, None) == 5
     assert L.pgb_batch_linear(one, one, None, one, 129, 16, 64, 0, None) == 7 and L.pgb_batch_linear(one, one, None, one, 4, 12, 64, 0, None) == 2
-    assert L.pgb_batch_linear_ex(one, one, one, one, 4, 16, 64, 0, one, 1, one, one, 1, 1e-5, None, None, None) == 1   # folded norm + bias
+    assert L.pgb_batch_linear_ex(one, one, one, one, 4, 16, 64, 0, one, 1, one, one, 1, 1e-5, None, None, 0, None) == 1   # folded norm + bias
+    assert L.pgb_batch_linear_ex(one, one, None, one, 4, 16, 64, 0, None, 0, None, None, 0, 0.0, None, None, 2, None) == 2  # unknown flag
     assert L.pgb_batch_linear_parts(768) == 48
     # the one-launch decode step: scratch size, then the rejects (bias missing for a layer norm, short scratch, batch, head dim)
     assert L.pgb_decode_token_work_bytes(1, 768, 2328, 3072) == 2 * (4 * 768 + 2328 + 3072)
