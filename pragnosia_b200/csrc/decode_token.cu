@@ -18,14 +18,14 @@
 // matrix-vector product per sequence: a warp owns groups of output rows (dealt round-robin over the grid's warps), keeps
 // a dozen 128-bit pieces of them in flight, and meets each piece with the same piece of every sequence's normalised row
 // held in shared memory. What a phase costs is a chain of dependent memory round trips, so everything that does not
-// depend on the previous phase is requested BEFORE the barrier that ends it: the first weights of the coming phase, the
-// norm vectors, the state slice of the recurrent step. Roundings sit where the separate ops put them (the residual sum,
-// the normalised row, every linear output and the pre-activation are bf16), and the accumulation order of every dot
-// product is the one of skinny_linear.cu.
+// depend on the previous phase is requested between the two halves of the barrier that ends it (arrive, then wait): the
+// first weights of the coming phase and their bias, the state slice of the recurrent step. Roundings sit where the
+// separate ops put them (the residual sum, the normalised row, every linear output and the pre-activation are bf16), and
+// the accumulation order of every dot product is the one of skinny_linear.cu.
 //
 // The barrier is one 64-bit arrival counter in global memory that only ever grows (nothing to reset between launches;
-// the second word of the pair is reserved). Its wait is bounded: a CTA that gives up raises a flag every other waiter also watches, so the
-// kernel winds down within about a second instead of hanging, and the host reads the flag.
+// the second word of the pair is reserved). Its wait is bounded: a CTA that gives up raises a flag every other waiter
+// also watches, so the kernel winds down within about a second instead of hanging, and the host reads the flag.
 #include "decode_step.cuh"
 
 namespace pgb {
@@ -55,7 +55,7 @@ struct DtArgs {
     const float *shift;
     __nv_bfloat16 *xa, *xb, *y, *o, *hmid, *dl;
     float *logits;
-    unsigned long long *sync;                                         // [0] arrivals, [1] generation
+    unsigned long long *sync;                                         // [0] arrivals, [1] reserved
     int L, B, d, H, NP, dff, V, ctx, fn_kind;
     float fn_eps;
 };
@@ -279,7 +279,7 @@ __device__ __noinline__ bool dt_phase_rb(const DtArgs &a, const DtRows &rw, bool
     const int nchunks = (K8 + 32 * U - 1) / (32 * U);
     const int first = blockIdx.x * DT_WARPS + warp;
     uint4 *wb = wstage + warp * DT_STAGE_U4 + lane;
-    float bias_q[DT_DEPTH] = {0.f, 0.f, 0.f};                                     // of the output this lane will finish, requested with the weights
+    float bias_q[DT_DEPTH] = {0.f, 0.f, 0.f};                         // of the output this lane will finish, requested with the weights
     // the items in order, walked by two cursors (requests ahead, multiplications behind) with no division in sight
     int ig = first, ic = 0, issued = 0;                               // next item to request: group, chunk; items requested so far
     auto issue = [&](int buf) {

@@ -1,7 +1,7 @@
 // Backward of the split operators (the reference's _bwd_chunk, src/assoc_kernel.py:75-126, _prefix_bwd, :206-228,
 // _delta_loop_bwd, :390-507, and _inv_bwd, :626-656, with their register_autograd wiring at :179, :299, :509, :704), so that
-// code written against membrae::assoc_out / prefix_scan / delta_loop_fwd / delta_inv can train through this library. Like the forward kernels in split_ops.cu
-// these are plain fp32 FFMA kernels built for exactness, not speed; every gradient leaves in fp32 and every sum is taken
+// code written against membrae::assoc_out / prefix_scan / delta_loop_fwd / delta_inv can train through this library.
+// Like the forward kernels in split_ops.cu these are plain fp32 FFMA kernels built for exactness, not speed; every gradient leaves in fp32 and every sum is taken
 // in a fixed order (no atomics).
 //
 // assoc_out   o_t = sum_{s<=t} (q_t.k_s) e^{L_t-L_s} v_s + e^{L_t} q_t S,   L = inclusive cumulative sum of la in the chunk
