@@ -127,7 +127,7 @@ int pgb_assoc_out_fwd(const void *q, const void *k, const void *v, int io_dtype,
                       int H, int T, int D, void *stream);
 int pgb_prefix_scan_fwd(const void *k, const void *v, int io_dtype, const float *w, const float *a_log, const float *S0, void *sent,
                         float *sfin, int B, int H, int NC, int D, void *stream);
-/* Backward of the two plain-rule operators above (src/assoc_kernel.py:75-126 _bwd_chunk, :206-228 _prefix_bwd, wired with
+/* Backward of the two plain-rule operators above (src/assoc_kernel.py:75-126 _bwd_chunk, :206-221 _prefix_bwd, wired with
  * register_autograd at :179 and :299). Every gradient is fp32; sums are taken in a fixed order.
  *   pgb_assoc_out_bwd:   dout [B][H][T][D] (io dtype) -> dq, dk, dv [B][H][T][D], dla [B][H][T], dsent [B][H][NC][D][D].
  *   pgb_prefix_scan_bwd: dsent [B][H][NC][D][D] and dsfin [B][H][D][D] (either may be NULL = zero), sent = the forward's
@@ -137,7 +137,7 @@ int pgb_assoc_out_bwd(const void *q, const void *k, const void *v, int io_dtype,
 int pgb_prefix_scan_bwd(const void *k, const void *v, int io_dtype, const float *w, const float *a_log, const void *sent,
                         const float *dsent, const float *dsfin, float *dk, float *dv, float *dw, float *da_log, float *dS0, int B, int H,
                         int NC, int D, void *stream);
-/* Backward of the two delta-rule operators below (src/assoc_kernel.py:390-507 _delta_loop_bwd, :626-656 _inv_bwd, wired with
+/* Backward of the two delta-rule operators below (src/assoc_kernel.py:390-459 _delta_loop_bwd, :626-656 _inv_bwd, wired with
  * register_autograd at :509 and :704). fp32 gradients, fixed summation order.
  *   pgb_delta_inv_bwd:  dX [B][H][NC][64][64] -> dk [B][H][T][D], dla, dbeta [B][H][T].
  *   pgb_delta_loop_bwd: dW [B][H][T][D], dsent [B][H][NC][D][D], dsfin [B][H][D][D] (each may be NULL = zero); sent = the

@@ -1,5 +1,5 @@
-// Backward of the split operators (the reference's _bwd_chunk, src/assoc_kernel.py:75-126, _prefix_bwd, :206-228,
-// _delta_loop_bwd, :390-507, and _inv_bwd, :626-656, with their register_autograd wiring at :179, :299, :509, :704), so that
+// Backward of the split operators (the reference's _bwd_chunk, src/assoc_kernel.py:75-126, _prefix_bwd, :206-221,
+// _delta_loop_bwd, :390-459, and _inv_bwd, :626-656, with their register_autograd wiring at :179, :299, :509, :704), so that
 // code written against membrae::assoc_out / prefix_scan / delta_loop_fwd / delta_inv can train through this library.
 // Like the forward kernels in split_ops.cu these are plain fp32 FFMA kernels built for exactness, not speed; every gradient leaves in fp32 and every sum is taken
 // in a fixed order (no atomics).
@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(SB_NT) delta_inv_bwd_kernel(const TIO *__restr
 // Forward per chunk:  rhs = beta (v - e^L (k S));  W = X rhs;  S' = e^{L_C} S + (k w)^T W,  w_s = e^{L_C - L_s}.
 // One CTA per (sequence-head, 64 value columns) walks the chunks backwards with G = dLoss/dS' (its columns) in shared
 // memory. Sums over value columns (dk, dla, dbeta, dX) leave as one partial per column slab; the caller adds the slabs.
-// (the reference's _delta_loop_bwd, src/assoc_kernel.py:390-507, wired at :509)
+// (the reference's _delta_loop_bwd, src/assoc_kernel.py:390-459, wired at :509)
 template <typename TIO, int D>
 __global__ void __launch_bounds__(SB_NT) delta_loop_bwd_kernel(const TIO *__restrict__ k, const TIO *__restrict__ v, const float *__restrict__ la,
                                                                const float *__restrict__ be, const __nv_bfloat16 *__restrict__ X,

@@ -231,7 +231,7 @@ def _prefix_setup(ctx, inputs, output):
 
 
 def _prefix_backward(ctx, dsent, dsfin):
-    """The reference's _prefix_bwd (src/assoc_kernel.py:206-228, wired at :299)."""
+    """The reference's _prefix_bwd (src/assoc_kernel.py:206-221, wired at :299)."""
     k, v, w, a_log, sent = ctx.saved_tensors[:5]
     dk, dv, dw, da, ds0 = prefix_scan_bwd(k, v, w, a_log, sent, None if dsent is None else dsent.contiguous(),
                                           None if dsfin is None else dsfin.contiguous(), ctx.has_s0)
@@ -313,7 +313,7 @@ def _loop_setup(ctx, inputs, output):
 
 
 def _loop_backward(ctx, dW, dsent, dsfin):
-    """The reference's _delta_loop_bwd (src/assoc_kernel.py:390-507, wired at :509)."""
+    """The reference's _delta_loop_bwd (src/assoc_kernel.py:390-459, wired at :509)."""
     k, v, la, be, X, sent = ctx.saved_tensors[:6]
     c = lambda t: None if t is None else t.contiguous()
     dk, dv, dla, dbe, dX, ds0 = delta_loop_bwd(k, v, la, be, X, sent, c(dW), c(dsent), c(dsfin), ctx.has_s0)

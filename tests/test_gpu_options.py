@@ -157,7 +157,7 @@ def test_min_p_sampling():
 
 @pytest.mark.parametrize("D,T,io", [(64, 200, torch.float32), (128, 130, torch.float32), (64, 333, torch.bfloat16)])
 def test_plain_rule_trains_through_the_split_operators(D, T, io):
-    """assoc_out and prefix_scan carry the reference's backward kernels (src/assoc_kernel.py:75-126, 206-228): the
+    """assoc_out and prefix_scan carry the reference's backward kernels (src/assoc_kernel.py:75-126, 206-221): the
     gradients of the plain-rule scan composed from them, against autograd through the CPU oracle's chunked scan."""
     with torch.enable_grad():
         _split_operator_gradients(D, T, io)
@@ -195,7 +195,7 @@ def _split_operator_gradients(D, T, io):
 
 @pytest.mark.parametrize("D,T,io", [(64, 200, torch.float32), (128, 130, torch.float32), (64, 333, torch.bfloat16)])
 def test_delta_rule_trains_through_the_split_operators(D, T, io):
-    """delta_inv and delta_loop_fwd carry the reference's backward kernels (src/assoc_kernel.py:390-507, 626-656): the
+    """delta_inv and delta_loop_fwd carry the reference's backward kernels (src/assoc_kernel.py:390-459, 626-656): the
     gradients of the delta-rule scan composed as the reference composes it (inverse, walk, assoc_out on the residuals),
     against autograd through the CPU oracle's chunked scan."""
     with torch.enable_grad():
