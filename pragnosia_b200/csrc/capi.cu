@@ -59,6 +59,7 @@ int decode_sample_launch(const void *, int, float, float, unsigned long long, lo
                          unsigned int *, int, int, int, cudaStream_t);
 int linear_gelu_launch(const void *, const void *, const void *, void *, long long, int, int, int, cudaStream_t);
 int linear_gelu_error_flag(int *);
+int linear_gelu_set_variant(int);
 int skinny_linear_launch(const void *, const void *, const void *, const void *, int, float, const void *, const void *, int, void *,
                          void *, int, int, int, int, cudaStream_t);
 int add_norm_launch(const void *, const void *, const void *, const void *, float, int, void *, void *, long long, int, int,
@@ -445,6 +446,8 @@ int pgb_linear_act(const void *x, const void *W, const void *bias, void *y, long
     if (!aligned(x, 16) || !aligned(W, 16) || !aligned(y, 16) || (bias && !aligned(bias, 16))) return PGB_ERR_MISALIGNED;
     return linear_gelu_launch(x, W, bias, y, M, N, K, act, (cudaStream_t)stream);
 }
+
+int pgb_linear_act_set_variant(int variant) { return linear_gelu_set_variant(variant); }
 
 int pgb_batch_linear_ex(const void *x, const void *W, const void *bias, void *y, int B, int N, int K, int act, const float *row_sums_in,
                         int parts_in, const float *c1, const float *c2, int norm_kind, float eps, const void *resid, float *row_sums_out,

@@ -51,6 +51,48 @@ __device__ __forceinline__ bool elect_one() {
     return e != 0;
 }
 
+// One epilogue warp's share of a tile: 32 accumulator rows (tensor-memory lanes of the warp's subpartition) x 64 columns
+// starting at tensor-memory address tacc, to y rows row0.. and columns n0.. . bias2: this lane's packed pair of the 64 bias
+// values. stage_out: the warp's 2 KiB staging block.
+__device__ __forceinline__ void lg_epilogue_block(uint32_t tacc, uint32_t bias2, uint8_t *stage_out, __nv_bfloat16 *__restrict__ y,
+                                                  long long row0, int n0, long long M, int N, int act, int lane) {
+    float v[2][32];
+    tmem_ld32_nowait(tacc, v[0]);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        tmem_ld_wait();
+        if (h == 0) tmem_ld32_nowait(tacc + 32, v[1]);                 // lands under the arithmetic below
+        const int col = n0 + 32 * h;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {                                  // 8 columns = one 16-byte store
+            uint4 outv;
+            __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(&outv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t braw = __shfl_sync(0xffffffffu, bias2, 16 * h + 4 * g + i);
+                const float2 bv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&braw));
+                // the pre-activation, rounded to bf16 as the separate Linear would hand it on
+                const float2 x = __bfloat1622float2(__floats2bfloat162_rn(v[h][8 * g + 2 * i] + bv.x, v[h][8 * g + 2 * i + 1] + bv.y));
+                o2[i] = act == 1 ? __floats2bfloat162_rn(lg_gelu(x.x), lg_gelu(x.y)) : __floats2bfloat162_rn(x.x, x.y);
+            }
+            // into the warp's staging block: row = lane, 16-byte piece g, pieces rotated by the row so that both this
+            // write and the read-back below touch every bank once per 128 bytes
+            *reinterpret_cast<uint4 *>(stage_out + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = outv;
+        }
+        __syncwarp();
+        // the block leaves as whole 64-byte row segments, eight rows per store instruction: a thread-per-row store
+        // would touch 32 lines per instruction and the load/store unit, not memory, would set the epilogue's pace
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = 8 * i + (lane >> 2), pc = lane & 3;
+            const uint4 val = *reinterpret_cast<const uint4 *>(stage_out + r * 64 + ((pc ^ ((r >> 1) & 3)) << 4));
+            const long long grow = row0 + r;
+            if (grow < M && col + 8 * pc < N) *reinterpret_cast<uint4 *>(y + (size_t)grow * N + col + 8 * pc) = val;
+        }
+        __syncwarp();
+    }
+}
+
 __global__ void __launch_bounds__(LG_NT, 1) linear_gelu_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant__ CUtensorMap mw,
                                                               const __nv_bfloat16 *__restrict__ bias, __nv_bfloat16 *__restrict__ y,
                                                               long long M, int N, int K, int act) {
@@ -143,41 +185,7 @@ __global__ void __launch_bounds__(LG_NT, 1) linear_gelu_kernel(const __grid_cons
             ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full(a), (ti >> 1) & 1, 74));
             if (!ok) break;
             tc_fence_after();
-            float v[2][32];
-            tmem_ld32_nowait(tmem + lane_base + a * LG_BN + part * CW, v[0]);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                tmem_ld_wait();
-                if (h == 0) tmem_ld32_nowait(tmem + lane_base + a * LG_BN + part * CW + 32, v[1]);   // lands under the arithmetic below
-                const int col = n0 + 32 * h;
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {                          // 8 columns = one 16-byte store
-                    uint4 outv;
-                    __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(&outv);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const uint32_t braw = __shfl_sync(0xffffffffu, bias2, 16 * h + 4 * g + i);
-                        const float2 bv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&braw));
-                        // the pre-activation, rounded to bf16 as the separate Linear would hand it on
-                        const float2 x = __bfloat1622float2(__floats2bfloat162_rn(v[h][8 * g + 2 * i] + bv.x, v[h][8 * g + 2 * i + 1] + bv.y));
-                        o2[i] = act == 1 ? __floats2bfloat162_rn(lg_gelu(x.x), lg_gelu(x.y)) : __floats2bfloat162_rn(x.x, x.y);
-                    }
-                    // into the warp's staging block: row = lane, 16-byte piece g, pieces rotated by the row so that both this
-                    // write and the read-back below touch every bank once per 128 bytes
-                    *reinterpret_cast<uint4 *>(stage_out + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = outv;
-                }
-                __syncwarp();
-                // the block leaves as whole 64-byte row segments, eight rows per store instruction: a thread-per-row store
-                // would touch 32 lines per instruction and the load/store unit, not memory, would set the epilogue's pace
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int r = 8 * i + (lane >> 2), pc = lane & 3;
-                    const uint4 val = *reinterpret_cast<const uint4 *>(stage_out + r * 64 + ((pc ^ ((r >> 1) & 3)) << 4));
-                    const long long grow = row0 + r;
-                    if (grow < M && col + 8 * pc < N) *reinterpret_cast<uint4 *>(y + (size_t)grow * N + col + 8 * pc) = val;
-                }
-                __syncwarp();
-            }
+            lg_epilogue_block(tmem + lane_base + a * LG_BN + part * CW, bias2, stage_out, y, row0, n0, M, N, act, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) lg_arrive(bar_acc_empty(a));
@@ -188,14 +196,239 @@ __global__ void __launch_bounds__(LG_NT, 1) linear_gelu_kernel(const __grid_cons
     if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
+// ------------------------------------------------------------------------------------------------ the pair kernel
+// The same GEMM on pairs of SMs: a cluster of two CTAs computes one 256 x 256 tile with tcgen05.mma.cta_group::2. Each CTA
+// loads its own 128 rows of x and its own 128 rows of W per 64-wide K block (32 KiB instead of the 48 KiB a lone CTA
+// needs for a 128 x 256 tile), the tensor cores of both SMs read the two halves of W from either CTA's shared memory, and
+// each CTA's tensor memory receives its own 128 rows of the tile. A third less operand traffic from the L2 -- what the
+// single-CTA kernel is bound by -- and six 32 KiB stages in flight.
+//   The CTA of cluster rank 0 issues every MMA. Its full[] barriers count the bytes of both CTAs' loads (each CTA's TMA
+//   names rank 0's barrier); a stage is handed back, and an accumulator handed on, by one tcgen05.commit per CTA (the
+//   rank-1 barrier through its cluster address); the epilogue warps of both CTAs arrive on rank 0's acc_empty[] barrier.
+//   No load is shared between the CTAs, so there is no multicast anywhere. Roles, epilogue and the bounded waits are those
+//   of the kernel above; the cluster meets twice more, after set-up and before tensor memory is freed. Results are those
+//   of the kernel above to the bit (the same products accumulated in the same order).
+constexpr int LP_BM = 256, LP_BN = 256, LP_STAGES = 6;
+constexpr int LP_A_BYTES = (LP_BM / 2) * LG_BK * 2, LP_B_BYTES = (LP_BN / 2) * LG_BK * 2, LP_STAGE = LP_A_BYTES + LP_B_BYTES;
+constexpr int LP_SMEM = LP_STAGES * LP_STAGE + 1024 + LG_EPI * LG_OUT_BYTES + 1024;
+static_assert(LP_SMEM <= 232448, "shared memory of the pair kernel");
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// the address, in the cluster's shared window, of this CTA's shared-memory address `addr` in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t cluster_addr(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void lp_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// bounded wait on a barrier of this CTA whose arrivals come from both CTAs of the pair
+__device__ __forceinline__ bool lp_wait_cluster(uint32_t bar, uint32_t parity, int code) {
+    const long long t0 = clock64();
+    do {
+        for (int i = 0; i < 32; ++i) {
+            uint32_t ok;
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+            if (ok) return true;
+        }
+    } while (clock64() - t0 < TC_WAIT_CYCLES);
+    atomicExch(&g_tc_error, code);
+    return false;
+}
+// this CTA's half of a stage; the bytes are counted on `cluster_bar`, a barrier of the pair's first CTA
+__device__ __forceinline__ void lp_tma_load(uint32_t dst, const CUtensorMap *map, uint32_t cluster_bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(0) : "memory");
+}
+__device__ __forceinline__ void lp_mma_elect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "@e tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// one arrival on `cluster_bar` (any CTA of the pair) once every MMA this thread has issued so far is complete
+__device__ __forceinline__ void lp_commit_elect(uint32_t cluster_bar) {
+    asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
+                 "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(cluster_bar) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(LG_NT, 1)
+linear_gelu_pair_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant__ CUtensorMap mw, const __nv_bfloat16 *__restrict__ bias,
+                        __nv_bfloat16 *__restrict__ y, long long M, int N, int K, int act) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;      // the same offset in both CTAs: one descriptor serves both
+    uint8_t *sm = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t mb = base + LP_STAGES * LP_STAGE;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm + LP_STAGES * LP_STAGE + 256);
+    auto bar_full = [&](int s) { return mb + 8 * s; };                 // used in the first CTA only
+    auto bar_empty = [&](int s) { return mb + 64 + 8 * s; };
+    auto bar_acc_full = [&](int a) { return mb + 128 + 8 * a; };
+    auto bar_acc_empty = [&](int a) { return mb + 144 + 8 * a; };      // used in the first CTA only
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t rank = cluster_rank();
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int tiles_n = (N + LP_BN - 1) / LP_BN;
+    const long long tiles = ((M + LP_BM - 1) / LP_BM) * tiles_n;
+    const int KB = (K + LG_BK - 1) / LG_BK;
+
+    if (tid == 0) {
+        for (int s = 0; s < LP_STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(bar_acc_full(a), 1); mbar_init(bar_acc_empty(a), 2 * LG_EPI); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {                                                   // the same warp of both CTAs, the same slot address
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                                // the partner's barriers and tensor memory exist from here on
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    pdl_wait();
+    pdl_launch_dependents();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------------------------------ producer (both CTAs)
+        const bool leader = elect_one();
+        uint32_t it = 0;
+        bool ok = true;
+        for (long long t = pair; t < tiles && ok; t += pairs) {
+            const int m0 = (int)(t / tiles_n) * LP_BM + (int)rank * (LP_BM / 2), n0 = (int)(t % tiles_n) * LP_BN + (int)rank * (LP_BN / 2);
+            for (int kb = 0; kb < KB && ok; ++kb, ++it) {
+                const int s = it % LP_STAGES;
+                if (it >= LP_STAGES) ok = __all_sync(0xffffffffu, mbar_wait(bar_empty(s), ((it / LP_STAGES) + 1) & 1, 75));
+                if (ok && leader) {
+                    const uint32_t sa = base + s * LP_STAGE, full0 = cluster_addr(bar_full(s), 0);
+                    if (rank == 0) mbar_expect_tx(bar_full(s), 2 * LP_STAGE);      // both CTAs' bytes
+                    lp_tma_load(sa, &mx, full0, kb * LG_BK, m0);
+                    lp_tma_load(sa + LP_A_BYTES, &mw, full0, kb * LG_BK, n0);
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------------------------------ MMA issuer (first CTA)
+        if (rank == 0) {
+            constexpr uint32_t IDESC = idesc_bf16(LP_BM, LP_BN, 0, 0);
+            uint32_t it = 0, ti = 0;
+            bool ok = true;
+            for (long long t = pair; t < tiles && ok; t += pairs, ++ti) {
+                const uint32_t a = ti & 1;
+                if (ti >= 2) ok = __all_sync(0xffffffffu, lp_wait_cluster(bar_acc_empty(a), ((ti >> 1) + 1) & 1, 76));
+                tc_fence_after();
+                for (int kb = 0; kb < KB && ok; ++kb, ++it) {
+                    const int s = it % LP_STAGES;
+                    ok = __all_sync(0xffffffffu, lp_wait_cluster(bar_full(s), (it / LP_STAGES) & 1, 77));
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = base + s * LP_STAGE;
+                    const uint64_t da = smem_desc(sa, 16, 1024), db = smem_desc(sa + LP_A_BYTES, 16, 1024);
+#pragma unroll
+                    for (int k = 0; k < LG_BK / 16; ++k) lp_mma_elect(tmem + a * LP_BN, da + k * 2, db + k * 2, IDESC, (kb | k) != 0);
+                    lp_commit_elect(bar_empty(s));                     // the stage is free in both CTAs once these MMAs have read it
+                    lp_commit_elect(cluster_addr(bar_empty(s), 1));
+                }
+                if (ok) {
+                    lp_commit_elect(bar_acc_full(a));
+                    lp_commit_elect(cluster_addr(bar_acc_full(a), 1));
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------------------------------ epilogue (both CTAs)
+        constexpr int CW = LP_BN / (LG_EPI / 4);
+        static_assert(CW == 64, "one packed bias pair per lane covers 64 columns");
+        const int sub = warp & 3, part = (warp - 2) >> 2;
+        const uint32_t lane_base = (uint32_t)(32 * sub) << 16;
+        uint8_t *stage_out = sm + LP_STAGES * LP_STAGE + 1024 + (warp - 2) * LG_OUT_BYTES;
+        uint32_t ti = 0;
+        bool ok = true;
+        for (long long t = pair; t < tiles && ok; t += pairs, ++ti) {
+            const uint32_t a = ti & 1;
+            const long long row0 = (t / tiles_n) * LP_BM + (long long)rank * (LP_BM / 2) + 32 * sub;
+            const int n0 = (int)(t % tiles_n) * LP_BN + part * CW;
+            uint32_t bias2 = 0u;
+            if (bias != nullptr && n0 + 2 * lane < N) bias2 = *reinterpret_cast<const uint32_t *>(bias + n0 + 2 * lane);
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full(a), (ti >> 1) & 1, 78));
+            if (!ok) break;
+            tc_fence_after();
+            lg_epilogue_block(tmem + lane_base + a * LP_BN + part * CW, bias2, stage_out, y, row0, n0, M, N, act, lane);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) lp_arrive_cluster(cluster_addr(bar_acc_empty(a), 0));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                                // neither CTA frees tensor memory the other's MMAs may still write
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+}
+
+// 0: one CTA per 128 x 256 tile; 1: the pair kernel whenever the problem has more than one 128-row block. Timed at the MLP's
+// shape (M 8192, K 768, N 3072, L2 flushed, event resolution 2 us) the pair kernel is ahead without an activation (41 vs
+// 43 us; 20.5 vs 22.5 us at N 768) and behind with the GELU (49 vs 45 us): once the pair has made the mainloop cheaper,
+// the epilogue -- unchanged, and as long as the mainloop -- is what a tile waits for. The model's only use is the one with
+// the GELU, so the single-CTA kernel stays the default.
+static int g_lg_variant = 0;
+int linear_gelu_set_variant(int v) {
+    if (v != 0 && v != 1) return PGB_ERR_BAD_SHAPE;
+    g_lg_variant = v;
+    return PGB_OK;
+}
+
+// clusters of two CTAs of the pair kernel that can be resident at once (cached per device); 0 if the query fails
+static int lp_resident_pairs(int dev) {
+    static int cached[64];
+    static bool have[64];
+    if (dev >= 0 && dev < 64 && have[dev]) return cached[dev];
+    int n = 0, sms = 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(sms > 1 ? sms & ~1 : 2)); cfg.blockDim = dim3(LG_NT); cfg.dynamicSmemBytes = LP_SMEM;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&n, linear_gelu_pair_kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+    if (dev >= 0 && dev < 64) { cached[dev] = n; have[dev] = true; }
+    return n;
+}
+
 int linear_gelu_launch(const void *x, const void *W, const void *bias, void *y, long long M, int N, int K, int act, cudaStream_t stream) {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     CUtensorMap mx, mw;
+    if (g_lg_variant == 1 && M > LG_BM) {
+        cudaError_t e = cudaFuncSetAttribute(linear_gelu_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LP_SMEM);
+        if (e != cudaSuccess) { set_cuda_error(e, "linear_gelu pair smem attribute"); return PGB_ERR_CUDA; }
+        const int room = lp_resident_pairs(dev);
+        if (room > 0) {
+            if (!tc_make_map(&mx, x, 1, M, K, K, (long long)M * K, LP_BM / 2) || !tc_make_map(&mw, W, 1, N, K, K, (long long)N * K, LP_BN / 2)) {
+                set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
+                return PGB_ERR_CUDA;
+            }
+            const long long tiles = ((M + LP_BM - 1) / LP_BM) * ((N + LP_BN - 1) / LP_BN);
+            const unsigned pairs = (unsigned)(tiles < room ? tiles : room);
+            e = pdl_launch(linear_gelu_pair_kernel, dim3(2 * pairs), dim3(LG_NT), (size_t)LP_SMEM, stream, mx, mw, (const __nv_bfloat16 *)bias,
+                           (__nv_bfloat16 *)y, M, N, K, act);
+            if (e != cudaSuccess) { set_cuda_error(e, "linear_gelu pair launch"); return PGB_ERR_CUDA; }
+            return check_launch("linear_gelu_pair_kernel");
+        }
+    }
     if (!tc_make_map(&mx, x, 1, M, K, K, (long long)M * K, LG_BM) || !tc_make_map(&mw, W, 1, N, K, K, (long long)N * K, LG_BN)) {
         set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
         return PGB_ERR_CUDA;
     }
-    int dev = 0, sms = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const long long tiles = ((M + LG_BM - 1) / LG_BM) * ((N + LG_BN - 1) / LG_BN);
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
     cudaError_t e = cudaFuncSetAttribute(linear_gelu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LG_SMEM);
