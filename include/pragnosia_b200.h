@@ -394,10 +394,12 @@ int pgb_decode_token_fwd(const void *layer_table, int L, const void *E, const vo
  * ------------------------------------------------------------------------------------------------------- */
 int pgb_linear_act(const void *x, const void *W, const void *bias, void *y, long long M, int N, int K, int act, void *stream);
 
-/* Which kernel pgb_linear_act uses: 0 (default) = one CTA per 128 x 256 tile; 1 = pairs of SMs share one 256 x 256 tile
+/* Which kernel pgb_linear_act uses. Bit 0: 0 (default) = one CTA per 128-row tile; 1 = pairs of SMs share one 256-row tile
  * (tcgen05.mma.cta_group::2: each CTA of a two-CTA cluster loads half of either operand, no multicast) whenever the
- * problem has more than 128 rows. Same results to the bit. The pair is faster without an activation and slower with the
- * GELU, whose epilogue then sets the pace. Process-wide; for A/B timing and tests. No counterpart in the reference. */
+ * problem has more than 128 rows. Bits 1-2: the tile's width, 0 or 1 = 256 columns (default), 2 = 192. variant in 0..5.
+ * Every choice gives the same results to the bit (and, timed at the MLP's shape, the same speed to within a few percent).
+ * The pair is faster without an activation and slower with the GELU, whose epilogue then sets the pace. Process-wide; for
+ * A/B timing and tests. No counterpart in the reference. */
 int pgb_linear_act_set_variant(int variant);
 
 /* Health check of the tensor-core prefill kernel: every wait inside it is bounded, and a wait that runs out sets a

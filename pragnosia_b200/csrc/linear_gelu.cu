@@ -18,12 +18,24 @@
 
 namespace pgb {
 
-constexpr int LG_BM = 128, LG_BN = 256, LG_BK = 64, LG_STAGES = 4;
+constexpr int LG_BM = 128, LG_BK = 64, LG_STAGES = 4;
 constexpr int LG_EPI = 16;                                            // epilogue warps: four per tensor-memory subpartition
 constexpr int LG_NT = (2 + LG_EPI) * 32;
-constexpr int LG_A_BYTES = LG_BM * LG_BK * 2, LG_B_BYTES = LG_BN * LG_BK * 2, LG_STAGE = LG_A_BYTES + LG_B_BYTES;
-constexpr int LG_OUT_BYTES = 32 * 64;                                 // per epilogue warp: 32 rows x 32 bf16 columns, staged for coalesced stores
-constexpr int LG_SMEM = LG_STAGES * LG_STAGE + 1024 + LG_EPI * LG_OUT_BYTES + 1024;   // stages, barriers, output staging, alignment slack
+constexpr int LG_A_BYTES = LG_BM * LG_BK * 2;
+// The tile is 128 x BN with BN = 256 (the default) or 192 columns. At N = 3072 on 148 SMs, 768 tiles of 256 are 5.2 rounds
+// and pay for 6, 1024 tiles of 192 are 6.9 rounds and pay for 7 three-quarter ones -- and take the same time to within
+// 2 % (39.4 vs 39.9 us), as do 24 epilogue warps in place of 16 (slower by 5 %): neither the rounding of the tile count nor
+// latency inside the epilogue is what the kernel waits for. An epilogue warp owns BN / 4 columns of 32 rows.
+template <int BN, int EPI = LG_EPI>
+struct LgCfg {
+    static constexpr int NT = (2 + EPI) * 32;
+    static constexpr int CW = BN / (EPI / 4);                         // columns per epilogue warp: 64, 48 or 32
+    static constexpr int B_BYTES = BN * LG_BK * 2, STAGE = LG_A_BYTES + B_BYTES;
+    static constexpr int OUT_BYTES = 32 * (CW == 64 ? 32 : CW) * 2;  // per epilogue warp: 32 rows of the columns it stages at a time
+    static constexpr int SMEM = LG_STAGES * STAGE + 1024 + EPI * OUT_BYTES + 1024;   // stages, barriers, output staging, alignment slack
+    static_assert(BN == 256 || BN == 192, "tile width");
+    static_assert(STAGE % 1024 == 0 && SMEM <= 232448, "shared memory");
+};
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
@@ -38,11 +50,13 @@ __device__ __forceinline__ void lg_arrive(uint32_t bar) {
 // no cancellation in either tail (1 + tanh would), and costs a dozen instructions with two special-function issues
 // against about twenty for an erf polynomial.
 __device__ __forceinline__ float lg_gelu(float x) {
-    const float z = fminf(fmaxf(x, -6.0f), 6.0f), z2 = z * z;
-    float p = fmaf(-1.6031776e-05f, z2, -1.6010797e-04f);
-    p = fmaf(p, z2, 3.6451768e-02f);
-    p = fmaf(p, z2, 7.9785311e-01f);
-    const float e = fast_exp2(z * p * -2.8853900817779268f);         // exp(-2 z p(z^2))
+    // the coefficients carry the factor -2 log2(e); the square is clamped, so beyond |x| = 6 the exponent keeps growing with
+    // x and the result goes to x or to -0 as it should
+    const float z2 = fminf(x * x, 36.0f);
+    float p = fmaf(4.6257928e-05f, z2, 4.6197393e-04f);
+    p = fmaf(p, z2, -1.0517757e-01f);
+    p = fmaf(p, z2, -2.3021175e+00f);
+    const float e = fast_exp2(x * p);                                 // exp(-2 x p(x^2))
     return __fdividef(x, 1.0f + e);
 }
 __device__ __forceinline__ bool elect_one() {
@@ -51,51 +65,68 @@ __device__ __forceinline__ bool elect_one() {
     return e != 0;
 }
 
-// One epilogue warp's share of a tile: 32 accumulator rows (tensor-memory lanes of the warp's subpartition) x 64 columns
-// starting at tensor-memory address tacc, to y rows row0.. and columns n0.. . bias2: this lane's packed pair of the 64 bias
-// values. stage_out: the warp's 2 KiB staging block.
+// columns of its block an epilogue warp stages at a time: half of a 64-column block, the whole of a 48-column one
+template <int CW> struct LgStage { static constexpr int cols = CW == 64 ? 32 : CW; };
+
+// One epilogue warp's share of a tile: 32 accumulator rows (tensor-memory lanes of the warp's subpartition) x CW columns
+// starting at tensor-memory address tacc, to y rows row0.. and columns n0.. . bias2: this lane's packed pair of the CW bias
+// values (lanes below CW / 2). stage_out: the warp's staging block, 32 rows of LgStage<CW>::cols bf16.
+//   16 columns at a time, the next 16 on their way from tensor memory while these are processed: + bias, round to bf16
+//   (where the separate Linear would round), GELU in fp32, round; the staged columns then leave as whole row segments
+//   (64 or 96 bytes), several rows per store instruction (a thread-per-row store would touch 32 lines per instruction and
+//   the load/store unit, not memory, would set the epilogue's pace).
+template <int CW>
 __device__ __forceinline__ void lg_epilogue_block(uint32_t tacc, uint32_t bias2, uint8_t *stage_out, __nv_bfloat16 *__restrict__ y,
                                                   long long row0, int n0, long long M, int N, int act, int lane) {
-    float v[2][32];
-    tmem_ld32_nowait(tacc, v[0]);
+    constexpr int SC = LgStage<CW>::cols, NP = SC / 16, RC = SC / 8;   // per staging round: 16-column pieces, 16-byte chunks per row
+    // chunk c of row r: with 64-byte rows the chunks are rotated by the row, so that the row-per-lane writes and the
+    // chunk-per-lane reads both touch every bank once per 128 bytes; 96-byte rows spread by themselves (two ways at worst)
+    auto chunk_at = [&](int r, int c) { return stage_out + r * (2 * SC) + ((SC == 32 ? (c ^ ((r >> 1) & 3)) : c) << 4); };
+    float v[2][16];
+    tmem_ld16_nowait(tacc, v[0]);
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        tmem_ld_wait();
-        if (h == 0) tmem_ld32_nowait(tacc + 32, v[1]);                 // lands under the arithmetic below
-        const int col = n0 + 32 * h;
+    for (int h = 0; h < CW / SC; ++h) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {                                  // 8 columns = one 16-byte store
-            uint4 outv;
-            __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(&outv);
+        for (int q = 0; q < NP; ++q) {
+            constexpr int TOTAL = CW / 16;
+            const int pc = h * NP + q;                                 // piece of the block
+            tmem_ld_wait();
+            if (pc + 1 < TOTAL) tmem_ld16_nowait(tacc + 16 * (pc + 1), v[(pc + 1) & 1]);
+            const float (&a)[16] = v[pc & 1];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t braw = __shfl_sync(0xffffffffu, bias2, 16 * h + 4 * g + i);
-                const float2 bv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&braw));
-                // the pre-activation, rounded to bf16 as the separate Linear would hand it on
-                const float2 x = __bfloat1622float2(__floats2bfloat162_rn(v[h][8 * g + 2 * i] + bv.x, v[h][8 * g + 2 * i + 1] + bv.y));
-                o2[i] = act == 1 ? __floats2bfloat162_rn(lg_gelu(x.x), lg_gelu(x.y)) : __floats2bfloat162_rn(x.x, x.y);
+            for (int g = 0; g < 2; ++g) {                              // 8 columns = one 16-byte chunk
+                uint4 outv;
+                __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(&outv);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t braw = __shfl_sync(0xffffffffu, bias2, 8 * pc + 4 * g + i);
+                    const float2 bv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&braw));
+                    // the pre-activation, rounded to bf16 as the separate Linear would hand it on
+                    const float2 x = __bfloat1622float2(__floats2bfloat162_rn(a[8 * g + 2 * i] + bv.x, a[8 * g + 2 * i + 1] + bv.y));
+                    o2[i] = act == 1 ? __floats2bfloat162_rn(lg_gelu(x.x), lg_gelu(x.y)) : __floats2bfloat162_rn(x.x, x.y);
+                }
+                *reinterpret_cast<uint4 *>(chunk_at(lane, 2 * q + g)) = outv;
             }
-            // into the warp's staging block: row = lane, 16-byte piece g, pieces rotated by the row so that both this
-            // write and the read-back below touch every bank once per 128 bytes
-            *reinterpret_cast<uint4 *>(stage_out + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = outv;
         }
         __syncwarp();
-        // the block leaves as whole 64-byte row segments, eight rows per store instruction: a thread-per-row store
-        // would touch 32 lines per instruction and the load/store unit, not memory, would set the epilogue's pace
+        const int col = n0 + SC * h;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int r = 8 * i + (lane >> 2), pc = lane & 3;
-            const uint4 val = *reinterpret_cast<const uint4 *>(stage_out + r * 64 + ((pc ^ ((r >> 1) & 3)) << 4));
+        for (int k = 0; k < RC; ++k) {
+            const int idx = lane + 32 * k, r = idx / RC, c = idx % RC;
+            const uint4 val = *reinterpret_cast<const uint4 *>(chunk_at(r, c));
             const long long grow = row0 + r;
-            if (grow < M && col + 8 * pc < N) *reinterpret_cast<uint4 *>(y + (size_t)grow * N + col + 8 * pc) = val;
+            if (grow < M && col + 8 * c < N) *reinterpret_cast<uint4 *>(y + (size_t)grow * N + col + 8 * c) = val;
         }
         __syncwarp();
     }
 }
 
-__global__ void __launch_bounds__(LG_NT, 1) linear_gelu_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant__ CUtensorMap mw,
+template <int BN, int EPI>
+__global__ void __launch_bounds__((2 + EPI) * 32, 1) linear_gelu_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant__ CUtensorMap mw,
                                                               const __nv_bfloat16 *__restrict__ bias, __nv_bfloat16 *__restrict__ y,
                                                               long long M, int N, int K, int act) {
+    using CF = LgCfg<BN, EPI>;
+    constexpr int LG_BN = BN, LG_STAGE = CF::STAGE;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *sm = smem_raw + (base - smem_u32(smem_raw));
@@ -113,7 +144,7 @@ __global__ void __launch_bounds__(LG_NT, 1) linear_gelu_kernel(const __grid_cons
 
     if (tid == 0) {
         for (int s = 0; s < LG_STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(bar_acc_full(a), 1); mbar_init(bar_acc_empty(a), LG_EPI); }
+        for (int a = 0; a < 2; ++a) { mbar_init(bar_acc_full(a), 1); mbar_init(bar_acc_empty(a), EPI); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
@@ -168,11 +199,10 @@ __global__ void __launch_bounds__(LG_NT, 1) linear_gelu_kernel(const __grid_cons
         }
     } else {
         // ------------------------------------------------------------------------------------------ epilogue
-        constexpr int CW = LG_BN / (LG_EPI / 4);                       // columns per warp: 64
-        static_assert(CW == 64, "one packed bias pair per lane covers 64 columns");
+        constexpr int CW = CF::CW;                                     // columns per warp: 64 or 48
         const int sub = warp & 3, part = (warp - 2) >> 2;
         const uint32_t lane_base = (uint32_t)(32 * sub) << 16;
-        uint8_t *stage_out = sm + LG_STAGES * LG_STAGE + 1024 + (warp - 2) * LG_OUT_BYTES;
+        uint8_t *stage_out = sm + LG_STAGES * LG_STAGE + 1024 + (warp - 2) * CF::OUT_BYTES;
         uint32_t ti = 0;
         bool ok = true;
         for (long long t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++ti) {
@@ -181,11 +211,11 @@ __global__ void __launch_bounds__(LG_NT, 1) linear_gelu_kernel(const __grid_cons
             const int n0 = (int)(t % tiles_n) * LG_BN + part * CW;
             // this warp's 64 bias values, two per lane, requested before the accumulator is waited for
             uint32_t bias2 = 0u;
-            if (bias != nullptr && n0 + 2 * lane < N) bias2 = *reinterpret_cast<const uint32_t *>(bias + n0 + 2 * lane);
+            if (bias != nullptr && 2 * lane < CW && n0 + 2 * lane < N) bias2 = *reinterpret_cast<const uint32_t *>(bias + n0 + 2 * lane);
             ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full(a), (ti >> 1) & 1, 74));
             if (!ok) break;
             tc_fence_after();
-            lg_epilogue_block(tmem + lane_base + a * LG_BN + part * CW, bias2, stage_out, y, row0, n0, M, N, act, lane);
+            lg_epilogue_block<CW>(tmem + lane_base + a * LG_BN + part * CW, bias2, stage_out, y, row0, n0, M, N, act, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) lg_arrive(bar_acc_empty(a));
@@ -208,10 +238,17 @@ __global__ void __launch_bounds__(LG_NT, 1) linear_gelu_kernel(const __grid_cons
 //   No load is shared between the CTAs, so there is no multicast anywhere. Roles, epilogue and the bounded waits are those
 //   of the kernel above; the cluster meets twice more, after set-up and before tensor memory is freed. Results are those
 //   of the kernel above to the bit (the same products accumulated in the same order).
-constexpr int LP_BM = 256, LP_BN = 256, LP_STAGES = 6;
-constexpr int LP_A_BYTES = (LP_BM / 2) * LG_BK * 2, LP_B_BYTES = (LP_BN / 2) * LG_BK * 2, LP_STAGE = LP_A_BYTES + LP_B_BYTES;
-constexpr int LP_SMEM = LP_STAGES * LP_STAGE + 1024 + LG_EPI * LG_OUT_BYTES + 1024;
-static_assert(LP_SMEM <= 232448, "shared memory of the pair kernel");
+constexpr int LP_BM = 256, LP_STAGES = 6;
+constexpr int LP_A_BYTES = (LP_BM / 2) * LG_BK * 2;
+template <int BN>
+struct LpCfg {
+    static constexpr int CW = BN / (LG_EPI / 4);
+    static constexpr int B_BYTES = (BN / 2) * LG_BK * 2, STAGE = LP_A_BYTES + B_BYTES;
+    static constexpr int OUT_BYTES = 32 * (CW == 64 ? 32 : CW) * 2;
+    static constexpr int SMEM = LP_STAGES * STAGE + 1024 + LG_EPI * OUT_BYTES + 1024;
+    static_assert(BN == 256 || BN == 192, "tile width");
+    static_assert(STAGE % 1024 == 0 && SMEM <= 232448, "shared memory of the pair kernel");
+};
 
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -260,9 +297,12 @@ __device__ __forceinline__ void lp_commit_elect(uint32_t cluster_bar) {
                  "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(cluster_bar) : "memory");
 }
 
+template <int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(LG_NT, 1)
 linear_gelu_pair_kernel(const __grid_constant__ CUtensorMap mx, const __grid_constant__ CUtensorMap mw, const __nv_bfloat16 *__restrict__ bias,
                         __nv_bfloat16 *__restrict__ y, long long M, int N, int K, int act) {
+    using CF = LpCfg<BN>;
+    constexpr int LP_BN = BN, LP_STAGE = CF::STAGE;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;      // the same offset in both CTAs: one descriptor serves both
     uint8_t *sm = smem_raw + (base - smem_u32(smem_raw));
@@ -346,11 +386,10 @@ linear_gelu_pair_kernel(const __grid_constant__ CUtensorMap mx, const __grid_con
         }
     } else {
         // ------------------------------------------------------------------------------------------ epilogue (both CTAs)
-        constexpr int CW = LP_BN / (LG_EPI / 4);
-        static_assert(CW == 64, "one packed bias pair per lane covers 64 columns");
+        constexpr int CW = CF::CW;
         const int sub = warp & 3, part = (warp - 2) >> 2;
         const uint32_t lane_base = (uint32_t)(32 * sub) << 16;
-        uint8_t *stage_out = sm + LP_STAGES * LP_STAGE + 1024 + (warp - 2) * LG_OUT_BYTES;
+        uint8_t *stage_out = sm + LP_STAGES * LP_STAGE + 1024 + (warp - 2) * CF::OUT_BYTES;
         uint32_t ti = 0;
         bool ok = true;
         for (long long t = pair; t < tiles && ok; t += pairs, ++ti) {
@@ -358,11 +397,11 @@ linear_gelu_pair_kernel(const __grid_constant__ CUtensorMap mx, const __grid_con
             const long long row0 = (t / tiles_n) * LP_BM + (long long)rank * (LP_BM / 2) + 32 * sub;
             const int n0 = (int)(t % tiles_n) * LP_BN + part * CW;
             uint32_t bias2 = 0u;
-            if (bias != nullptr && n0 + 2 * lane < N) bias2 = *reinterpret_cast<const uint32_t *>(bias + n0 + 2 * lane);
+            if (bias != nullptr && 2 * lane < CW && n0 + 2 * lane < N) bias2 = *reinterpret_cast<const uint32_t *>(bias + n0 + 2 * lane);
             ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_full(a), (ti >> 1) & 1, 78));
             if (!ok) break;
             tc_fence_after();
-            lg_epilogue_block(tmem + lane_base + a * LP_BN + part * CW, bias2, stage_out, y, row0, n0, M, N, act, lane);
+            lg_epilogue_block<CW>(tmem + lane_base + a * LP_BN + part * CW, bias2, stage_out, y, row0, n0, M, N, act, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) lp_arrive_cluster(cluster_addr(bar_acc_empty(a), 0));
@@ -374,19 +413,21 @@ linear_gelu_pair_kernel(const __grid_constant__ CUtensorMap mx, const __grid_con
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
 }
 
-// 0: one CTA per 128 x 256 tile; 1: the pair kernel whenever the problem has more than one 128-row block. Timed at the MLP's
-// shape (M 8192, K 768, N 3072, L2 flushed, event resolution 2 us) the pair kernel is ahead without an activation (41 vs
-// 43 us; 20.5 vs 22.5 us at N 768) and behind with the GELU (49 vs 45 us): once the pair has made the mainloop cheaper,
+// 0: one CTA per 128 x BN tile; 1: the pair kernel whenever the problem has more than one 128-row block. Timed at the MLP's
+// shape (M 8192, K 768, N 3072; launches back to back over rotating buffers) with 256-wide tiles, the pair is ahead without
+// an activation (34.8 vs 36.7 us) and behind with the GELU (40.7 vs 39.7 us): once the pair has made the mainloop cheaper,
 // the epilogue -- unchanged, and as long as the mainloop -- is what a tile waits for. The model's only use is the one with
 // the GELU, so the single-CTA kernel stays the default.
+// Bits 1-2 pick the tile width (0 or 1: 256, 2: 192) for timing and tests.
 static int g_lg_variant = 0;
 int linear_gelu_set_variant(int v) {
-    if (v != 0 && v != 1) return PGB_ERR_BAD_SHAPE;
+    if (v < 0 || v > 5 || (v >> 1) > 2) return PGB_ERR_BAD_SHAPE;
     g_lg_variant = v;
     return PGB_OK;
 }
 
 // clusters of two CTAs of the pair kernel that can be resident at once (cached per device); 0 if the query fails
+template <int BN>
 static int lp_resident_pairs(int dev) {
     static int cached[64];
     static bool have[64];
@@ -394,49 +435,66 @@ static int lp_resident_pairs(int dev) {
     int n = 0, sms = 0;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(sms > 1 ? sms & ~1 : 2)); cfg.blockDim = dim3(LG_NT); cfg.dynamicSmemBytes = LP_SMEM;
+    cfg.gridDim = dim3((unsigned)(sms > 1 ? sms & ~1 : 2)); cfg.blockDim = dim3(LG_NT); cfg.dynamicSmemBytes = LpCfg<BN>::SMEM;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
-    if (cudaOccupancyMaxActiveClusters(&n, linear_gelu_pair_kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+    if (cudaOccupancyMaxActiveClusters(&n, linear_gelu_pair_kernel<BN>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
     if (dev >= 0 && dev < 64) { cached[dev] = n; have[dev] = true; }
     return n;
+}
+
+template <int BN, int EPI>
+static int lg_launch_single(const void *x, const void *W, const void *bias, void *y, long long M, int N, int K, int act, int sms,
+                            cudaStream_t stream) {
+    CUtensorMap mx, mw;
+    if (!tc_make_map(&mx, x, 1, M, K, K, (long long)M * K, LG_BM) || !tc_make_map(&mw, W, 1, N, K, K, (long long)N * K, BN)) {
+        set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
+        return PGB_ERR_CUDA;
+    }
+    const long long tiles = ((M + LG_BM - 1) / LG_BM) * ((N + BN - 1) / BN);
+    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+    cudaError_t e = cudaFuncSetAttribute(linear_gelu_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, LgCfg<BN, EPI>::SMEM);
+    if (e != cudaSuccess) { set_cuda_error(e, "linear_gelu smem attribute"); return PGB_ERR_CUDA; }
+    e = pdl_launch(linear_gelu_kernel<BN, EPI>, dim3(grid), dim3(LgCfg<BN, EPI>::NT), (size_t)LgCfg<BN, EPI>::SMEM, stream, mx, mw, (const __nv_bfloat16 *)bias,
+                   (__nv_bfloat16 *)y, M, N, K, act);
+    if (e != cudaSuccess) { set_cuda_error(e, "linear_gelu launch"); return PGB_ERR_CUDA; }
+    return check_launch("linear_gelu_kernel");
+}
+
+template <int BN>
+static int lg_launch_pair(const void *x, const void *W, const void *bias, void *y, long long M, int N, int K, int act, int room,
+                          cudaStream_t stream) {
+    CUtensorMap mx, mw;
+    if (!tc_make_map(&mx, x, 1, M, K, K, (long long)M * K, LP_BM / 2) || !tc_make_map(&mw, W, 1, N, K, K, (long long)N * K, BN / 2)) {
+        set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
+        return PGB_ERR_CUDA;
+    }
+    const long long tiles = ((M + LP_BM - 1) / LP_BM) * ((N + BN - 1) / BN);
+    const unsigned pairs = (unsigned)(tiles < room ? tiles : room);
+    cudaError_t e = pdl_launch(linear_gelu_pair_kernel<BN>, dim3(2 * pairs), dim3(LG_NT), (size_t)LpCfg<BN>::SMEM, stream, mx, mw,
+                               (const __nv_bfloat16 *)bias, (__nv_bfloat16 *)y, M, N, K, act);
+    if (e != cudaSuccess) { set_cuda_error(e, "linear_gelu pair launch"); return PGB_ERR_CUDA; }
+    return check_launch("linear_gelu_pair_kernel");
 }
 
 int linear_gelu_launch(const void *x, const void *W, const void *bias, void *y, long long M, int N, int K, int act, cudaStream_t stream) {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    CUtensorMap mx, mw;
-    if (g_lg_variant == 1 && M > LG_BM) {
-        cudaError_t e = cudaFuncSetAttribute(linear_gelu_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LP_SMEM);
+    const int pin = g_lg_variant >> 1;                                 // 2: tiles 192 columns wide
+    if ((g_lg_variant & 1) && M > LG_BM) {
+        cudaError_t e = cudaFuncSetAttribute(linear_gelu_pair_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, LpCfg<256>::SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_gelu_pair_kernel<192>, cudaFuncAttributeMaxDynamicSharedMemorySize, LpCfg<192>::SMEM);
         if (e != cudaSuccess) { set_cuda_error(e, "linear_gelu pair smem attribute"); return PGB_ERR_CUDA; }
-        const int room = lp_resident_pairs(dev);
-        if (room > 0) {
-            if (!tc_make_map(&mx, x, 1, M, K, K, (long long)M * K, LP_BM / 2) || !tc_make_map(&mw, W, 1, N, K, K, (long long)N * K, LP_BN / 2)) {
-                set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
-                return PGB_ERR_CUDA;
-            }
-            const long long tiles = ((M + LP_BM - 1) / LP_BM) * ((N + LP_BN - 1) / LP_BN);
-            const unsigned pairs = (unsigned)(tiles < room ? tiles : room);
-            e = pdl_launch(linear_gelu_pair_kernel, dim3(2 * pairs), dim3(LG_NT), (size_t)LP_SMEM, stream, mx, mw, (const __nv_bfloat16 *)bias,
-                           (__nv_bfloat16 *)y, M, N, K, act);
-            if (e != cudaSuccess) { set_cuda_error(e, "linear_gelu pair launch"); return PGB_ERR_CUDA; }
-            return check_launch("linear_gelu_pair_kernel");
+        const int r256 = lp_resident_pairs<256>(dev), r192 = lp_resident_pairs<192>(dev);
+        if (r256 > 0 && r192 > 0) {
+            if (pin == 2) return lg_launch_pair<192>(x, W, bias, y, M, N, K, act, r192, stream);
+            return lg_launch_pair<256>(x, W, bias, y, M, N, K, act, r256, stream);
         }
     }
-    if (!tc_make_map(&mx, x, 1, M, K, K, (long long)M * K, LG_BM) || !tc_make_map(&mw, W, 1, N, K, K, (long long)N * K, LG_BN)) {
-        set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled");
-        return PGB_ERR_CUDA;
-    }
-    const long long tiles = ((M + LG_BM - 1) / LG_BM) * ((N + LG_BN - 1) / LG_BN);
-    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    cudaError_t e = cudaFuncSetAttribute(linear_gelu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LG_SMEM);
-    if (e != cudaSuccess) { set_cuda_error(e, "linear_gelu smem attribute"); return PGB_ERR_CUDA; }
-    e = pdl_launch(linear_gelu_kernel, dim3(grid), dim3(LG_NT), (size_t)LG_SMEM, stream, mx, mw, (const __nv_bfloat16 *)bias,
-                   (__nv_bfloat16 *)y, M, N, K, act);
-    if (e != cudaSuccess) { set_cuda_error(e, "linear_gelu launch"); return PGB_ERR_CUDA; }
-    return check_launch("linear_gelu_kernel");
+    if (pin == 2) return lg_launch_single<192, LG_EPI>(x, W, bias, y, M, N, K, act, sms, stream);
+    return lg_launch_single<256, LG_EPI>(x, W, bias, y, M, N, K, act, sms, stream);
 }
 
 int linear_gelu_error_flag(int *out) { return tc_read_error_flag(out); }

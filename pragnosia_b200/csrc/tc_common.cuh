@@ -148,6 +148,16 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, float (&v)[32])
                  : "r"(taddr) : "memory");
 }
 
+// 32 lanes x 16 columns of 32-bit, no wait (tmem_ld_wait() before v is used)
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, float (&v)[16]) {
+    uint32_t *r = reinterpret_cast<uint32_t *>(v);
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+}
+
 // 16 lanes x 256 bits per repetition: thread l of the warp gets, for block j of 8 columns,
 //   v[4j+0], v[4j+1] = lane (base + l/4),     columns 8j + 2(l%4), +1
 //   v[4j+2], v[4j+3] = lane (base + l/4 + 8), same columns

@@ -458,10 +458,11 @@ def test_linear_act_tensor_core_gemm(M, K, N, act):
     assert torch.equal(y, ops.linear_act(x, W, b, act=act))                   # deterministic
     y3 = ops.linear_act(x.view(-1, 1, K) if M % 1 == 0 else x, W, None, act=act)
     assert tuple(y3.shape) == (M, 1, N)
-    # the same tile on a pair of SMs (two-CTA cluster, tcgen05.mma.cta_group::2): the same bits
-    _lib.check(_lib.lib().pgb_linear_act_set_variant(1), "pgb_linear_act_set_variant")
+    # tiles 256 and 192 columns wide, on one SM and on a pair of SMs (two-CTA cluster, tcgen05.mma.cta_group::2): the same bits
     try:
-        assert torch.equal(y, ops.linear_act(x, W, b, act=act))
+        for variant in (2, 4, 1, 3, 5):
+            _lib.check(_lib.lib().pgb_linear_act_set_variant(variant), "pgb_linear_act_set_variant")
+            assert torch.equal(y, ops.linear_act(x, W, b, act=act)), variant
     finally:
         _lib.check(_lib.lib().pgb_linear_act_set_variant(0), "pgb_linear_act_set_variant")
     out = ctypes.c_int(-1)
