@@ -326,7 +326,7 @@ def kernel_rooflines(pk):
     HBM copy bandwidth. The first entry is the kernel the timed step spends its carrier time in."""
     from pragnosia_b200 import kernel_bench as kb
     out = []
-    for name in ("layer_prefill_cfg1", "layer_prefill", "prefill", "prefill_d128", "prefill_delta", "prefill_delta_d64", "decode", "decode_b1024",
+    for name in ("layer_prefill_cfg1", "layer_prefill", "prefill", "prefill_d128", "prefill_delta", "prefill_delta_d64", "prefill_delta_cfg3", "decode", "decode_b1024",
                  "decode_delta", "decode_token", "decode_token_b4", "batch_linear", "lambda", "lambda_bcast", "prep", "add_norm"):
         us, alg = kb.time_case(name)
         out.append(dict(kernel=name, what=kb.CASES[name][1], bound="hbm", achieved=alg / us / 1e3, peak=pk["hbm_gbs"], unit="GB/s",

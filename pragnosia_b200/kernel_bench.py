@@ -42,11 +42,17 @@ def _layer_prefill(B, H, T, D):
     return fn, alg
 
 
-def _prefill_delta(B, H, T, D):
+def _prefill_delta(B, H, T, D, on_device=False):
     dev = "cuda"
-    x = synth.assoc_op_inputs(B, H, T, D, seed=1, delta=True, with_state=True)
-    q, k, v = (x[n].to(dev).to(torch.bfloat16) for n in "qkv")
-    la, be, S0 = x["la"].to(dev), x["beta"].to(dev), x["S0"].to(dev)
+    if on_device:                                                     # the same distributions drawn on the GPU (a full-size case)
+        g = torch.Generator(device=dev).manual_seed(1)
+        r = lambda *shape: torch.randn(*shape, generator=g, device=dev)
+        q, k, v = r(B, H, T, D).to(torch.bfloat16), torch.nn.functional.normalize(r(B, H, T, D), dim=-1).to(torch.bfloat16), r(B, H, T, D).to(torch.bfloat16)
+        la, be, S0 = torch.nn.functional.logsigmoid(r(B, H, T) + 2.0), torch.sigmoid(r(B, H, T)), r(B, H, D, D) * 0.1
+    else:
+        x = synth.assoc_op_inputs(B, H, T, D, seed=1, delta=True, with_state=True)
+        q, k, v = (x[n].to(dev).to(torch.bfloat16) for n in "qkv")
+        la, be, S0 = x["la"].to(dev), x["beta"].to(dev), x["S0"].to(dev)
     alg = B * H * T * (4 * D * 2 + 8) + 2 * B * H * D * D * 4
     return (lambda: ops.prefill(q, k, v, la, be, S0)), alg
 
@@ -97,6 +103,7 @@ CASES = {
     "layer_prefill_cfg1": (lambda: _layer_prefill(16, 12, 512, 64), "the same at one configuration-1 window: B16 H12 T512 D64"),
     "prefill_delta": (lambda: _prefill_delta(8, 16, 1024, 128), "delta-rule chunked prefill, tensor cores: B8 H16 T1024 D128 bf16 I/O"),
     "prefill_delta_d64": (lambda: _prefill_delta(16, 12, 1024, 64), "the same at head dim 64: B16 H12 T1024 D64"),
+    "prefill_delta_cfg3": (lambda: _prefill_delta(8, 16, 8192, 128, on_device=True), "configuration 3 at full size: B8 H16 T8192 D128 bf16 I/O"),
     "prep": (lambda: _prep(16, 512, 12, 64), "normalise / gate / rotate / transpose: B16 T512 H12 D64 bf16"),
     "decode": (lambda: _decode(64, 12, 64), "fused recurrent decode step, plain rule, in place: B64 H12 D64"),
     "decode_delta": (lambda: _decode(64, 12, 64, True), "fused recurrent decode step, delta rule, in place: B64 H12 D64"),
