@@ -112,6 +112,7 @@ CASES = {
     "lambda_bcast": (lambda: _lambda(64, 1024, 768, True), "per-token lambda scan, one angle per channel: B64 T1024 D768 fp32"),
     "add_norm": (lambda: _add_norm(8192, 768), "residual add + RMS norm: 8192 rows of 768 bf16"),
     "mlp_up": (lambda: _linear_act(8192, 768, 3072), "MLP up-projection + bias + erf-GELU as one tensor-core GEMM: M8192 K768 N3072 bf16"),
+    "mlp_up_pair": (lambda: _linear_act(8192, 768, 3072, variant=1), "the same GEMM with a 256 x 256 tile per pair of SMs (two-CTA cluster, cta_group::2)"),
     "skinny": (lambda: _skinny(1, 768, 3072), "decode-step linear (add + RMS norm + linear + GELU) at batch 1: K768 N3072 bf16"),
     "batch_linear": (lambda: _batch_linear(64, 768, 2328), "decode-step linear for 64 rows on the tensor cores (bias): K768 N2328 bf16"),
     "decode_token": (lambda: _decode_token(1), "the whole decode step of the configuration-2 model as one launch, batch 1 (12 layers, d768, vocabulary 8192)"),
@@ -119,15 +120,24 @@ CASES = {
 }
 
 # floating-point operations per launch of the cases that are bound by the tensor pipe rather than by HBM
-FLOPS = {"mlp_up": 2 * 8192 * 768 * 3072}
+FLOPS = {"mlp_up": 2 * 8192 * 768 * 3072, "mlp_up_pair": 2 * 8192 * 768 * 3072}
 
 
-def _linear_act(M, K, N):
+def _linear_act(M, K, N, variant=0):
     dev = "cuda"
     x = torch.randn(M, K, device=dev).to(torch.bfloat16)
     W = (torch.randn(N, K, device=dev) * K ** -0.5).to(torch.bfloat16)
     b = torch.randn(N, device=dev).to(torch.bfloat16)
-    return (lambda: ops.linear_act(x, W, b, act="gelu")), (M * K + N * K + N + M * N) * 2
+
+    def fn():
+        if variant:                                                   # the process-wide switch, put back after the launch
+            _lib.check(_lib.lib().pgb_linear_act_set_variant(variant), "pgb_linear_act_set_variant")
+        try:
+            return ops.linear_act(x, W, b, act="gelu")
+        finally:
+            if variant:
+                _lib.check(_lib.lib().pgb_linear_act_set_variant(0), "pgb_linear_act_set_variant")
+    return fn, (M * K + N * K + N + M * N) * 2
 
 
 def _skinny(B, K, N):
