@@ -146,3 +146,16 @@ def test_new_entry_points_reject_bad_calls(L):
     tok = lambda **kw: L.pgb_decode_token_fwd(one, 12, one, one, one, kw.get("nb", one), 2, 1e-5, one, one, one, one, kw.get("wb", 10 ** 6),
                                               one, one, kw.get("B", 1), 768, 12, kw.get("D", 64), 2328, 3072, 50257, 512, 0, None)
     assert tok(nb=None) == 1 and tok(wb=10) == 2 and tok(B=5) == 7 and tok(D=96) == 3
+
+
+def test_bench_table_names_are_kernel_bench_cases():
+    """bench.py's per-kernel table is built from kernel_bench cases by name: every name it asks for exists."""
+    import ast
+    import pathlib
+    from pragnosia_b200 import kernel_bench as kb
+    src = (pathlib.Path(__file__).resolve().parents[1] / "bench.py").read_text()
+    fn = next(n for n in ast.walk(ast.parse(src)) if isinstance(n, ast.FunctionDef) and n.name == "kernel_rooflines")
+    names = [c.value for t in ast.walk(fn) if isinstance(t, ast.Tuple) for c in t.elts if isinstance(c, ast.Constant) and isinstance(c.value, str)]
+    asked = [n for n in names if n in kb.CASES or n.startswith(("prefill", "decode", "lambda", "layer_"))]
+    assert len(asked) >= 15 and all(n in kb.CASES for n in asked), [n for n in asked if n not in kb.CASES]
+    assert all(n in kb.CASES for n in kb.FLOPS)

@@ -554,3 +554,19 @@ def test_batch_linear_folded_norm_and_residual(norm_cls):
     xe, se = ops.decode_embed(torch.arange(B, device=DEV), torch.tensor([3], device=DEV), W[:64].contiguous(), W[100:120].contiguous(), want_sums=True)
     assert torch.allclose(se[0, :, 0].cpu(), xe.float().sum(1).cpu(), rtol=1e-4, atol=1e-3)
     assert torch.allclose(se[0, :, 1].cpu(), (xe.float() ** 2).sum(1).cpu(), rtol=1e-4, atol=1e-3)
+
+
+def test_every_kernel_bench_case_launches():
+    """The timed cases of pragnosia_b200.kernel_bench (what bench.py's per-kernel table and the profiling commands run):
+    each one builds its inputs, launches once and leaves the wait-error flag clear."""
+    from pragnosia_b200 import kernel_bench as kb
+    with torch.no_grad():
+        for name in sorted(kb.CASES):
+            fn, alg = kb.CASES[name][0]()
+            fn()
+            torch.cuda.synchronize()
+            assert alg > 0, name
+            del fn
+    out = ctypes.c_int(-1)
+    _lib.check(_lib.lib().pgb_tc_error_flag(ctypes.byref(out)), "pgb_tc_error_flag")
+    assert out.value == 0
