@@ -447,6 +447,12 @@ int pgb_aspin_decode_step(const void *qp, const void *kp, const void *vp, int in
                           const float *rms_weight, float rms_eps, void *o, int out_dtype, long long out_stride_b,
                           int B, int H, int D, void *stream);
 
+/* Which kernel pgb_aspin_decode_step uses at head dim 64: 0 (default) = from 512 (sequence, head) pairs up one warp per
+ * pair, a lane owning two value columns of all key rows (no block barrier, no partial sums through shared memory), below
+ * that one 256-thread CTA per pair (the kernel head dim 128 always uses); 1 = always the CTA per pair; 2 = always the warp
+ * per pair. Process-wide; for A/B timing and tests. No counterpart in the reference. */
+int pgb_decode_set_variant(int variant);
+
 #ifdef __cplusplus
 }
 #endif

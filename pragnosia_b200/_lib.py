@@ -50,6 +50,7 @@ SIGNATURES = {
     "pgb_tc_error_flag": [_vp],
     "pgb_tc_set_variant": [_i],
     "pgb_linear_act_set_variant": [_i],
+    "pgb_decode_set_variant": [_i],
     "pgb_rotate_pairs": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "pgb_skinny_linear_ex": [_vp, _vp, _vp, _vp, _i, _f, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp],
     "pgb_lambda_scan_time_segments": [_i, _i, _i, _i],

@@ -60,6 +60,7 @@ int decode_sample_launch(const void *, int, float, float, unsigned long long, lo
 int linear_gelu_launch(const void *, const void *, const void *, void *, long long, int, int, int, cudaStream_t);
 int linear_gelu_error_flag(int *);
 int linear_gelu_set_variant(int);
+int decode_set_variant(int);
 int skinny_linear_launch(const void *, const void *, const void *, const void *, int, float, const void *, const void *, int, void *,
                          void *, int, int, int, int, cudaStream_t);
 int add_norm_launch(const void *, const void *, const void *, const void *, float, int, void *, void *, long long, int, int,
@@ -448,6 +449,8 @@ int pgb_linear_act(const void *x, const void *W, const void *bias, void *y, long
 }
 
 int pgb_linear_act_set_variant(int variant) { return linear_gelu_set_variant(variant); }
+
+int pgb_decode_set_variant(int variant) { return decode_set_variant(variant); }
 
 int pgb_batch_linear_ex(const void *x, const void *W, const void *bias, void *y, int B, int N, int K, int act, const float *row_sums_in,
                         int parts_in, const float *c1, const float *c2, int norm_kind, float eps, const void *resid, float *row_sums_out,

@@ -140,6 +140,7 @@ def test_new_entry_points_reject_bad_calls(L):
     assert L.pgb_batch_linear_ex(one, one, one, one, 4, 16, 64, 0, one, 1, one, one, 1, 1e-5, None, None, 0, None) == 1   # folded norm + bias
     assert L.pgb_batch_linear_ex(one, one, None, one, 4, 16, 64, 0, None, 0, None, None, 0, 0.0, None, None, 2, None) == 2  # unknown flag
     assert L.pgb_batch_linear_parts(768) == 48
+    assert L.pgb_decode_set_variant(3) == 2 and L.pgb_decode_set_variant(0) == 0
     assert L.pgb_linear_act_set_variant(6) == 2 and L.pgb_linear_act_set_variant(-1) == 2 and L.pgb_linear_act_set_variant(0) == 0
     # the one-launch decode step: scratch size, then the rejects (bias missing for a layer norm, short scratch, batch, head dim)
     assert L.pgb_decode_token_work_bytes(1, 768, 2328, 3072) == 2 * (4 * 768 + 2328 + 3072)

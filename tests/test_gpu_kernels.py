@@ -246,7 +246,19 @@ def test_prefill_extreme_decay_is_finite():
 @pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("delta", [False, True])
 @pytest.mark.parametrize("B", [1, 64])
-def test_decode_step_against_oracle(D, delta, B):
+@pytest.mark.parametrize("variant", [1, 2])
+def test_decode_step_against_oracle(D, delta, B, variant):
+    """variant 1: one CTA per (sequence, head) everywhere; 2: head dim 64 runs one warp per (sequence, head)."""
+    if variant == 2 and D == 128:
+        pytest.skip("head dim 128 has one kernel")
+    _lib.check(_lib.lib().pgb_decode_set_variant(variant), "pgb_decode_set_variant")
+    try:
+        _decode_step_against_oracle(D, delta, B)
+    finally:
+        _lib.check(_lib.lib().pgb_decode_set_variant(0), "pgb_decode_set_variant")
+
+
+def _decode_step_against_oracle(D, delta, B):
     H = 3
     g = torch.Generator().manual_seed(D + B)
     qp, kp, vp = (torch.randn(B, H, D, generator=g) * 2 for _ in range(3))
