@@ -4,6 +4,7 @@ There is no fallback: if the shared library is missing, or a call returns a non-
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
 from pathlib import Path
 
@@ -142,3 +143,20 @@ def need_cuda(*ts) -> None:
     for t in ts:
         if t is not None and not t.is_cuda:
             raise RuntimeError("pragnosia_b200 ops run on CUDA tensors only (there is no CPU path)")
+
+
+@contextlib.contextmanager
+def graph_capture(graph, **kw):
+    """torch.cuda.graph(graph, **kw) with the cyclic garbage collector out of the way. A CUDAGraph of an earlier model
+    that the collector frees in the middle of a capture destroys its executable graph; CUDA refuses that call while the
+    thread is capturing and the capture is invalidated. So: collect first, then no collections until the capture ends."""
+    import gc
+    gc.collect()
+    was_enabled = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph, **kw):
+            yield
+    finally:
+        if was_enabled:
+            gc.enable()

@@ -14,6 +14,7 @@ import torch
 import torch.nn.functional as F
 
 from . import ops
+from ._lib import graph_capture
 from .assoc import AssocCarrier
 
 
@@ -254,7 +255,7 @@ class Decoder:
                 for _ in range(2): self._step()
             torch.cuda.current_stream().wait_stream(s)
             self._graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self._graph):
+            with graph_capture(self._graph):
                 self.logits = self._step()
             for st, sv in zip(self.states, saved):           # warm-up and capture advanced the state: restore it
                 for a, b in zip(st, sv):
@@ -313,7 +314,7 @@ class Decoder:
                 for _ in range(2): self._token_body(temp, seed)
             torch.cuda.current_stream().wait_stream(s)
             self._gen_graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self._gen_graph):
+            with graph_capture(self._gen_graph):
                 self._token_body(temp, seed)
             for st, sv in zip(self.states, saved):           # warm-up and capture advanced the state: restore it
                 for a, b in zip(st, sv):

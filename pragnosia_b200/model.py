@@ -8,6 +8,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from . import ops
+from ._lib import graph_capture
 from .assoc import AssocCarrier
 from .spin import SpinCarrier
 
@@ -211,7 +212,7 @@ class _StepGraph:
             torch.cuda.current_stream().wait_stream(warm)
             torch.cuda.synchronize()
             self.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph):
+            with graph_capture(self.graph):
                 self.out, self.states = self._pass()
         self.ids.copy_(ids)
         self.graph.replay()
@@ -258,10 +259,10 @@ class _WindowGraphs:
             self._pass(st, True)
         torch.cuda.current_stream().wait_stream(side)
         self.first = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.first):
+        with graph_capture(self.first):
             self.out_first, self.states = self._pass(none, False)
         self.later = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.later, pool=self.first.pool()):
+        with graph_capture(self.later, pool=self.first.pool()):
             self.out_later, _ = self._pass(self.states, True)
 
     def __call__(self, ids, first):

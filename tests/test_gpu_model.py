@@ -210,3 +210,30 @@ def test_mid_batch_decode_through_the_tensor_core_linear(mixer, norm, B):
         # tolerances in test_gpu_config2
         assert err[k][0] <= max(3e-2, 2.0 * err[(False, False)][0]), err
         assert err[k][1] <= max(1e-2, 1.25 * err[(False, False)][1]), err
+
+
+def test_capture_survives_garbage_graphs():
+    """Models whose CUDA graphs are garbage in reference cycles, and a collector set to run every few allocations: the next
+    capture still succeeds (a graph freed by the collector in the middle of a capture would invalidate it)."""
+    import gc
+    ids = synth.token_ids(2, 128, 256, seed=5).to(DEV)
+    m, _, _ = small_lm("aspin", "rms", torch.bfloat16)
+    ref = m.forward_carried(ids).clone()
+
+    class Box:
+        pass
+    for _ in range(3):
+        m2, _, _ = small_lm("aspin", "rms", torch.bfloat16)
+        m2.forward_carried(ids)
+        b = Box(); b.m = m2; b.me = b                                 # a cycle: only the cyclic collector frees the model and its graphs
+        del m2, b
+    old = gc.get_threshold()
+    gc.set_threshold(5, 2, 2)
+    try:
+        m3, _, _ = small_lm("aspin", "rms", torch.bfloat16)
+        out = m3.forward_carried(ids)
+        dec = Decoder(m3, batch=2)
+        dec.prefill(ids[:, :40]); dec.step(ids[:, 40])
+    finally:
+        gc.set_threshold(*old)
+    assert torch.equal(out, ref)
