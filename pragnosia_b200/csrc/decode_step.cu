@@ -118,8 +118,7 @@ __global__ void __launch_bounds__(DW_WARPS * 32) decode_step_warp_kernel(DecodeA
     // ---- the read: optional per-head RMS norm, store
     if (a.rms_w != nullptr) {
         const float sc = rsqrtf(warp_sum(acc.x * acc.x + acc.y * acc.y) / (float)D + a.rms_eps);
-        const float2 wv = *reinterpret_cast<const float2 *>(a.rms_w + 2 * lane);
-        acc.x = acc.x * sc * wv.x; acc.y = acc.y * sc * wv.y;
+        acc.x = acc.x * sc * a.rms_w[2 * lane]; acc.y = acc.y * sc * a.rms_w[2 * lane + 1];   // two loads: the weight need only be 4-byte aligned
     }
     TOUT *o = (TOUT *)a.o + (size_t)b * a.out_sb + (size_t)h * D + 2 * lane;
     from_f32(o[0], acc.x); from_f32(o[1], acc.y);
